@@ -1,0 +1,452 @@
+// Python bindings: thin checks + raw-pointer calls into the C entry points of fmb_api.h. Every
+// function enqueues on the current CUDA stream of the tensor's device and never synchronises.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "fmb_api.h"
+
+extern "C" {
+int fmb_sqnorm_f32_scratch(const float* x, float* partial, float* out, long long n, int accumulate, cudaStream_t stream);
+int fmb_router_blocks(long long rows);
+int fmb_router_fwd(const void* logits, long long ld, int dtype, float* probs, float* weights, int* idx, float* lse,
+                   float* psum_partial, int* counts, long long rows, int E, int k, int nblocks, cudaStream_t stream);
+int fmb_router_bwd(const float* probs, const int* idx, const float* weights, const float* lse, const float* dweights,
+                   const float* aux_grad, const float* zc, void* dlogits, long long ld, int dtype, long long rows, int E,
+                   int k, cudaStream_t stream);
+int fmb_moe_plan(const int* idx, int* chunk_counts, int* region, int* meta, int* slot_of_entry, int* token_of_slot,
+                 long long entries, int E, int k, int align, int cap, int mode, cudaStream_t stream);
+int fmb_moe_combine_bwd(const void* dout, const void* ys, const int* slot_of_entry, const float* w, void* dys, float* dw,
+                        long long entries, int k, int d, cudaStream_t stream);
+}
+
+namespace {
+
+using torch::Tensor;
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int dt(const Tensor& t) {
+  if (t.scalar_type() == at::kBFloat16) return FMB_BF16;
+  if (t.scalar_type() == at::kFloat) return FMB_F32;
+  TORCH_CHECK(false, "forgeminds_b200: unsupported dtype ", t.scalar_type());
+}
+
+void ok(int rc, const char* what) {
+  TORCH_CHECK(rc == 0, "forgeminds_b200 native call '", what, "' failed with code ", rc);
+}
+
+void cuda_contig(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+
+const void* cptr(const c10::optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+
+// D = alpha * op(A) op(B)^T + beta * C.  A is [M,K] (a_mn=false) or [K,M] (a_mn=true); B is [N,K]
+// or [K,N]. Rows may be strided (last dim contiguous).
+void gemm(const Tensor& A, const Tensor& B, Tensor& D, const c10::optional<Tensor>& C, bool a_mn, bool b_mn,
+          double alpha, double beta, const c10::optional<Tensor>& alpha_dev, bool allow_split,
+          const c10::optional<Tensor>& status, int64_t force_bn) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && D.is_cuda(), "gemm: CUDA tensors required");
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: bf16 operands required");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && D.dim() == 2, "gemm: 2-D tensors required");
+  TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1 && D.stride(1) == 1, "gemm: innermost dimension must be contiguous");
+  const int64_t M = a_mn ? A.size(1) : A.size(0);
+  const int64_t K = a_mn ? A.size(0) : A.size(1);
+  const int64_t N = b_mn ? B.size(1) : B.size(0);
+  const int64_t Kb = b_mn ? B.size(0) : B.size(1);
+  TORCH_CHECK(K == Kb, "gemm: inner dimensions differ: ", K, " vs ", Kb);
+  TORCH_CHECK(D.size(0) == M && D.size(1) == N, "gemm: output shape mismatch");
+  const bool d_f32 = D.scalar_type() == at::kFloat;
+  TORCH_CHECK(d_f32 || D.scalar_type() == at::kBFloat16, "gemm: output must be bf16 or fp32");
+  const void* c = nullptr;
+  int64_t ldc = 0;
+  int c_f32 = 0;
+  if (C.has_value() && C->defined()) {
+    TORCH_CHECK(C->dim() == 2 && C->size(0) == M && C->size(1) == N && C->stride(1) == 1, "gemm: C shape mismatch");
+    c = C->data_ptr();
+    ldc = C->stride(0);
+    c_f32 = C->scalar_type() == at::kFloat;
+    TORCH_CHECK(c_f32 || C->scalar_type() == at::kBFloat16, "gemm: C must be bf16 or fp32");
+  }
+  c10::cuda::CUDAGuard guard(A.device());
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  int rc = fmb_gemm_bf16(A.data_ptr(), B.data_ptr(), D.data_ptr(), c, static_cast<int>(M), static_cast<int>(N),
+                         static_cast<int>(K), a_mn, b_mn, A.stride(0), B.stride(0), D.stride(0), ldc, d_f32, c_f32,
+                         static_cast<float>(alpha), static_cast<float>(beta), static_cast<const float*>(cptr(alpha_dev)), allow_split, st,
+                         static_cast<int>(force_bn), cur_stream());
+  ok(rc, "gemm_bf16");
+}
+
+std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
+  cuda_contig(x, "x"); cuda_contig(w, "w");
+  const int64_t d = x.size(-1);
+  const int64_t rows = x.numel() / d;
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  Tensor rstd = torch::empty({rows}, x.options().dtype(at::kFloat));
+  ok(fmb_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows, static_cast<int>(d),
+                     static_cast<float>(eps), dt(x), dt(w), cur_stream()), "rmsnorm_fwd");
+  return {y, rstd};
+}
+
+std::vector<Tensor> add_rmsnorm_fwd(const Tensor& x, const Tensor& delta, const Tensor& w, double eps) {
+  cuda_contig(x, "x"); cuda_contig(delta, "delta"); cuda_contig(w, "w");
+  const int64_t d = x.size(-1);
+  const int64_t rows = x.numel() / d;
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor xn = torch::empty_like(x), y = torch::empty_like(x);
+  Tensor rstd = torch::empty({rows}, x.options().dtype(at::kFloat));
+  ok(fmb_add_rmsnorm_fwd(x.data_ptr(), delta.data_ptr(), w.data_ptr(), xn.data_ptr(), y.data_ptr(),
+                         rstd.data_ptr<float>(), rows, static_cast<int>(d), static_cast<float>(eps), dt(x), dt(w),
+                         cur_stream()), "add_rmsnorm_fwd");
+  return {xn, y, rstd};
+}
+
+// returns (dx, dw fp32)
+std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd,
+                                const c10::optional<Tensor>& dres, bool need_dw) {
+  cuda_contig(dy, "dy"); cuda_contig(x, "x"); cuda_contig(w, "w");
+  const int64_t d = x.size(-1);
+  const int64_t rows = x.numel() / d;
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor dx = torch::empty_like(x);
+  const int nb = fmb_rmsnorm_bwd_blocks(rows, static_cast<int>(d));
+  Tensor dwp, dw;
+  if (need_dw) {
+    dwp = torch::empty({nb, d}, x.options().dtype(at::kFloat));
+    dw = torch::empty({d}, x.options().dtype(at::kFloat));
+  }
+  if (dres.has_value() && dres->defined()) cuda_contig(*dres, "dres");
+  ok(fmb_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), cptr(dres), dx.data_ptr(),
+                     need_dw ? dwp.data_ptr<float>() : nullptr, need_dw ? dw.data_ptr<float>() : nullptr, 0, rows,
+                     static_cast<int>(d), dt(x), dt(w), nb, cur_stream()), "rmsnorm_bwd");
+  return {dx, dw};
+}
+
+Tensor swiglu_fwd(const Tensor& gate, const Tensor& up) {
+  TORCH_CHECK(gate.is_cuda() && gate.stride(-1) == 1 && up.stride(-1) == 1 && gate.dim() == 2 && up.dim() == 2);
+  TORCH_CHECK(gate.stride(0) == up.stride(0), "swiglu: gate and up must share a row pitch");
+  c10::cuda::CUDAGuard guard(gate.device());
+  Tensor out = torch::empty({gate.size(0), gate.size(1)}, gate.options());
+  ok(fmb_swiglu_fwd(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.size(0), static_cast<int>(gate.size(1)),
+                    gate.stride(0), dt(gate), cur_stream()), "swiglu_fwd");
+  return out;
+}
+
+void swiglu_bwd(const Tensor& gate, const Tensor& up, const Tensor& dy, Tensor& dgate, Tensor& dup) {
+  TORCH_CHECK(gate.dim() == 2 && gate.stride(0) == up.stride(0) && dgate.stride(0) == gate.stride(0) &&
+              dup.stride(0) == gate.stride(0), "swiglu_bwd: all gate/up views must share one row pitch");
+  cuda_contig(dy, "dy");
+  c10::cuda::CUDAGuard guard(gate.device());
+  ok(fmb_swiglu_bwd(gate.data_ptr(), up.data_ptr(), dy.data_ptr(), dgate.data_ptr(), dup.data_ptr(), gate.size(0),
+                    static_cast<int>(gate.size(1)), gate.stride(0), dt(gate), cur_stream()), "swiglu_bwd");
+}
+
+void rope(const Tensor& x, Tensor& out, const Tensor& cos, const Tensor& sin, int64_t T, int64_t n_rot,
+          int64_t heads_total, int64_t hd, double sign) {
+  cuda_contig(x, "x"); cuda_contig(out, "out"); cuda_contig(cos, "cos"); cuda_contig(sin, "sin");
+  TORCH_CHECK(out.numel() == x.numel() && out.scalar_type() == x.scalar_type(), "rope: out must match x");
+  TORCH_CHECK(cos.scalar_type() == at::kFloat && sin.scalar_type() == at::kFloat, "rope tables must be fp32");
+  TORCH_CHECK(cos.numel() >= T * hd / 2, "rope table shorter than the sequence");
+  const int64_t rows = x.numel() / (heads_total * hd);
+  c10::cuda::CUDAGuard guard(x.device());
+  ok(fmb_rope(x.data_ptr(), out.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), rows, static_cast<int>(T),
+              static_cast<int>(n_rot), static_cast<int>(heads_total), static_cast<int>(hd), static_cast<float>(sign),
+              dt(x), cur_stream()), "rope");
+}
+
+std::vector<Tensor> qk_norm_rope_fwd(const Tensor& x, const Tensor& w, const Tensor& cos, const Tensor& sin, double eps) {
+  cuda_contig(x, "x"); cuda_contig(w, "w"); cuda_contig(cos, "cos"); cuda_contig(sin, "sin");
+  TORCH_CHECK(x.dim() == 4, "qk_norm_rope expects [B,T,H,D]");
+  const int64_t T = x.size(1), H = x.size(2), hd = x.size(3);
+  const int64_t rows = x.size(0) * T;
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  Tensor rstd = torch::empty({rows * H}, x.options().dtype(at::kFloat));
+  ok(fmb_qk_norm_rope_fwd(x.data_ptr(), w.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), y.data_ptr(),
+                          rstd.data_ptr<float>(), rows, static_cast<int>(T), static_cast<int>(H), static_cast<int>(hd),
+                          static_cast<float>(eps), dt(x), dt(w), cur_stream()), "qk_norm_rope_fwd");
+  return {y, rstd};
+}
+
+std::vector<Tensor> qk_norm_rope_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& cos,
+                                     const Tensor& sin, const Tensor& rstd) {
+  cuda_contig(dy, "dy"); cuda_contig(x, "x");
+  const int64_t T = x.size(1), H = x.size(2), hd = x.size(3);
+  const int64_t rows = x.size(0) * T;
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor dx = torch::empty_like(x);
+  const int nb = 296;
+  Tensor dwp = torch::zeros({nb, hd}, x.options().dtype(at::kFloat));
+  Tensor dw = torch::empty({hd}, x.options().dtype(at::kFloat));
+  ok(fmb_qk_norm_rope_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(),
+                          rstd.data_ptr<float>(), dx.data_ptr(), dwp.data_ptr<float>(), dw.data_ptr<float>(), rows,
+                          static_cast<int>(T), static_cast<int>(H), static_cast<int>(hd), dt(x), dt(w), nb,
+                          cur_stream()), "qk_norm_rope_bwd");
+  return {dx, dw};
+}
+
+Tensor softmax_fwd(const Tensor& x) {
+  cuda_contig(x, "x");
+  const int64_t n = x.size(-1);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  ok(fmb_softmax_fwd(x.data_ptr(), y.data_ptr(), x.numel() / n, static_cast<int>(n), dt(x), cur_stream()), "softmax_fwd");
+  return y;
+}
+
+Tensor softmax_bwd(const Tensor& y, const Tensor& dy) {
+  cuda_contig(y, "y"); cuda_contig(dy, "dy");
+  const int64_t n = y.size(-1);
+  c10::cuda::CUDAGuard guard(y.device());
+  Tensor dx = torch::empty_like(y);
+  ok(fmb_softmax_bwd(y.data_ptr(), dy.data_ptr(), dx.data_ptr(), y.numel() / n, static_cast<int>(n), dt(y),
+                     cur_stream()), "softmax_bwd");
+  return dx;
+}
+
+std::vector<Tensor> topk(const Tensor& x, int64_t k) {
+  cuda_contig(x, "x");
+  const int64_t n = x.size(-1);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto shape = x.sizes().vec();
+  shape.back() = k;
+  Tensor values = torch::empty(shape, x.options());
+  Tensor indices = torch::empty(shape, x.options().dtype(at::kLong));
+  ok(fmb_topk(x.data_ptr(), values.data_ptr(), reinterpret_cast<long long*>(indices.data_ptr<int64_t>()),
+              x.numel() / n, static_cast<int>(n), static_cast<int>(k), dt(x), cur_stream()), "topk");
+  return {values, indices};
+}
+
+// logits [rows, V] bf16 are overwritten with their gradient (scaled); returns per-row losses
+Tensor ce_fwd_bwd(Tensor& logits, const Tensor& labels, double grad_scale, const c10::optional<Tensor>& scale_dev,
+                  int64_t ignore_index, bool write_grad) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1 && logits.scalar_type() == at::kBFloat16);
+  cuda_contig(labels, "labels");
+  TORCH_CHECK(labels.scalar_type() == at::kLong && labels.numel() == logits.size(0));
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor row_loss = torch::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  ok(fmb_ce_fwd_bwd(logits.data_ptr(), reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()),
+                    row_loss.data_ptr<float>(), logits.size(0), static_cast<int>(logits.size(1)), logits.stride(0),
+                    static_cast<float>(grad_scale), static_cast<const float*>(cptr(scale_dev)), ignore_index, write_grad,
+                    cur_stream()), "ce_fwd_bwd");
+  return row_loss;
+}
+
+std::vector<Tensor> kl_fwd_bwd(const Tensor& student, const Tensor& teacher, double grad_scale, bool write_grad,
+                               bool reuse_student) {
+  cuda_contig(student, "student"); cuda_contig(teacher, "teacher");
+  const int64_t V = student.size(-1);
+  const int64_t rows = student.numel() / V;
+  c10::cuda::CUDAGuard guard(student.device());
+  Tensor row_loss = torch::empty({rows}, student.options().dtype(at::kFloat));
+  Tensor grad;
+  if (write_grad) grad = reuse_student ? student : torch::empty_like(student);
+  ok(fmb_kl_fwd_bwd(student.data_ptr(), teacher.data_ptr(), row_loss.data_ptr<float>(),
+                    write_grad ? grad.data_ptr() : nullptr, rows, static_cast<int>(V), static_cast<float>(grad_scale),
+                    dt(student), write_grad, cur_stream()), "kl_fwd_bwd");
+  return {row_loss, grad};
+}
+
+void sum_f32(const Tensor& x, Tensor& out, double scale, bool accumulate) {
+  cuda_contig(x, "x");
+  TORCH_CHECK(x.scalar_type() == at::kFloat && out.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(x.device());
+  ok(fmb_sum_f32(x.data_ptr<float>(), out.data_ptr<float>(), x.numel(), static_cast<float>(scale), accumulate,
+                 cur_stream()), "sum_f32");
+}
+
+void adamw_flat(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const c10::optional<Tensor>& shadow, double lr,
+                double beta1, double beta2, double eps, double wd, double bc1, double bc2,
+                const c10::optional<Tensor>& ctl) {
+  cuda_contig(p, "p"); cuda_contig(g, "g"); cuda_contig(m, "m"); cuda_contig(v, "v");
+  TORCH_CHECK(p.scalar_type() == at::kFloat && g.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat &&
+              v.scalar_type() == at::kFloat, "adamw_flat: fp32 state required");
+  TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel());
+  void* sh = nullptr;
+  if (shadow.has_value() && shadow->defined()) {
+    TORCH_CHECK(shadow->scalar_type() == at::kBFloat16 && shadow->numel() == p.numel() && shadow->is_contiguous());
+    sh = shadow->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(p.device());
+  ok(fmb_adamw_flat(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), sh, p.numel(),
+                    static_cast<float>(lr), static_cast<float>(beta1), static_cast<float>(beta2),
+                    static_cast<float>(eps), static_cast<float>(wd), static_cast<float>(bc1), static_cast<float>(bc2),
+                    static_cast<const float*>(cptr(ctl)), cur_stream()), "adamw_flat");
+}
+
+void sqnorm(const Tensor& x, Tensor& scratch, Tensor& out, bool accumulate) {
+  cuda_contig(x, "x");
+  TORCH_CHECK(x.scalar_type() == at::kFloat && scratch.numel() >= 1024 && scratch.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(x.device());
+  ok(fmb_sqnorm_f32_scratch(x.data_ptr<float>(), scratch.data_ptr<float>(), out.data_ptr<float>(), x.numel(),
+                            accumulate, cur_stream()), "sqnorm");
+}
+
+void scale_cast(const Tensor& src, Tensor& dst, double scale) {
+  cuda_contig(src, "src"); cuda_contig(dst, "dst");
+  TORCH_CHECK(src.numel() == dst.numel());
+  c10::cuda::CUDAGuard guard(src.device());
+  ok(fmb_scale_cast(src.data_ptr(), dst.data_ptr(), src.numel(), static_cast<float>(scale), dt(src), dt(dst),
+                    cur_stream()), "scale_cast");
+}
+
+void ns_axpby(const Tensor& x, const Tensor& y, Tensor& out, double a, double b) {
+  cuda_contig(x, "x"); cuda_contig(y, "y"); cuda_contig(out, "out");
+  c10::cuda::CUDAGuard guard(x.device());
+  ok(fmb_ns_axpby(x.data_ptr(), y.data_ptr(), out.data_ptr(), x.numel(), static_cast<float>(a), static_cast<float>(b),
+                  dt(x), cur_stream()), "ns_axpby");
+}
+
+// ---- router / MoE
+std::vector<Tensor> router_fwd(const Tensor& logits, int64_t k) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
+  const int64_t rows = logits.size(0), E = logits.size(1);
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto f32 = logits.options().dtype(at::kFloat);
+  auto i32 = logits.options().dtype(at::kInt);
+  const int nb = fmb_router_blocks(rows);
+  Tensor probs = torch::empty({rows, E}, f32), weights = torch::empty({rows, k}, f32), idx = torch::empty({rows, k}, i32);
+  Tensor lse = torch::empty({rows}, f32), partial = torch::empty({nb, E + 1}, f32), counts = torch::zeros({E}, i32);
+  ok(fmb_router_fwd(logits.data_ptr(), logits.stride(0), dt(logits), probs.data_ptr<float>(), weights.data_ptr<float>(),
+                    idx.data_ptr<int>(), lse.data_ptr<float>(), partial.data_ptr<float>(), counts.data_ptr<int>(), rows,
+                    static_cast<int>(E), static_cast<int>(k), nb, cur_stream()), "router_fwd");
+  return {probs, weights, idx, lse, partial, counts};
+}
+
+Tensor router_bwd(const Tensor& probs, const Tensor& idx, const Tensor& weights, const Tensor& lse,
+                  const c10::optional<Tensor>& dweights, const c10::optional<Tensor>& aux_grad,
+                  const c10::optional<Tensor>& zc, at::ScalarType out_dtype) {
+  const int64_t rows = probs.size(0), E = probs.size(1), k = idx.size(1);
+  c10::cuda::CUDAGuard guard(probs.device());
+  Tensor dl = torch::empty({rows, E}, probs.options().dtype(out_dtype));
+  if (dweights.has_value() && dweights->defined()) cuda_contig(*dweights, "dweights");
+  ok(fmb_router_bwd(probs.data_ptr<float>(), idx.data_ptr<int>(), weights.data_ptr<float>(), lse.data_ptr<float>(),
+                    static_cast<const float*>(cptr(dweights)), static_cast<const float*>(cptr(aux_grad)),
+                    static_cast<const float*>(cptr(zc)), dl.data_ptr(), E, dt(dl), rows, static_cast<int>(E),
+                    static_cast<int>(k), cur_stream()), "router_bwd");
+  return dl;
+}
+
+// returns (slot_of_entry [N*k], token_of_slot [max_slots], region [E,3], meta [1])
+std::vector<Tensor> moe_plan(const Tensor& idx, int64_t E, int64_t align, int64_t cap, int64_t mode, int64_t max_slots) {
+  cuda_contig(idx, "idx");
+  TORCH_CHECK(idx.scalar_type() == at::kInt && idx.dim() == 2);
+  const int64_t entries = idx.numel(), k = idx.size(1);
+  c10::cuda::CUDAGuard guard(idx.device());
+  auto i32 = idx.options();
+  const int64_t nchunks = (entries + 1023) / 1024;
+  Tensor chunk = torch::empty({nchunks, E}, i32), region = torch::empty({E, 3}, i32), meta = torch::empty({1}, i32);
+  Tensor slot_of = torch::empty({entries}, i32), token_of = torch::full({max_slots}, -1, i32);
+  ok(fmb_moe_plan(idx.data_ptr<int>(), chunk.data_ptr<int>(), region.data_ptr<int>(), meta.data_ptr<int>(),
+                  slot_of.data_ptr<int>(), token_of.data_ptr<int>(), entries, static_cast<int>(E), static_cast<int>(k),
+                  static_cast<int>(align), static_cast<int>(cap), static_cast<int>(mode), cur_stream()), "moe_plan");
+  return {slot_of, token_of, region, meta};
+}
+
+Tensor moe_gather(const Tensor& x, const Tensor& token_of_slot) {
+  cuda_contig(x, "x"); cuda_contig(token_of_slot, "token_of_slot");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty({token_of_slot.numel(), x.size(1)}, x.options());
+  ok(fmb_moe_gather(x.data_ptr(), token_of_slot.data_ptr<int>(), out.data_ptr(), token_of_slot.numel(),
+                    static_cast<int>(x.size(1)), cur_stream()), "moe_gather");
+  return out;
+}
+
+Tensor moe_combine(const Tensor& ys, const Tensor& slot_of_entry, const c10::optional<Tensor>& w, int64_t tokens, int64_t k) {
+  cuda_contig(ys, "ys"); cuda_contig(slot_of_entry, "slot_of_entry");
+  TORCH_CHECK(ys.scalar_type() == at::kBFloat16 && ys.dim() == 2);
+  c10::cuda::CUDAGuard guard(ys.device());
+  Tensor out = torch::empty({tokens, ys.size(1)}, ys.options());
+  ok(fmb_moe_combine(ys.data_ptr(), slot_of_entry.data_ptr<int>(), static_cast<const float*>(cptr(w)), out.data_ptr(),
+                     tokens, static_cast<int>(k), static_cast<int>(ys.size(1)), cur_stream()), "moe_combine");
+  return out;
+}
+
+std::vector<Tensor> moe_combine_bwd(const Tensor& dout, const Tensor& ys, const Tensor& slot_of_entry, const Tensor& w,
+                                    int64_t k) {
+  cuda_contig(dout, "dout"); cuda_contig(ys, "ys");
+  c10::cuda::CUDAGuard guard(ys.device());
+  Tensor dys = torch::zeros_like(ys);
+  Tensor dw = torch::empty({slot_of_entry.numel()}, ys.options().dtype(at::kFloat));
+  ok(fmb_moe_combine_bwd(dout.data_ptr(), ys.data_ptr(), slot_of_entry.data_ptr<int>(), w.data_ptr<float>(),
+                         dys.data_ptr(), dw.data_ptr<float>(), slot_of_entry.numel(), static_cast<int>(k),
+                         static_cast<int>(ys.size(1)), cur_stream()), "moe_combine_bwd");
+  return {dys, dw};
+}
+
+#ifdef FMB_WITH_ATTENTION
+// q [B,T,Hq,hd], k/v [B,T,Hkv,hd] (rows may be views into one fused qkv buffer): returns (o, lse)
+std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale, bool causal,
+                             const c10::optional<Tensor>& status) {
+  TORCH_CHECK(q.is_cuda() && q.dim() == 4 && k.dim() == 4 && v.dim() == 4 && q.scalar_type() == at::kBFloat16);
+  const int64_t B = q.size(0), T = q.size(1), Hq = q.size(2), hd = q.size(3), Hkv = k.size(2);
+  TORCH_CHECK(q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1 && q.stride(2) == hd && k.stride(2) == hd &&
+              v.stride(2) == hd, "attention: heads must be packed inside a token row");
+  TORCH_CHECK(q.stride(0) == T * q.stride(1) && k.stride(0) == T * k.stride(1) && v.stride(0) == T * v.stride(1) &&
+              k.stride(1) == v.stride(1), "attention: batch must be contiguous over tokens");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor o = torch::empty({B, T, Hq, hd}, q.options());
+  Tensor lse = torch::empty({B, Hq, T}, q.options().dtype(at::kFloat));
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  ok(fmb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), static_cast<int>(B),
+                  static_cast<int>(T), static_cast<int>(Hq), static_cast<int>(Hkv), static_cast<int>(hd), q.stride(1),
+                  k.stride(1), o.stride(1), static_cast<float>(scale), causal, st, cur_stream()), "attn_fwd");
+  return {o, lse};
+}
+
+// writes dq/dk/dv into the given (possibly strided) views
+void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o, const Tensor& lse,
+              Tensor& dq, Tensor& dk, Tensor& dv, double scale, bool causal, const c10::optional<Tensor>& status) {
+  const int64_t B = q.size(0), T = q.size(1), Hq = q.size(2), hd = q.size(3), Hkv = k.size(2);
+  TORCH_CHECK(d_o.is_contiguous() && o.is_contiguous(), "attention backward: o and d_o must be contiguous");
+  TORCH_CHECK(dk.stride(1) == dv.stride(1), "attention backward: dk and dv must share a token pitch");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor delta = torch::empty({B, Hq, T}, q.options().dtype(at::kFloat));
+  Tensor dq_acc = torch::zeros({B, T, Hq, hd}, q.options().dtype(at::kFloat));
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  ok(fmb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr<float>(),
+                  dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr<float>(), dq_acc.data_ptr<float>(),
+                  static_cast<int>(B), static_cast<int>(T), static_cast<int>(Hq), static_cast<int>(Hkv),
+                  static_cast<int>(hd), q.stride(1), k.stride(1), o.stride(1), dq.stride(1), dk.stride(1),
+                  static_cast<float>(scale), causal, st, cur_stream()), "attn_bwd");
+}
+#endif
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "forgeminds_b200 native kernels (sm_100a)";
+  m.def("gemm", &gemm);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("rope", &rope);
+  m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
+  m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
+  m.def("softmax_fwd", &softmax_fwd);
+  m.def("softmax_bwd", &softmax_bwd);
+  m.def("topk", &topk);
+  m.def("ce_fwd_bwd", &ce_fwd_bwd);
+  m.def("kl_fwd_bwd", &kl_fwd_bwd);
+  m.def("sum_f32", &sum_f32);
+  m.def("adamw_flat", &adamw_flat);
+  m.def("sqnorm", &sqnorm);
+  m.def("scale_cast", &scale_cast);
+  m.def("ns_axpby", &ns_axpby);
+  m.def("router_fwd", &router_fwd);
+  m.def("router_bwd", &router_bwd);
+  m.def("moe_plan", &moe_plan);
+  m.def("moe_gather", &moe_gather);
+  m.def("moe_combine", &moe_combine);
+  m.def("moe_combine_bwd", &moe_combine_bwd);
+#ifdef FMB_WITH_ATTENTION
+  m.def("attn_fwd", &attn_fwd);
+  m.def("attn_bwd", &attn_bwd);
+#endif
+}

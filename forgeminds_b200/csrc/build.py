@@ -1,0 +1,120 @@
+"""In-tree build of the native library for sm_100a.
+
+``python -m forgeminds_b200.csrc.build`` compiles every ``.cu`` file in this directory with nvcc
+(``-gencode arch=compute_100a,code=sm_100a``; cross-compiles without a GPU), the pybind11 binding
+with g++, and links ``forgeminds_b200/_C.so``. Objects are cached by source hash under
+``build/`` next to the sources, so a second call only rebuilds what changed.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+PKG = HERE.parent
+OBJ = HERE / "build"
+TARGET = PKG / "_C.so"
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--use_fast_math",
+              "-DFMB_BUILD"]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wno-attributes"]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _cuda_home() -> Path:
+    return Path(_nvcc()).resolve().parent.parent
+
+
+def _digest(paths, extra="") -> str:
+    h = hashlib.sha256(extra.encode())
+    for p in sorted(paths):
+        h.update(Path(p).read_bytes())
+    return h.hexdigest()[:16]
+
+
+def _run(cmd, log_path=None):
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if log_path is not None:
+        Path(log_path).write_text(" ".join(map(str, cmd)) + "\n" + proc.stdout)
+    if proc.returncode != 0:
+        raise RuntimeError(f"command failed ({proc.returncode}): {' '.join(map(str, cmd))}\n{proc.stdout[-6000:]}")
+    return proc.stdout
+
+
+def build(verbose: bool = False, force: bool = False) -> Path:
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    OBJ.mkdir(exist_ok=True)
+    headers = sorted(HERE.glob("*.cuh")) + sorted(HERE.glob("*.h"))
+    hdr_sig = _digest(headers, " ".join(NVCC_FLAGS) + torch.__version__)
+    cuda_inc = str(_cuda_home() / "include")
+    jobs = []
+    objects = []
+    for src in sorted(HERE.glob("*.cu")):
+        sig = _digest([src], hdr_sig)
+        obj = OBJ / f"{src.stem}.{sig}.o"
+        objects.append(obj)
+        if obj.exists() and not force:
+            continue
+        for stale in OBJ.glob(f"{src.stem}.*.o"):
+            stale.unlink()
+        jobs.append(([_nvcc(), *NVCC_FLAGS, "-I", str(HERE), "-c", str(src), "-o", str(obj)],
+                     OBJ / f"{src.stem}.log"))
+    torch_inc = [f"-I{p}" for p in ce.include_paths()]
+    py_inc = f"-I{sysconfig.get_paths()['include']}"
+    for src in sorted(HERE.glob("*.cpp")):
+        sig = _digest([src], hdr_sig)
+        obj = OBJ / f"{src.stem}.{sig}.o"
+        objects.append(obj)
+        if obj.exists() and not force:
+            continue
+        for stale in OBJ.glob(f"{src.stem}.*.o"):
+            stale.unlink()
+        abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+        jobs.append((["g++", *CXX_FLAGS, f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-DTORCH_EXTENSION_NAME=_C",
+                      "-DTORCH_API_INCLUDE_EXTENSION_H", f"-I{HERE}", f"-I{cuda_inc}", py_inc, *torch_inc,
+                      "-c", str(src), "-o", str(obj)], OBJ / f"{src.stem}.log"))
+    if jobs:
+        with cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
+            for out in pool.map(lambda j: _run(*j), jobs):
+                if verbose:
+                    print(out)
+    stamp = OBJ / "link.sig"
+    link_sig = _digest(objects)
+    if force or jobs or not TARGET.exists() or not stamp.exists() or stamp.read_text() != link_sig:
+        lib_dirs = ce.library_paths()
+        cuda_lib = str(_cuda_home() / "lib64")
+        cmd = ["g++", "-shared", "-o", str(TARGET), *map(str, objects)]
+        for d in [*lib_dirs, cuda_lib]:
+            cmd += [f"-L{d}", f"-Wl,-rpath,{d}"]
+        cmd += ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python", "-lcudart"]
+        _run(cmd, OBJ / "link.log")
+        stamp.write_text(link_sig)
+    return TARGET
+
+
+def ptxas_report() -> str:
+    """Registers / spills / shared memory per kernel, as printed by ``-Xptxas -v`` at build time."""
+    out = []
+    for log in sorted(OBJ.glob("*.log")):
+        out.append(f"== {log.name}\n{log.read_text()}")
+    return "\n".join(out)
+
+
+if __name__ == "__main__":
+    path = build(verbose="-v" in sys.argv, force="--force" in sys.argv)
+    print(path)

@@ -1,0 +1,743 @@
+// Bandwidth-bound kernels: RMSNorm (+residual), SwiGLU, rotary embedding, per-head QK norm + RoPE,
+// softmax and top-k. All of them move 16-byte vectors, accumulate in fp32 and round once at the
+// store. Row reductions use one warp per row up to 2048 columns and one 256-thread block per row
+// above that, so no row ever makes a second trip to HBM.
+#include "ptx_sm100.cuh"
+#include "tensormap.h"
+#include "fmb_api.h"
+#include <math_constants.h>
+
+namespace fmb {
+
+// ------------------------------------------------------------------ 8-wide vector access
+template <typename T> struct V8;
+template <> struct V8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&f)[8]) {
+    uint4 u;
+    u.x = pack_bf16(f[0], f[1]); u.y = pack_bf16(f[2], f[3]); u.z = pack_bf16(f[4], f[5]); u.w = pack_bf16(f[6], f[7]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <> struct V8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&f)[8]) {
+    float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&f)[8]) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over the TPR threads that share a row. TPR = 32: a warp; TPR = 256: the whole block.
+template <int TPR>
+__device__ __forceinline__ float row_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  if constexpr (TPR > 32) {
+    const int w = threadIdx.x >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[w] = v;
+    __syncthreads();
+    v = 0.f;
+#pragma unroll
+    for (int i = 0; i < TPR / 32; ++i) v += scratch[i];
+  }
+  return v;
+}
+
+constexpr int ROW_THREADS = 256;
+
+// ------------------------------------------------------------------ RMSNorm forward
+template <typename T, typename WT, int TPR, int VPL, bool ADD>
+__global__ void __launch_bounds__(ROW_THREADS)
+rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ delta, const WT* __restrict__ w,
+                   T* __restrict__ xn, T* __restrict__ y, float* __restrict__ rstd, long long rows, int d, float eps) {
+  __shared__ float scratch[ROW_THREADS / 32];
+  constexpr int RPB = ROW_THREADS / TPR;
+  const int sub = threadIdx.x / TPR, t = threadIdx.x % TPR;
+  const long long row = static_cast<long long>(blockIdx.x) * RPB + sub;
+  const bool live = row < rows;
+  const int nvec = d >> 3;
+  float v[VPL][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int vi = i * TPR + t;
+    if (live && vi < nvec) {
+      V8<T>::load(x + row * d + vi * 8, v[i]);
+      if constexpr (ADD) {
+        float dl[8];
+        V8<T>::load(delta + row * d + vi * 8, dl);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] += dl[j];
+        // the residual stream is stored in T, and the norm is taken over the stored values
+        V8<T>::store(xn + row * d + vi * 8, v[i]);
+        if constexpr (sizeof(T) == 2) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16(v[i][j]));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+    }
+  }
+  ss = row_sum<TPR>(ss, scratch);
+  const float r = rsqrtf(ss / static_cast<float>(d) + eps);
+  if (live && t == 0 && rstd != nullptr) rstd[row] = r;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int vi = i * TPR + t;
+    if (live && vi < nvec) {
+      float wv[8], o[8];
+      V8<WT>::load(w + vi * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * r * wv[j];
+      V8<T>::store(y + row * d + vi * 8, o);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm backward
+// dx = r * (dy*w) - x * r^3 / d * sum(dy*w*x) (+ dres);   dw += dy * x * r, reduced over rows in
+// two deterministic stages (per-block partial rows, then a column sum).
+template <typename T, typename WT, int TPR, int VPL>
+__global__ void __launch_bounds__(ROW_THREADS)
+rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const WT* __restrict__ w,
+                   const float* __restrict__ rstd, const T* __restrict__ dres, T* __restrict__ dx,
+                   float* __restrict__ dw_partial, long long rows, int d) {
+  __shared__ float scratch[ROW_THREADS / 32];
+  extern __shared__ float dw_smem[];           // d floats, only used when TPR == 32
+  constexpr int RPB = ROW_THREADS / TPR;
+  const int sub = threadIdx.x / TPR, t = threadIdx.x % TPR;
+  const int nvec = d >> 3;
+  float wv[VPL][8], dwacc[VPL][8];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int vi = i * TPR + t;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dwacc[i][j] = 0.f; wv[i][j] = 0.f; }
+    if (vi < nvec) V8<WT>::load(w + vi * 8, wv[i]);
+  }
+  for (long long base = static_cast<long long>(blockIdx.x) * RPB; base < rows;
+       base += static_cast<long long>(gridDim.x) * RPB) {
+    const long long row = base + sub;
+    const bool live = row < rows;
+    const float r = live ? rstd[row] : 0.f;
+    float g[VPL][8], xv[VPL][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int vi = i * TPR + t;
+      if (live && vi < nvec) {
+        V8<T>::load(dy + row * d + vi * 8, g[i]);
+        V8<T>::load(x + row * d + vi * 8, xv[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          dwacc[i][j] += g[i][j] * xv[i][j] * r;
+          g[i][j] *= wv[i][j];
+          dot += g[i][j] * xv[i][j];
+        }
+      }
+    }
+    dot = row_sum<TPR>(dot, scratch);
+    const float c = dot * r * r * r / static_cast<float>(d);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int vi = i * TPR + t;
+      if (live && vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = g[i][j] * r - xv[i][j] * c;
+        if (dres != nullptr) {
+          float rs[8];
+          V8<T>::load(dres + row * d + vi * 8, rs);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += rs[j];
+        }
+        V8<T>::store(dx + row * d + vi * 8, o);
+      }
+    }
+  }
+  if (dw_partial == nullptr) return;
+  if constexpr (TPR == 32) {
+    // the 8 warps of the block hold partial sums of the same columns: fold them in warp order
+    for (int turn = 0; turn < RPB; ++turn) {
+      if (sub == turn) {
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+          const int vi = i * TPR + t;
+          if (vi < nvec) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float prev = turn == 0 ? 0.f : dw_smem[vi * 8 + j];
+              dw_smem[vi * 8 + j] = prev + dwacc[i][j];
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+    for (int c = threadIdx.x; c < d; c += ROW_THREADS) dw_partial[static_cast<long long>(blockIdx.x) * d + c] = dw_smem[c];
+  } else {
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int vi = i * TPR + t;
+      if (vi < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dw_partial[static_cast<long long>(blockIdx.x) * d + vi * 8 + j] = dwacc[i][j];
+      }
+    }
+  }
+}
+
+__global__ void colsum_kernel(const float* __restrict__ part, float* __restrict__ out, int nrows, int d, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  float s = 0.f;
+  for (int r = 0; r < nrows; ++r) s += part[static_cast<long long>(r) * d + c];
+  out[c] = accumulate ? out[c] + s : s;
+}
+
+// ------------------------------------------------------------------ SwiGLU
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out,
+                                  long long rows, int h, long long ld_in) {
+  const int hv = h >> 3;
+  const long long total = rows * hv;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / hv;
+    const int c = static_cast<int>(i % hv) * 8;
+    float g[8], u[8], o[8];
+    V8<T>::load(gate + r * ld_in + c, g);
+    V8<T>::load(up + r * ld_in + c, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    V8<T>::store(out + r * h + c, o);
+  }
+}
+
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ gate, const T* __restrict__ up, const T* __restrict__ dy,
+                                  T* __restrict__ dgate, T* __restrict__ dup, long long rows, int h, long long ld_in) {
+  const int hv = h >> 3;
+  const long long total = rows * hv;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / hv;
+    const int c = static_cast<int>(i % hv) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    V8<T>::load(gate + r * ld_in + c, g);
+    V8<T>::load(up + r * ld_in + c, u);
+    V8<T>::load(dy + r * h + c, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = 1.f / (1.f + __expf(-g[j]));
+      du[j] = d[j] * g[j] * s;
+      dg[j] = d[j] * u[j] * s * (1.f + g[j] * (1.f - s));
+    }
+    V8<T>::store(dgate + r * ld_in + c, dg);
+    V8<T>::store(dup + r * ld_in + c, du);
+  }
+}
+
+// ------------------------------------------------------------------ RoPE (half-split)
+// Rotates the first n_rot heads of every row; the remaining heads are copied when dst != src.
+template <typename T>
+__global__ void rope_kernel(const T* __restrict__ src, T* __restrict__ dst, const float* __restrict__ cs,
+                            const float* __restrict__ sn, long long rows, int T_len, int n_rot, int heads_total, int hd,
+                            float sign) {
+  const int half = hd >> 1;
+  const int hv = half >> 3;
+  const bool inplace = src == dst;
+  const int heads = inplace ? n_rot : heads_total;
+  const long long total = rows * heads * hv;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % hv) * 8;
+    const long long rh = i / hv;
+    const int head = static_cast<int>(rh % heads);
+    const long long row = rh / heads;
+    const long long off = (row * heads_total + head) * hd + c;
+    float a[8], b[8], oa[8], ob[8];
+    V8<T>::load(src + off, a);
+    V8<T>::load(src + off + half, b);
+    if (head < n_rot) {
+      const int pos = static_cast<int>(row % T_len);
+      float co[8], si[8];
+      V8<float>::load(cs + static_cast<long long>(pos) * half + c, co);
+      V8<float>::load(sn + static_cast<long long>(pos) * half + c, si);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float s = si[j] * sign;
+        oa[j] = a[j] * co[j] - b[j] * s;
+        ob[j] = a[j] * s + b[j] * co[j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { oa[j] = a[j]; ob[j] = b[j]; }
+    }
+    V8<T>::store(dst + off, oa);
+    V8<T>::store(dst + off + half, ob);
+  }
+}
+
+// ------------------------------------------------------------------ per-head RMSNorm + RoPE
+// Eight lanes per (row, head): lane l holds elements [8l, 8l+8) of each half (hd <= 128).
+template <typename T, typename WT>
+__global__ void qknorm_rope_fwd_kernel(const T* __restrict__ x, const WT* __restrict__ w, const float* __restrict__ cs,
+                                       const float* __restrict__ sn, T* __restrict__ y, float* __restrict__ rstd,
+                                       long long n_heads_rows, int T_len, int H, int hd, float eps) {
+  const int half = hd >> 1;
+  const int l = threadIdx.x & 7;
+  const long long item = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
+  const bool live = item < n_heads_rows;
+  const bool has = live && (l * 8 < half);
+  float a[8] = {0}, b[8] = {0};
+  const long long off = item * hd + l * 8;
+  if (has) { V8<T>::load(x + off, a); V8<T>::load(x + off + half, b); }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ss += a[j] * a[j] + b[j] * b[j];
+  ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+  ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+  const float r = rsqrtf(ss / static_cast<float>(hd) + eps);
+  if (live && l == 0 && rstd != nullptr) rstd[item] = r;
+  if (!has) return;
+  const int pos = static_cast<int>((item / H) % T_len);
+  float wa[8], wb[8], co[8], si[8], oa[8], ob[8];
+  V8<WT>::load(w + l * 8, wa);
+  V8<WT>::load(w + half + l * 8, wb);
+  V8<float>::load(cs + static_cast<long long>(pos) * half + l * 8, co);
+  V8<float>::load(sn + static_cast<long long>(pos) * half + l * 8, si);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float y1 = a[j] * r * wa[j], y2 = b[j] * r * wb[j];
+    oa[j] = y1 * co[j] - y2 * si[j];
+    ob[j] = y1 * si[j] + y2 * co[j];
+  }
+  V8<T>::store(y + off, oa);
+  V8<T>::store(y + off + half, ob);
+}
+
+template <typename T, typename WT>
+__global__ void qknorm_rope_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const WT* __restrict__ w,
+                                       const float* __restrict__ cs, const float* __restrict__ sn,
+                                       const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_partial,
+                                       long long n_heads_rows, int T_len, int H, int hd) {
+  const int half = hd >> 1;
+  const int l = threadIdx.x & 7;
+  const bool col_ok = l * 8 < half;
+  float wa[8] = {0}, wb[8] = {0}, dwa[8] = {0}, dwb[8] = {0};
+  if (col_ok) { V8<WT>::load(w + l * 8, wa); V8<WT>::load(w + half + l * 8, wb); }
+  const long long groups = (static_cast<long long>(gridDim.x) * blockDim.x) >> 3;
+  for (long long item = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
+       item < ((n_heads_rows + groups - 1) / groups) * groups; item += groups) {
+    const bool live = item < n_heads_rows;
+    const bool has = live && col_ok;
+    float a[8] = {0}, b[8] = {0}, ga[8] = {0}, gb[8] = {0};
+    const long long off = item * hd + l * 8;
+    float r = 0.f;
+    if (has) {
+      float g1[8], g2[8], co[8], si[8];
+      r = rstd[item];
+      const int pos = static_cast<int>((item / H) % T_len);
+      V8<T>::load(x + off, a); V8<T>::load(x + off + half, b);
+      V8<T>::load(dy + off, g1); V8<T>::load(dy + off + half, g2);
+      V8<float>::load(cs + static_cast<long long>(pos) * half + l * 8, co);
+      V8<float>::load(sn + static_cast<long long>(pos) * half + l * 8, si);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {   // undo the rotation: gradient w.r.t. the normalised values
+        ga[j] = g1[j] * co[j] + g2[j] * si[j];
+        gb[j] = -g1[j] * si[j] + g2[j] * co[j];
+      }
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      dwa[j] += ga[j] * a[j] * r; dwb[j] += gb[j] * b[j] * r;
+      ga[j] *= wa[j]; gb[j] *= wb[j];
+      dot += ga[j] * a[j] + gb[j] * b[j];
+    }
+    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+    dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+    if (has) {
+      const float c = dot * r * r * r / static_cast<float>(hd);
+      float oa[8], ob[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { oa[j] = ga[j] * r - a[j] * c; ob[j] = gb[j] * r - b[j] * c; }
+      V8<T>::store(dx + off, oa);
+      V8<T>::store(dx + off + half, ob);
+    }
+  }
+  // fold the lanes that share a column (same l) inside the block, in a fixed order
+  __shared__ float acc[ROW_THREADS / 8][16];
+  const int grp = threadIdx.x >> 3;
+  float* mine = nullptr;
+  for (int part = 0; part < 8; ++part) {       // 8 lanes x 16 values per group, staged through smem
+    __syncthreads();
+    if (l == part) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { acc[grp][j] = dwa[j]; acc[grp][8 + j] = dwb[j]; }
+    }
+    __syncthreads();
+    if (threadIdx.x < 16 && part * 8 < half) {
+      float s = 0.f;
+      for (int g2 = 0; g2 < ROW_THREADS / 8; ++g2) s += acc[g2][threadIdx.x];
+      const int col = threadIdx.x < 8 ? part * 8 + threadIdx.x : half + part * 8 + (threadIdx.x - 8);
+      dw_partial[static_cast<long long>(blockIdx.x) * hd + col] = s;
+    }
+  }
+  (void)mine;
+}
+
+// ------------------------------------------------------------------ softmax
+template <typename T>
+__global__ void softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, long long rows, int n) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const T* xr = x + row * n;
+  float m = -CUDART_INF_F;
+  bool has_nan = false;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = static_cast<float>(xr[i]);
+    has_nan |= (v != v);
+    m = fmaxf(m, v);
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = red[0];
+  for (int i = 1; i < (blockDim.x >> 5); ++i) m = fmaxf(m, red[i]);
+  __syncthreads();
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += __expf(static_cast<float>(xr[i]) - m);
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  s = 0.f;
+  for (int i = 0; i < (blockDim.x >> 5); ++i) s += red[i];
+  const int any_nan = __syncthreads_or(has_nan ? 1 : 0);
+  const float inv = 1.f / s;     // all -inf row: exp(nan) -> nan, like torch
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = __expf(static_cast<float>(xr[i]) - m) * inv;
+    if (any_nan) v = CUDART_NAN_F;
+    y[row * n + i] = static_cast<T>(v);
+  }
+}
+
+template <typename T>
+__global__ void softmax_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx,
+                                   long long rows, int n) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    s += static_cast<float>(y[row * n + i]) * static_cast<float>(dy[row * n + i]);
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  s = 0.f;
+  for (int i = 0; i < (blockDim.x >> 5); ++i) s += red[i];
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float yv = static_cast<float>(y[row * n + i]);
+    dx[row * n + i] = static_cast<T>((static_cast<float>(dy[row * n + i]) - s) * yv);
+  }
+}
+
+// ------------------------------------------------------------------ top-k
+// Exact selection in k rounds; order: value descending (NaN counts as largest), then index
+// ascending, which also fixes which of several equal values at the boundary is kept.
+__device__ __forceinline__ bool key_before(float va, int ia, float vb, int ib) {
+  const bool na = va != va, nb = vb != vb;
+  if (na != nb) return na;
+  if (!na && va != vb) return va > vb;
+  return ia < ib;
+}
+
+template <typename T>
+__global__ void topk_kernel(const T* __restrict__ x, T* __restrict__ values, long long* __restrict__ indices,
+                            long long rows, int n, int k) {
+  __shared__ float s_val[32];
+  __shared__ int s_idx[32];
+  __shared__ float last_v;
+  __shared__ int last_i;
+  const long long row = blockIdx.x;
+  const T* xr = x + row * n;
+  for (int round = 0; round < k; ++round) {
+    float bv = 0.f;
+    int bi = -1;
+    const float lv = last_v;
+    const int li = last_i;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const float v = static_cast<float>(xr[i]);
+      if (round > 0 && !key_before(lv, li, v, i)) continue;      // already taken (or is the last pick)
+      if (bi < 0 || key_before(v, i, bv, bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi >= 0 && (bi < 0 || key_before(ov, oi, bv, bi))) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = bv; s_idx[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int wq = 1; wq < (blockDim.x >> 5); ++wq) {
+        if (s_idx[wq] >= 0 && (bi < 0 || key_before(s_val[wq], s_idx[wq], bv, bi))) { bv = s_val[wq]; bi = s_idx[wq]; }
+      }
+      last_v = bv;
+      last_i = bi;
+      values[row * k + round] = xr[bi];
+      indices[row * k + round] = bi;
+    }
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------ dispatch helpers
+template <typename F>
+static int by_dtype(int dtype, F&& f) {
+  if (dtype == FMB_BF16) return f(static_cast<__nv_bfloat16*>(nullptr));
+  if (dtype == FMB_F32) return f(static_cast<float*>(nullptr));
+  return -1;
+}
+
+static int grid_for(long long work_items, int threads) {
+  long long b = (work_items + threads - 1) / threads;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+template <typename T, typename WT, bool ADD>
+static int launch_rms_fwd(const void* x, const void* delta, const void* w, void* xn, void* y, float* rstd,
+                          long long rows, int d, float eps, cudaStream_t st) {
+  const int nvec = d / 8;
+#define FMB_RMS_FWD(TPR, VPL)                                                                         \
+  {                                                                                                   \
+    constexpr int RPB = ROW_THREADS / TPR;                                                            \
+    const unsigned blocks = static_cast<unsigned>((rows + RPB - 1) / RPB);                            \
+    rmsnorm_fwd_kernel<T, WT, TPR, VPL, ADD><<<blocks, ROW_THREADS, 0, st>>>(                         \
+        static_cast<const T*>(x), static_cast<const T*>(delta), static_cast<const WT*>(w),            \
+        static_cast<T*>(xn), static_cast<T*>(y), rstd, rows, d, eps);                                 \
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;                                                \
+  }
+  if (nvec <= 32) FMB_RMS_FWD(32, 1)
+  if (nvec <= 64) FMB_RMS_FWD(32, 2)
+  if (nvec <= 128) FMB_RMS_FWD(32, 4)
+  if (nvec <= 256) FMB_RMS_FWD(32, 8)
+  if (nvec <= 512) FMB_RMS_FWD(256, 2)
+  if (nvec <= 1024) FMB_RMS_FWD(256, 4)
+  if (nvec <= 2048) FMB_RMS_FWD(256, 8)
+#undef FMB_RMS_FWD
+  return -2;
+}
+
+template <typename T, typename WT>
+static int launch_rms_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                          float* dwp, long long rows, int d, int nblocks, cudaStream_t st) {
+  const int nvec = d / 8;
+#define FMB_RMS_BWD(TPR, VPL)                                                                         \
+  {                                                                                                   \
+    const size_t sm = TPR == 32 ? sizeof(float) * d : 0;                                              \
+    rmsnorm_bwd_kernel<T, WT, TPR, VPL><<<nblocks, ROW_THREADS, sm, st>>>(                            \
+        static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const WT*>(w), rstd,         \
+        static_cast<const T*>(dres), static_cast<T*>(dx), dwp, rows, d);                              \
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;                                                \
+  }
+  if (nvec <= 32) FMB_RMS_BWD(32, 1)
+  if (nvec <= 64) FMB_RMS_BWD(32, 2)
+  if (nvec <= 128) FMB_RMS_BWD(32, 4)
+  if (nvec <= 256) FMB_RMS_BWD(32, 8)
+  if (nvec <= 512) FMB_RMS_BWD(256, 2)
+  if (nvec <= 1024) FMB_RMS_BWD(256, 4)
+  if (nvec <= 2048) FMB_RMS_BWD(256, 8)
+#undef FMB_RMS_BWD
+  return -2;
+}
+
+}  // namespace fmb
+
+using namespace fmb;
+
+extern "C" int fmb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int d, float eps,
+                               int dtype, int w_dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (d % 8) return -2;
+  return by_dtype(dtype, [&](auto* tp) {
+    using T = std::remove_pointer_t<decltype(tp)>;
+    if (w_dtype == dtype) return launch_rms_fwd<T, T, false>(x, nullptr, w, nullptr, y, rstd, rows, d, eps, stream);
+    if (w_dtype == FMB_F32) return launch_rms_fwd<T, float, false>(x, nullptr, w, nullptr, y, rstd, rows, d, eps, stream);
+    return -1;
+  });
+}
+
+extern "C" int fmb_add_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* xn, void* y, float* rstd,
+                                   long long rows, int d, float eps, int dtype, int w_dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (d % 8) return -2;
+  return by_dtype(dtype, [&](auto* tp) {
+    using T = std::remove_pointer_t<decltype(tp)>;
+    if (w_dtype == dtype) return launch_rms_fwd<T, T, true>(x, delta, w, xn, y, rstd, rows, d, eps, stream);
+    if (w_dtype == FMB_F32) return launch_rms_fwd<T, float, true>(x, delta, w, xn, y, rstd, rows, d, eps, stream);
+    return -1;
+  });
+}
+
+extern "C" int fmb_rmsnorm_bwd_blocks(long long rows, int d) {
+  const int tpr = (d / 8) <= 256 ? 32 : 256;
+  const int rpb = ROW_THREADS / tpr;
+  long long need = (rows + rpb - 1) / rpb;
+  long long cap = static_cast<long long>(sm_count()) * 2;
+  return static_cast<int>(need < 1 ? 1 : (need > cap ? cap : need));
+}
+
+extern "C" int fmb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                               void* dx, float* dw_partial, float* dw, int dw_accumulate, long long rows, int d,
+                               int dtype, int w_dtype, int nblocks, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (d % 8) return -2;
+  int rc = by_dtype(dtype, [&](auto* tp) {
+    using T = std::remove_pointer_t<decltype(tp)>;
+    if (w_dtype == dtype) return launch_rms_bwd<T, T>(dy, x, w, rstd, dres, dx, dw_partial, rows, d, nblocks, stream);
+    if (w_dtype == FMB_F32) return launch_rms_bwd<T, float>(dy, x, w, rstd, dres, dx, dw_partial, rows, d, nblocks, stream);
+    return -1;
+  });
+  if (rc != 0 || dw_partial == nullptr || dw == nullptr) return rc;
+  colsum_kernel<<<(d + 127) / 128, 128, 0, stream>>>(dw_partial, dw, nblocks, d, dw_accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int fmb_swiglu_fwd(const void* gate, const void* up, void* out, long long rows, int h, long long ld_in,
+                              int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (h % 8 || ld_in % 8) return -2;
+  return by_dtype(dtype, [&](auto* tp) {
+    using T = std::remove_pointer_t<decltype(tp)>;
+    swiglu_fwd_kernel<T><<<grid_for(rows * (h / 8), 256), 256, 0, stream>>>(
+        static_cast<const T*>(gate), static_cast<const T*>(up), static_cast<T*>(out), rows, h, ld_in);
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  });
+}
+
+extern "C" int fmb_swiglu_bwd(const void* gate, const void* up, const void* dy, void* dgate, void* dup, long long rows,
+                              int h, long long ld_in, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (h % 8 || ld_in % 8) return -2;
+  return by_dtype(dtype, [&](auto* tp) {
+    using T = std::remove_pointer_t<decltype(tp)>;
+    swiglu_bwd_kernel<T><<<grid_for(rows * (h / 8), 256), 256, 0, stream>>>(
+        static_cast<const T*>(gate), static_cast<const T*>(up), static_cast<const T*>(dy), static_cast<T*>(dgate),
+        static_cast<T*>(dup), rows, h, ld_in);
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  });
+}
+
+extern "C" int fmb_rope(const void* src, void* dst, const float* cos, const float* sin, long long rows, int T,
+                        int n_rot_heads, int heads_total, int hd, float sign, int dtype, cudaStream_t stream) {
+  if (rows <= 0 || n_rot_heads <= 0) return 0;
+  if (hd % 16) return -2;
+  const int heads = src == dst ? n_rot_heads : heads_total;
+  return by_dtype(dtype, [&](auto* tp) {
+    using Tt = std::remove_pointer_t<decltype(tp)>;
+    rope_kernel<Tt><<<grid_for(rows * heads * (hd / 16), 256), 256, 0, stream>>>(
+        static_cast<const Tt*>(src), static_cast<Tt*>(dst), cos, sin, rows, T, n_rot_heads, heads_total, hd, sign);
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  });
+}
+
+extern "C" int fmb_qk_norm_rope_fwd(const void* x, const void* w, const float* cos, const float* sin, void* y,
+                                    float* rstd, long long rows, int T, int H, int hd, float eps, int dtype,
+                                    int w_dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hd % 16 || hd > 128) return -2;
+  const long long items = rows * H;
+  const unsigned blocks = static_cast<unsigned>((items * 8 + ROW_THREADS - 1) / ROW_THREADS);
+  return by_dtype(dtype, [&](auto* tp) {
+    using Tt = std::remove_pointer_t<decltype(tp)>;
+    if (w_dtype == dtype)
+      qknorm_rope_fwd_kernel<Tt, Tt><<<blocks, ROW_THREADS, 0, stream>>>(
+          static_cast<const Tt*>(x), static_cast<const Tt*>(w), cos, sin, static_cast<Tt*>(y), rstd, items, T, H, hd, eps);
+    else if (w_dtype == FMB_F32)
+      qknorm_rope_fwd_kernel<Tt, float><<<blocks, ROW_THREADS, 0, stream>>>(
+          static_cast<const Tt*>(x), static_cast<const float*>(w), cos, sin, static_cast<Tt*>(y), rstd, items, T, H, hd, eps);
+    else return -1;
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  });
+}
+
+extern "C" int fmb_qk_norm_rope_bwd(const void* dy, const void* x, const void* w, const float* cos, const float* sin,
+                                    const float* rstd, void* dx, float* dw_partial, float* dw, long long rows, int T,
+                                    int H, int hd, int dtype, int w_dtype, int nblocks, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hd % 16 || hd > 128) return -2;
+  const long long items = rows * H;
+  int rc = by_dtype(dtype, [&](auto* tp) {
+    using Tt = std::remove_pointer_t<decltype(tp)>;
+    if (w_dtype == dtype)
+      qknorm_rope_bwd_kernel<Tt, Tt><<<nblocks, ROW_THREADS, 0, stream>>>(
+          static_cast<const Tt*>(dy), static_cast<const Tt*>(x), static_cast<const Tt*>(w), cos, sin, rstd,
+          static_cast<Tt*>(dx), dw_partial, items, T, H, hd);
+    else if (w_dtype == FMB_F32)
+      qknorm_rope_bwd_kernel<Tt, float><<<nblocks, ROW_THREADS, 0, stream>>>(
+          static_cast<const Tt*>(dy), static_cast<const Tt*>(x), static_cast<const float*>(w), cos, sin, rstd,
+          static_cast<Tt*>(dx), dw_partial, items, T, H, hd);
+    else return -1;
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  });
+  if (rc != 0) return rc;
+  colsum_kernel<<<(hd + 127) / 128, 128, 0, stream>>>(dw_partial, dw, nblocks, hd, 0);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int fmb_softmax_fwd(const void* x, void* y, long long rows, int n, int dtype, cudaStream_t stream) {
+  if (rows <= 0 || n <= 0) return 0;
+  const int threads = n >= 1024 ? 256 : (n >= 128 ? 128 : 32);
+  return by_dtype(dtype, [&](auto* tp) {
+    using T = std::remove_pointer_t<decltype(tp)>;
+    softmax_fwd_kernel<T><<<static_cast<unsigned>(rows), threads, 0, stream>>>(static_cast<const T*>(x), static_cast<T*>(y), rows, n);
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  });
+}
+
+extern "C" int fmb_softmax_bwd(const void* y, const void* dy, void* dx, long long rows, int n, int dtype,
+                               cudaStream_t stream) {
+  if (rows <= 0 || n <= 0) return 0;
+  const int threads = n >= 1024 ? 256 : (n >= 128 ? 128 : 32);
+  return by_dtype(dtype, [&](auto* tp) {
+    using T = std::remove_pointer_t<decltype(tp)>;
+    softmax_bwd_kernel<T><<<static_cast<unsigned>(rows), threads, 0, stream>>>(
+        static_cast<const T*>(y), static_cast<const T*>(dy), static_cast<T*>(dx), rows, n);
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  });
+}
+
+extern "C" int fmb_topk(const void* x, void* values, long long* indices, long long rows, int n, int k, int dtype,
+                        cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (k < 1 || k > n) return -2;
+  const int threads = n >= 4096 ? 512 : (n >= 512 ? 256 : 64);
+  return by_dtype(dtype, [&](auto* tp) {
+    using T = std::remove_pointer_t<decltype(tp)>;
+    topk_kernel<T><<<static_cast<unsigned>(rows), threads, 0, stream>>>(static_cast<const T*>(x), static_cast<T*>(values), indices, rows, n, k);
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  });
+}

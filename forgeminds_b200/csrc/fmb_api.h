@@ -1,0 +1,92 @@
+// C entry points of the native library. Every function enqueues work on `stream` and returns 0 on
+// success or a negative code when the arguments cannot be served (the Python layer raises). None
+// of them synchronises. Pointers are device pointers unless stated otherwise. `status` (may be
+// null) is a device int that a kernel sets to a non-zero fmb::ERR_* code when one of its bounded
+// waits ran out.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// dtype codes used across the API
+#define FMB_BF16 0
+#define FMB_F32 1
+
+// ---- GEMM (gemm_sm100.cu)
+int fmb_gemm_bf16(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int a_mn, int b_mn,
+                  long long lda, long long ldb, long long ldd, long long ldc, int d_f32, int c_f32, float alpha,
+                  float beta, const float* alpha_ptr, int allow_split, int* status, int force_bn,
+                  cudaStream_t stream);
+
+// ---- normalisation / elementwise (elementwise.cu)
+int fmb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int d, float eps, int dtype,
+                    int w_dtype, cudaStream_t stream);
+int fmb_add_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* xn, void* y, float* rstd,
+                        long long rows, int d, float eps, int dtype, int w_dtype, cudaStream_t stream);
+// dx = norm backward (+ dres when given); dw_partial is [nblocks, d] fp32 scratch, dw receives its column sum.
+int fmb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                    float* dw_partial, float* dw, int dw_accumulate, long long rows, int d, int dtype, int w_dtype,
+                    int nblocks, cudaStream_t stream);
+int fmb_rmsnorm_bwd_blocks(long long rows, int d);
+int fmb_swiglu_fwd(const void* gate, const void* up, void* out, long long rows, int h, long long ld_in, int dtype,
+                   cudaStream_t stream);
+int fmb_swiglu_bwd(const void* gate, const void* up, const void* dy, void* dgate, void* dup, long long rows, int h,
+                   long long ld_in, int dtype, cudaStream_t stream);
+// Half-split rotary embedding of the first n_rot_heads heads of each row of
+// src[rows, n_heads_total * hd] into dst (dst may be src; otherwise the other heads are copied);
+// position = row % T; sign = +1 forward, -1 backward.
+int fmb_rope(const void* src, void* dst, const float* cos, const float* sin, long long rows, int T, int n_rot_heads,
+             int heads_total, int hd, float sign, int dtype, cudaStream_t stream);
+int fmb_qk_norm_rope_fwd(const void* x, const void* w, const float* cos, const float* sin, void* y, float* rstd,
+                         long long rows, int T, int H, int hd, float eps, int dtype, int w_dtype, cudaStream_t stream);
+int fmb_qk_norm_rope_bwd(const void* dy, const void* x, const void* w, const float* cos, const float* sin,
+                         const float* rstd, void* dx, float* dw_partial, float* dw, long long rows, int T, int H, int hd,
+                         int dtype, int w_dtype, int nblocks, cudaStream_t stream);
+int fmb_softmax_fwd(const void* x, void* y, long long rows, int n, int dtype, cudaStream_t stream);
+int fmb_softmax_bwd(const void* y, const void* dy, void* dx, long long rows, int n, int dtype, cudaStream_t stream);
+int fmb_topk(const void* x, void* values, long long* indices, long long rows, int n, int k, int dtype,
+             cudaStream_t stream);
+
+// ---- losses (loss.cu)
+// In place: logits[rows, V] (bf16) become dlogits = (softmax - onehot) * grad_scale; per-row loss
+// (lse - logit[label], 0 for ignored rows) goes to row_loss.
+int fmb_ce_fwd_bwd(void* logits, const long long* labels, float* row_loss, long long rows, int V, long long ld,
+                   float grad_scale, const float* grad_scale_ptr, long long ignore_index, int write_grad,
+                   cudaStream_t stream);
+int fmb_kl_fwd_bwd(const void* student, const void* teacher, float* row_loss, void* grad, long long rows, int V,
+                   float grad_scale, int dtype, int write_grad, cudaStream_t stream);
+int fmb_sum_f32(const float* x, float* out, long long n, float scale, int accumulate, cudaStream_t stream);
+
+// ---- router (moe.cu)
+int fmb_router_topk(const float* logits, float* weights, int* idx, float* probs_sum, int* counts, float* z_sum,
+                    long long rows, int E, int k, cudaStream_t stream);
+int fmb_moe_gather(const void* x, const int* token_of_slot, void* out, long long slots, int d, cudaStream_t stream);
+int fmb_moe_combine(const void* ys, const int* slot_of_token, const float* w, void* out, long long tokens, int k,
+                    int d, cudaStream_t stream);
+
+// ---- optimizer (optim.cu)
+// Flat AdamW over n fp32 elements. `ctl` points to {float clip_coef, int ok}; when ok == 0 the
+// kernel leaves everything untouched. shadow (bf16, may be null) receives the updated weights.
+int fmb_adamw_flat(float* p, const float* g, float* m, float* v, void* shadow, long long n, float lr, float beta1,
+                   float beta2, float eps, float wd, float bc1, float bc2, const float* ctl, cudaStream_t stream);
+int fmb_sqnorm_f32(const float* x, float* out, long long n, int accumulate, cudaStream_t stream);
+int fmb_scale_cast(const void* src, void* dst, long long n, float scale, int src_dtype, int dst_dtype,
+                   cudaStream_t stream);
+int fmb_ns_axpby(const void* x, const void* y, void* out, long long n, float a, float b, int dtype,
+                 cudaStream_t stream);
+
+// ---- attention (attention_sm100.cu)
+int fmb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T, int Hq, int Hkv,
+                 int hd, long long q_stride_t, long long kv_stride_t, long long o_stride_t, float scale, int causal,
+                 int* status, cudaStream_t stream);
+int fmb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                 void* dq, void* dk, void* dv, float* delta, float* dq_acc, int B, int T, int Hq, int Hkv, int hd,
+                 long long q_stride_t, long long kv_stride_t, long long o_stride_t, long long dq_stride_t,
+                 long long dkv_stride_t, float scale, int causal, int* status, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,77 @@
+"""Loader and autograd wrappers for the sm_100a kernels.
+
+``native()`` returns the compiled extension (``forgeminds_b200/_C.so``, built in-tree by
+``forgeminds_b200.csrc.build``). On a machine with a CUDA device a missing extension is an error,
+not a silent fall-back: :func:`require` raises with the build command. On CPU the pure-PyTorch
+paths in :mod:`forgeminds_b200.kernels.reference` are used instead.
+"""
+from __future__ import annotations
+
+import importlib
+import threading
+
+import torch
+
+_lock = threading.Lock()
+_mod = None
+_err: Exception | None = None
+
+
+def native():
+    """The extension module, or ``None`` if it cannot be imported."""
+    global _mod, _err
+    if _mod is not None or _err is not None:
+        return _mod
+    with _lock:
+        if _mod is None and _err is None:
+            try:
+                _mod = importlib.import_module("forgeminds_b200._C")
+            except Exception as exc:  # missing file, wrong ABI, no libcudart ...
+                _err = exc
+    return _mod
+
+
+def available() -> bool:
+    """True when the kernels can run here: a CUDA device of compute capability 10.x and the extension."""
+    if not torch.cuda.is_available():
+        return False
+    try:
+        major, _ = torch.cuda.get_device_capability()
+    except Exception:
+        return False
+    return major == 10 and native() is not None
+
+
+def require():
+    """Extension module or a loud error (used by every GPU code path)."""
+    mod = native()
+    if mod is None:
+        raise RuntimeError(
+            "forgeminds_b200: the native extension forgeminds_b200/_C.so is missing or failed to load "
+            f"({_err!r}). Build it with `python -m forgeminds_b200.csrc.build`.")
+    return mod
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 word that kernels set when one of their bounded waits runs out."""
+    key = torch.device(device)
+    word = _status.get(key)
+    if word is None:
+        word = _status[key] = torch.zeros(1, dtype=torch.int32, device=key)
+    return word
+
+
+_status: dict = {}
+
+
+class CommTimeout(RuntimeError):
+    """A device-side wait gave up; the status word holds the error code."""
+
+
+def check_status(device, sync_value: int | None = None) -> None:
+    """Raise :class:`CommTimeout` if a kernel reported a timed-out wait. ``sync_value`` lets a
+    caller pass a value it already brought to the host so that no extra sync is paid."""
+    code = int(status_word(device).item()) if sync_value is None else int(sync_value)
+    if code:
+        status_word(device).zero_()
+        raise CommTimeout(f"forgeminds_b200: a kernel wait timed out (code {code})")

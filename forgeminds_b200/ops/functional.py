@@ -1,0 +1,383 @@
+"""Autograd wrappers around the native kernels (GPU only; callers pick the torch path on CPU).
+
+Conventions
+-----------
+* Activations are bf16, 2-D ``[tokens, features]`` inside these functions.
+* ``linear`` computes ``x @ W.T`` with ``W`` in ``nn.Linear`` layout. The weight may be an fp32
+  master parameter: a bf16 shadow copy is cached on the parameter (``_fm_shadow``) and refreshed
+  only when the parameter's version changed, instead of being re-cast on every forward.
+* Weight gradients are produced in fp32 by the GEMM epilogue. If the parameter carries a
+  ``_fm_main_grad`` buffer, the weight-gradient GEMM accumulates straight into it (no separate
+  add pass) and autograd receives ``None`` for that parameter.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch.autograd.function import once_differentiable
+
+from . import require, status_word
+
+BF16 = torch.bfloat16
+
+
+# ------------------------------------------------------------------------------ helpers
+def bf16_of(p: torch.Tensor) -> torch.Tensor:
+    """bf16 view of a parameter: itself when already bf16, else a cached shadow copy."""
+    if p.dtype == BF16:
+        return p.detach()
+    cached = getattr(p, "_fm_shadow", None)
+    if cached is not None and cached[1] == p._version and cached[0].device == p.device:
+        return cached[0]
+    shadow = torch.empty(p.shape, dtype=BF16, device=p.device)
+    src = p.detach()
+    if src.dtype == torch.float32 and src.is_contiguous():
+        require().scale_cast(src, shadow, 1.0)
+    else:
+        shadow.copy_(src)
+    try:
+        p._fm_shadow = (shadow, p._version)
+    except Exception:
+        pass
+    return shadow
+
+
+def gemm(a, b, *, a_mn=False, b_mn=False, out=None, c=None, alpha=1.0, beta=0.0, alpha_dev=None,
+         out_dtype=BF16, allow_split=False, force_bn=0):
+    """``out = alpha * A' @ B'.T + beta * c`` where ``A'`` is ``a`` ([M,K]) or ``a.T`` when
+    ``a_mn`` (``a`` stored [K,M]); likewise for ``b`` ([N,K] or [K,N])."""
+    C = require()
+    M = a.shape[1] if a_mn else a.shape[0]
+    N = b.shape[1] if b_mn else b.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    C.gemm(a, b, out, c, a_mn, b_mn, float(alpha), float(beta), alpha_dev, allow_split, status_word(a.device),
+           int(force_bn))
+    return out
+
+
+def _rows(x):
+    return x.reshape(-1, x.shape[-1])
+
+
+# ------------------------------------------------------------------------------ linear
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, residual):
+        w = bf16_of(weight)
+        x2 = _rows(x)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        res2 = None
+        if residual is not None:
+            res2 = _rows(residual)
+            if not res2.is_contiguous():
+                res2 = res2.contiguous()
+        y = gemm(x2, w, c=res2, beta=1.0 if res2 is not None else 0.0)
+        ctx.save_for_backward(x2, w)
+        ctx.weight = weight
+        ctx.x_shape = x.shape
+        ctx.has_res = residual is not None
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        weight = ctx.weight
+        dy2 = _rows(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            main = getattr(weight, "_fm_main_grad", None)
+            if main is not None:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=main, c=main, beta=1.0, allow_split=True)
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32, allow_split=True)
+                if dw.dtype != weight.dtype:
+                    dw = dw.to(weight.dtype)
+        return dx, dw, (dy if ctx.has_res else None)
+
+
+def linear(x, weight, residual=None):
+    """``x @ weight.T (+ residual)`` on the tcgen05 GEMM; the residual add runs in the epilogue."""
+    return _Linear.apply(x, weight, residual)
+
+
+# ------------------------------------------------------------------------------ RMSNorm
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        C = require()
+        x2 = _rows(x).contiguous()
+        wd = w.detach()
+        if wd.dtype not in (torch.float32, x2.dtype):
+            wd = wd.to(x2.dtype)
+        y, rstd = C.rmsnorm_fwd(x2, wd.contiguous(), eps)
+        ctx.save_for_backward(x2, wd, rstd)
+        ctx.w_dtype = w.dtype
+        return y.view(x.shape)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dy):
+        C = require()
+        x2, wd, rstd = ctx.saved_tensors
+        dx, dw = C.rmsnorm_bwd(_rows(dy).contiguous(), x2, wd, rstd, None, ctx.needs_input_grad[1])
+        if dw is not None and dw.dtype != ctx.w_dtype:
+            dw = dw.to(ctx.w_dtype)
+        return dx.view(dy.shape), dw, None
+
+
+def rms_norm(x, w, eps=1e-6):
+    return _RMSNorm.apply(x, w, eps)
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, delta, w, eps):
+        C = require()
+        x2, d2 = _rows(x).contiguous(), _rows(delta).contiguous()
+        wd = w.detach()
+        if wd.dtype not in (torch.float32, x2.dtype):
+            wd = wd.to(x2.dtype)
+        xn, y, rstd = C.add_rmsnorm_fwd(x2, d2, wd.contiguous(), eps)
+        ctx.save_for_backward(xn, wd, rstd)
+        ctx.w_dtype = w.dtype
+        return xn.view(x.shape), y.view(x.shape)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, gxn, gy):
+        C = require()
+        xn, wd, rstd = ctx.saved_tensors
+        gy2 = _rows(gy).contiguous() if gy is not None else torch.zeros_like(xn)
+        res = _rows(gxn).contiguous() if gxn is not None else None
+        dx, dw = C.rmsnorm_bwd(gy2, xn, wd, rstd, res, ctx.needs_input_grad[2])
+        if dw is not None and dw.dtype != ctx.w_dtype:
+            dw = dw.to(ctx.w_dtype)
+        dx = dx.view(gy.shape if gy is not None else gxn.shape)
+        return dx, dx, dw, None
+
+
+def add_rms_norm(x, delta, w, eps=1e-6):
+    """Returns ``(x + delta, rms_norm(x + delta) * w)`` from one pass over the row."""
+    return _AddRMSNorm.apply(x, delta, w, eps)
+
+
+# ------------------------------------------------------------------------------ SwiGLU
+class _SwiGLUSplit(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        C = require()
+        g2 = _rows(gu)
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        h = g2.shape[1] // 2
+        out = C.swiglu_fwd(g2[:, :h], g2[:, h:])
+        ctx.save_for_backward(g2)
+        return out.view(*gu.shape[:-1], h)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dy):
+        C = require()
+        (g2,) = ctx.saved_tensors
+        h = g2.shape[1] // 2
+        dgu = torch.empty_like(g2)
+        C.swiglu_bwd(g2[:, :h], g2[:, h:], _rows(dy).contiguous(), dgu[:, :h], dgu[:, h:])
+        return dgu.view(*dy.shape[:-1], 2 * h)
+
+
+def swiglu_split(gu):
+    """``silu(gu[..., :h]) * gu[..., h:]``"""
+    return _SwiGLUSplit.apply(gu)
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        C = require()
+        g2, u2 = _rows(gate).contiguous(), _rows(up).contiguous()
+        out = C.swiglu_fwd(g2, u2)
+        ctx.save_for_backward(g2, u2)
+        return out.view(gate.shape)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dy):
+        C = require()
+        g2, u2 = ctx.saved_tensors
+        dg, du = torch.empty_like(g2), torch.empty_like(u2)
+        C.swiglu_bwd(g2, u2, _rows(dy).contiguous(), dg, du)
+        return dg.view(dy.shape), du.view(dy.shape)
+
+
+def swiglu(gate, up):
+    return _SwiGLU.apply(gate, up)
+
+
+# ------------------------------------------------------------------------------ RoPE on a fused qkv buffer
+class _RopeQKV(torch.autograd.Function):
+    """Rotates the q and k heads of ``qkv [B, T, (Hq + 2 Hkv) * hd]`` in place (v untouched)."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, n_q, n_kv, hd):
+        C = require()
+        B, T = qkv.shape[0], qkv.shape[1]
+        C.rope(qkv, qkv, cos, sin, T, n_q + n_kv, n_q + 2 * n_kv, hd, 1.0)
+        ctx.mark_dirty(qkv)
+        ctx.save_for_backward(cos, sin)
+        ctx.dims = (T, n_q, n_kv, hd)
+        return qkv
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, g):
+        C = require()
+        cos, sin = ctx.saved_tensors
+        T, n_q, n_kv, hd = ctx.dims
+        g = g.contiguous()
+        out = torch.empty_like(g)           # the incoming gradient is not ours to overwrite
+        C.rope(g, out, cos, sin, T, n_q + n_kv, n_q + 2 * n_kv, hd, -1.0)
+        return out, None, None, None, None, None
+
+
+def rope_qkv_(qkv, cos, sin, n_q, n_kv, hd):
+    return _RopeQKV.apply(qkv, cos, sin, n_q, n_kv, hd)
+
+
+# ------------------------------------------------------------------------------ attention
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, n_q, n_kv, hd, causal):
+        C = require()
+        B, T, _ = qkv.shape
+        q = qkv[..., : n_q * hd].unflatten(-1, (n_q, hd))
+        k = qkv[..., n_q * hd: (n_q + n_kv) * hd].unflatten(-1, (n_kv, hd))
+        v = qkv[..., (n_q + n_kv) * hd:].unflatten(-1, (n_kv, hd))
+        o, lse = C.attn_fwd(q, k, v, 1.0 / math.sqrt(hd), causal, status_word(qkv.device))
+        ctx.save_for_backward(qkv, o, lse)
+        ctx.dims = (n_q, n_kv, hd, causal)
+        return o.view(B, T, n_q * hd)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, d_o):
+        C = require()
+        qkv, o, lse = ctx.saved_tensors
+        n_q, n_kv, hd, causal = ctx.dims
+        B, T, _ = qkv.shape
+        dqkv = torch.empty_like(qkv)
+        q = qkv[..., : n_q * hd].unflatten(-1, (n_q, hd))
+        k = qkv[..., n_q * hd: (n_q + n_kv) * hd].unflatten(-1, (n_kv, hd))
+        v = qkv[..., (n_q + n_kv) * hd:].unflatten(-1, (n_kv, hd))
+        dq = dqkv[..., : n_q * hd].unflatten(-1, (n_q, hd))
+        dk = dqkv[..., n_q * hd: (n_q + n_kv) * hd].unflatten(-1, (n_kv, hd))
+        dv = dqkv[..., (n_q + n_kv) * hd:].unflatten(-1, (n_kv, hd))
+        C.attn_bwd(q, k, v, o, d_o.contiguous().view(B, T, n_q, hd), lse, dq, dk, dv, 1.0 / math.sqrt(hd), causal,
+                   status_word(qkv.device))
+        return dqkv, None, None, None, None
+
+
+def attention_qkv(qkv, n_q, n_kv, hd, causal=True):
+    """Causal GQA flash attention reading q, k, v as slices of one fused projection output."""
+    return _Attention.apply(qkv, n_q, n_kv, hd, causal)
+
+
+# ------------------------------------------------------------------------------ fused lm_head + cross-entropy
+class _LinearCrossEntropy(torch.autograd.Function):
+    """``mean CE(h @ W.T, labels)`` without keeping fp32 logits: each chunk of bf16 logits is
+    turned into its gradient in place by the loss kernel; the two gradient GEMMs run once in the
+    backward over all chunks, scaled by the incoming gradient through a device scalar."""
+
+    @staticmethod
+    def forward(ctx, h, weight, labels, chunk, ignore_index):
+        C = require()
+        w = bf16_of(weight)
+        h2 = _rows(h)
+        if not h2.is_contiguous():
+            h2 = h2.contiguous()
+        y = labels.reshape(-1)
+        n_tok, V = h2.shape[0], w.shape[0]
+        valid = (y != ignore_index).sum().clamp(min=1).to(torch.float32)
+        inv_n = valid.reciprocal()
+        need_grad = any(ctx.needs_input_grad[:2])
+        dlogits = torch.empty((n_tok, V), dtype=BF16, device=h.device)
+        row_loss = torch.empty(n_tok, dtype=torch.float32, device=h.device)
+        for i in range(0, n_tok, chunk):
+            j = min(n_tok, i + chunk)
+            gemm(h2[i:j], w, out=dlogits[i:j])
+            row_loss[i:j] = C.ce_fwd_bwd(dlogits[i:j], y[i:j], 1.0, inv_n, ignore_index, need_grad)
+        total = torch.empty((), dtype=torch.float32, device=h.device)
+        C.sum_f32(row_loss, total, 1.0, False)
+        ctx.save_for_backward(h2, w, dlogits if need_grad else None)
+        ctx.weight = weight
+        ctx.h_shape = h.shape
+        return total * inv_n
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, g):
+        h2, w, dlogits = ctx.saved_tensors
+        weight = ctx.weight
+        g32 = g.to(torch.float32).reshape(1).contiguous()
+        dh = dw = None
+        if ctx.needs_input_grad[0]:
+            dh = gemm(dlogits, w, b_mn=True, alpha_dev=g32).view(ctx.h_shape)
+        if ctx.needs_input_grad[1]:
+            main = getattr(weight, "_fm_main_grad", None)
+            if main is not None:
+                gemm(dlogits, h2, a_mn=True, b_mn=True, out=main, c=main, beta=1.0, alpha_dev=g32, allow_split=True)
+            else:
+                dw = gemm(dlogits, h2, a_mn=True, b_mn=True, out_dtype=torch.float32, alpha_dev=g32, allow_split=True)
+                if dw.dtype != weight.dtype:
+                    dw = dw.to(weight.dtype)
+        return dh, dw, None, None, None
+
+
+def linear_cross_entropy(h, weight, labels, chunk=4096, ignore_index=-100):
+    return _LinearCrossEntropy.apply(h, weight, labels, int(chunk), int(ignore_index))
+
+
+# ------------------------------------------------------------------------------ softmax / top-k
+class _Softmax(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        y = require().softmax_fwd(x.contiguous())
+        ctx.save_for_backward(y)
+        return y
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dy):
+        (y,) = ctx.saved_tensors
+        return require().softmax_bwd(y, dy.contiguous())
+
+
+def softmax_lastdim(x):
+    return _Softmax.apply(x)
+
+
+class _TopK(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, k):
+        values, indices = require().topk(x.contiguous(), k)
+        ctx.save_for_backward(indices)
+        ctx.shape = x.shape
+        ctx.mark_non_differentiable(indices)
+        return values, indices
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, gv, _gi):
+        (indices,) = ctx.saved_tensors
+        return gv.new_zeros(ctx.shape).scatter_(-1, indices, gv), None
+
+
+def topk_lastdim(x, k):
+    return _TopK.apply(x, k)

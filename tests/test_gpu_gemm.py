@@ -1,0 +1,111 @@
+"""tcgen05 GEMM against an fp32 PyTorch reference: all operand layouts, epilogues, ragged edges."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_mn, b_mn):
+    A = a.float().t() if a_mn else a.float()
+    B = b.float().t() if b_mn else b.float()
+    return A @ B.t()
+
+
+def _mk(rows, cols, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(rows, cols, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+
+
+def _close(out, ref, K):
+    tol = 2e-2 * (K ** 0.5) * 0.25 + 1e-2
+    err = (out.float() - ref).abs().max().item()
+    assert err < tol, f"max err {err} > {tol}"
+    rel = (out.float() - ref).norm() / ref.norm().clamp(min=1e-6)
+    assert rel < 1e-2, f"relative error {rel}"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 384, 320), (1024, 1536, 1024), (200, 136, 72)])
+def test_layouts(M, N, K, a_mn, b_mn, cuda_status):
+    from forgeminds_b200.ops.functional import gemm
+    a = _mk(K, M, 1) if a_mn else _mk(M, K, 1)
+    b = _mk(K, N, 2) if b_mn else _mk(N, K, 2)
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    _close(out, _ref(a, b, a_mn, b_mn), K)
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_tile_widths(bn, cuda_status):
+    from forgeminds_b200.ops.functional import gemm
+    a, b = _mk(640, 512, 3), _mk(768, 512, 4)
+    out = gemm(a, b, force_bn=bn)
+    _close(out, _ref(a, b, False, False), 512)
+
+
+def test_residual_epilogue(cuda_status):
+    from forgeminds_b200.ops.functional import gemm
+    a, b, r = _mk(512, 256, 5), _mk(384, 256, 6), _mk(512, 384, 7)
+    out = gemm(a, b, c=r, beta=1.0)
+    _close(out, _ref(a, b, False, False) + r.float(), 256)
+
+
+def test_fp32_accumulate_and_split_k(cuda_status):
+    from forgeminds_b200.ops.functional import gemm
+    # weight-gradient shape: few output tiles, long reduction -> split-K with atomics
+    dy, x = _mk(8192, 256, 8), _mk(8192, 384, 9)
+    acc = torch.full((256, 384), 0.5, device="cuda")
+    gemm(dy, x, a_mn=True, b_mn=True, out=acc, c=acc, beta=1.0, allow_split=True)
+    ref = dy.float().t() @ x.float() + 0.5
+    assert (acc - ref).abs().max() < 0.35
+    assert (acc - ref).norm() / ref.norm() < 2e-3
+    fresh = gemm(dy, x, a_mn=True, b_mn=True, out_dtype=torch.float32, allow_split=True)
+    assert (fresh - (ref - 0.5)).norm() / ref.norm() < 2e-3
+
+
+def test_device_alpha(cuda_status):
+    from forgeminds_b200.ops.functional import gemm
+    a, b = _mk(256, 128, 10), _mk(256, 128, 11)
+    s = torch.tensor([0.25], device="cuda")
+    out = gemm(a, b, alpha=2.0, alpha_dev=s)
+    _close(out, 0.5 * _ref(a, b, False, False), 128)
+
+
+def test_strided_rows(cuda_status):
+    from forgeminds_b200.ops.functional import gemm
+    big = _mk(512, 1024, 12)
+    a = big[:, 256:512]                       # row pitch 1024, 256 columns
+    b = _mk(128, 256, 13)
+    out = gemm(a, b)
+    _close(out, a.float() @ b.float().t(), 256)
+
+
+def test_linear_autograd(cuda_status):
+    from forgeminds_b200.ops.functional import linear
+    x = _mk(512, 256, 14).requires_grad_()
+    w = torch.randn(384, 256, device="cuda", requires_grad=True) * 0.05
+    w = w.detach().requires_grad_()
+    res = _mk(512, 384, 15).requires_grad_()
+    y = linear(x, w, res)
+    g = _mk(512, 384, 16)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().to(torch.bfloat16).float().requires_grad_()
+    rr = res.detach().float().requires_grad_()
+    yr = xr @ wr.t() + rr
+    yr.backward(g.float())
+    assert (y.float() - yr).abs().max() < 0.1
+    assert (x.grad.float() - xr.grad).norm() / xr.grad.norm() < 1e-2
+    assert (w.grad - wr.grad).norm() / wr.grad.norm() < 1e-2
+    assert torch.equal(res.grad, g)
+
+
+def test_main_grad_accumulation(cuda_status):
+    from forgeminds_b200.ops.functional import linear
+    x = _mk(1024, 256, 17)
+    w = (torch.randn(128, 256, device="cuda") * 0.05).requires_grad_()
+    w._fm_main_grad = torch.zeros(128, 256, device="cuda")
+    for _ in range(2):
+        linear(x, w).sum().backward()
+    assert w.grad is None
+    ref = 2 * torch.ones(1024, 128, device="cuda").t() @ x.float()
+    assert (w._fm_main_grad - ref).norm() / ref.norm() < 2e-3
