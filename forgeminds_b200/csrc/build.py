@@ -24,7 +24,7 @@ TARGET = PKG / "_C.so"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--use_fast_math",
               "-DFMB_BUILD"]
-CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wno-attributes"]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wno-attributes", "-DFMB_WITH_ATTENTION"]
 
 
 def _nvcc() -> str:

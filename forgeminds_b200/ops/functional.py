@@ -108,6 +108,130 @@ def linear(x, weight, residual=None):
     return _Linear.apply(x, weight, residual)
 
 
+def _adjacent(views) -> bool:
+    """True when the tensors are contiguous row blocks lying back to back in one storage."""
+    nxt = None
+    for v in views:
+        if v is None or not v.is_contiguous():
+            return False
+        if nxt is not None and v.data_ptr() != nxt:
+            return False
+        nxt = v.data_ptr() + v.numel() * v.element_size()
+    return True
+
+
+def _stack_view(views):
+    """Zero-copy ``[sum rows, K]`` view over adjacent row blocks."""
+    first = views[0]
+    rows = sum(v.shape[0] for v in views)
+    return torch.as_strided(first, (rows, first.shape[1]), (first.shape[1], 1))
+
+
+def fused_bf16(weights) -> torch.Tensor:
+    """bf16 ``[sum N_i, K]`` matrix of several ``[N_i, K]`` weights. No copy when their shadows are
+    neighbours in memory (the flat parameter store lays them out that way); otherwise the
+    concatenation is cached on the first weight until any of the versions changes."""
+    shadows = [bf16_of(w) for w in weights]
+    if len(shadows) == 1:
+        return shadows[0]
+    if _adjacent(shadows):
+        return _stack_view(shadows)
+    head = weights[0]
+    key = tuple((id(w), w._version) for w in weights)
+    cached = getattr(head, "_fm_fused", None)
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    fused = torch.cat(shadows, dim=0)
+    head._fm_fused = (key, fused)
+    return fused
+
+
+def fused_main_grad(weights):
+    grads = [getattr(w, "_fm_main_grad", None) for w in weights]
+    if any(g is None for g in grads):
+        return None
+    if len(grads) == 1:
+        return grads[0]
+    return _stack_view(grads) if _adjacent(grads) else None
+
+
+class _LinearMulti(torch.autograd.Function):
+    """``x @ cat(weights).T`` as one GEMM (fused q|k|v or gate|up projection) while the weights
+    stay separate parameters."""
+
+    @staticmethod
+    def forward(ctx, x, *weights):
+        w = fused_bf16(weights)
+        x2 = _rows(x)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        y = gemm(x2, w)
+        ctx.save_for_backward(x2, w)
+        ctx.weights = weights
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        weights = ctx.weights
+        dy2 = _rows(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = gemm(dy2, w, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        grads = [None] * len(weights)
+        if any(ctx.needs_input_grad[1:]):
+            main = fused_main_grad(weights)
+            if main is not None:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=main, c=main, beta=1.0, allow_split=True)
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32, allow_split=True)
+                lo = 0
+                for i, wt in enumerate(weights):
+                    piece = dw[lo: lo + wt.shape[0]]
+                    lo += wt.shape[0]
+                    own = getattr(wt, "_fm_main_grad", None)
+                    if own is not None:
+                        own.add_(piece)
+                    elif ctx.needs_input_grad[1 + i]:
+                        grads[i] = piece if piece.dtype == wt.dtype else piece.to(wt.dtype)
+        return (dx, *grads)
+
+
+def linear_multi(x, weights):
+    return _LinearMulti.apply(x, *weights)
+
+
+class _Embedding(torch.autograd.Function):
+    """Row gather from the bf16 shadow of an fp32 table; the gradient is scattered in fp32."""
+
+    @staticmethod
+    def forward(ctx, tokens, weight):
+        table = bf16_of(weight)
+        ctx.save_for_backward(tokens)
+        ctx.weight = weight
+        return torch.nn.functional.embedding(tokens, table)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dy):
+        (tokens,) = ctx.saved_tensors
+        weight = ctx.weight
+        flat = tokens.reshape(-1)
+        rows = dy.reshape(-1, dy.shape[-1]).to(torch.float32)
+        main = getattr(weight, "_fm_main_grad", None)
+        if main is not None:
+            main.index_add_(0, flat, rows)
+            return None, None
+        dw = torch.zeros(weight.shape, dtype=torch.float32, device=dy.device).index_add_(0, flat, rows)
+        return None, dw if dw.dtype == weight.dtype else dw.to(weight.dtype)
+
+
+def embedding(tokens, weight):
+    return _Embedding.apply(tokens, weight)
+
+
 # ------------------------------------------------------------------------------ RMSNorm
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
