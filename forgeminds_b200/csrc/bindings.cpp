@@ -4,6 +4,8 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include <atomic>
+
 #include "fmb_api.h"
 
 extern "C" {
@@ -32,9 +34,15 @@ int dt(const Tensor& t) {
   TORCH_CHECK(false, "forgeminds_b200: unsupported dtype ", t.scalar_type());
 }
 
-void ok(int rc, const char* what) {
+// Number of kernels of this library enqueued so far by this process (reported by the benchmarks).
+std::atomic<long long> g_launches{0};
+
+void ok(int rc, const char* what, int kernels = 1) {
   TORCH_CHECK(rc == 0, "forgeminds_b200 native call '", what, "' failed with code ", rc);
+  g_launches.fetch_add(kernels, std::memory_order_relaxed);
 }
+
+long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 void cuda_contig(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
@@ -121,7 +129,7 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
   if (dres.has_value() && dres->defined()) cuda_contig(*dres, "dres");
   ok(fmb_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), cptr(dres), dx.data_ptr(),
                      need_dw ? dwp.data_ptr<float>() : nullptr, need_dw ? dw.data_ptr<float>() : nullptr, 0, rows,
-                     static_cast<int>(d), dt(x), dt(w), nb, cur_stream()), "rmsnorm_bwd");
+                     static_cast<int>(d), dt(x), dt(w), nb, cur_stream()), "rmsnorm_bwd", need_dw ? 2 : 1);
   return {dx, dw};
 }
 
@@ -184,7 +192,7 @@ std::vector<Tensor> qk_norm_rope_bwd(const Tensor& dy, const Tensor& x, const Te
   ok(fmb_qk_norm_rope_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(),
                           rstd.data_ptr<float>(), dx.data_ptr(), dwp.data_ptr<float>(), dw.data_ptr<float>(), rows,
                           static_cast<int>(T), static_cast<int>(H), static_cast<int>(hd), dt(x), dt(w), nb,
-                          cur_stream()), "qk_norm_rope_bwd");
+                          cur_stream()), "qk_norm_rope_bwd", 2);
   return {dx, dw};
 }
 
@@ -282,7 +290,7 @@ void sqnorm(const Tensor& x, Tensor& scratch, Tensor& out, bool accumulate) {
   TORCH_CHECK(x.scalar_type() == at::kFloat && scratch.numel() >= 1024 && scratch.scalar_type() == at::kFloat);
   c10::cuda::CUDAGuard guard(x.device());
   ok(fmb_sqnorm_f32_scratch(x.data_ptr<float>(), scratch.data_ptr<float>(), out.data_ptr<float>(), x.numel(),
-                            accumulate, cur_stream()), "sqnorm");
+                            accumulate, cur_stream()), "sqnorm", 2);
 }
 
 void scale_cast(const Tensor& src, Tensor& dst, double scale) {
@@ -342,7 +350,7 @@ std::vector<Tensor> moe_plan(const Tensor& idx, int64_t E, int64_t align, int64_
   Tensor slot_of = torch::empty({entries}, i32), token_of = torch::full({max_slots}, -1, i32);
   ok(fmb_moe_plan(idx.data_ptr<int>(), chunk.data_ptr<int>(), region.data_ptr<int>(), meta.data_ptr<int>(),
                   slot_of.data_ptr<int>(), token_of.data_ptr<int>(), entries, static_cast<int>(E), static_cast<int>(k),
-                  static_cast<int>(align), static_cast<int>(cap), static_cast<int>(mode), cur_stream()), "moe_plan");
+                  static_cast<int>(align), static_cast<int>(cap), static_cast<int>(mode), cur_stream()), "moe_plan", 3);
   return {slot_of, token_of, region, meta};
 }
 
@@ -412,7 +420,7 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
                   dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr<float>(), dq_acc.data_ptr<float>(),
                   static_cast<int>(B), static_cast<int>(T), static_cast<int>(Hq), static_cast<int>(Hkv),
                   static_cast<int>(hd), q.stride(1), k.stride(1), o.stride(1), dq.stride(1), dk.stride(1),
-                  static_cast<float>(scale), causal, st, cur_stream()), "attn_bwd");
+                  static_cast<float>(scale), causal, st, cur_stream()), "attn_bwd", 3);
 }
 #endif
 
@@ -420,6 +428,7 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "forgeminds_b200 native kernels (sm_100a)";
+  m.def("launch_count", &launch_count);
   m.def("gemm", &gemm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);

@@ -80,8 +80,10 @@ class TokenFile(Dataset):
             self.data = np.empty(0, dtype=self.dtype)
 
     def __del__(self):  # pragma: no cover
-        with contextlib.suppress(Exception):
+        try:
             self.close()
+        except Exception:
+            pass
 
 
 # ------------------------------------------------------------------------------ sampler
@@ -396,6 +398,9 @@ class BatchStream:
 
     # ---- control
     def resume(self, epoch: int, batches: int) -> None:
+        self._halt()                 # the old producer must be gone before the sampler is touched
+        self._box.drain()
+        self._release_iterator()
         self.epoch, self.batches = epoch, batches
         self._from = (epoch, batches)
         self.sampler.skip = batches * int(getattr(self.loader, "batch_size", 0) or 0)
@@ -443,8 +448,10 @@ class BatchStream:
         return False
 
     def __del__(self):  # pragma: no cover
-        with contextlib.suppress(Exception):
+        try:
             self.close()
+        except Exception:
+            pass
 
 
 # ------------------------------------------------------------------------------ generic prefetcher
@@ -522,8 +529,10 @@ class _AsyncLoader:
         return False
 
     def __del__(self):  # pragma: no cover
-        with contextlib.suppress(Exception):
+        try:
             self.close()
+        except Exception:
+            pass
 
 
 def async_loader(loader, device, depth: int = 2):

@@ -158,17 +158,17 @@ class Attention(nn.Module):
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=q.shape[1] != k.shape[1])
         return self.wo(o.transpose(1, 2).reshape(B, T, -1))
 
-    # -- sm_100a path: x [B,T,d] bf16 -> (residual + attention output)
-    def forward_native(self, x, residual):
+    # -- sm_100a path: residual stream x [B,T,d] bf16 -> x + attention(norm(x))
+    def forward_native(self, x, norm):
         from ..ops import functional as Fn
         B, T, _ = x.shape
         hd = self.hd
         n_q, n_kv = self.wq.weight.shape[0] // hd, self.wk.weight.shape[0] // hd
-        qkv = Fn.linear_multi(x, (self.wq.weight, self.wk.weight, self.wv.weight))
+        qkv = Fn.norm_linear_multi(x, norm.weight, norm.eps, (self.wq.weight, self.wk.weight, self.wv.weight))
         cos, sin = rope_tables(T, hd, self.theta, x.device, torch.float32)
         qkv = Fn.rope_qkv_(qkv, cos.reshape(T, hd // 2), sin.reshape(T, hd // 2), n_q, n_kv, hd)
         o = Fn.attention_qkv(qkv, n_q, n_kv, hd, True)
-        return Fn.linear(o, self.wo.weight, residual)
+        return Fn.linear(o, self.wo.weight, x)
 
 
 class SwiGLU(nn.Module):
@@ -181,10 +181,11 @@ class SwiGLU(nn.Module):
     def forward(self, x):
         return self.w2(F.silu(self.w1(x)) * self.w3(x))
 
-    def forward_native(self, x, residual):
+    def forward_native(self, x, norm):
+        """``x + mlp(norm(x))``; the norm output and the activation are recomputed in the backward."""
         from ..ops import functional as Fn
-        gu = Fn.linear_multi(x, (self.w1.weight, self.w3.weight))
-        return Fn.linear(Fn.swiglu_split(gu), self.w2.weight, residual)
+        gu = Fn.norm_linear_multi(x, norm.weight, norm.eps, (self.w1.weight, self.w3.weight))
+        return Fn.swiglu_linear(gu, self.w2.weight, x)
 
 
 class Block(nn.Module):
@@ -220,11 +221,10 @@ class Block(nn.Module):
         from ..ops import functional as Fn
         if x.dtype != torch.bfloat16:
             x = x.to(torch.bfloat16)
-        x = self.attn.forward_native(Fn.rms_norm(x, self.attn_norm.weight, self.attn_norm.eps), x)
-        h = Fn.rms_norm(x, self.ffn_norm.weight, self.ffn_norm.eps)
-        if hasattr(self.ffn, "forward_native"):
-            return self.ffn.forward_native(h, x)
-        return x + self.ffn(h)
+        x = self.attn.forward_native(x, self.attn_norm)
+        if isinstance(self.ffn, SwiGLU):
+            return self.ffn.forward_native(x, self.ffn_norm)
+        return x + self.ffn(Fn.rms_norm(x, self.ffn_norm.weight, self.ffn_norm.eps))
 
 
 class GPT(nn.Module):

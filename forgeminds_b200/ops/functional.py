@@ -28,9 +28,12 @@ def bf16_of(p: torch.Tensor) -> torch.Tensor:
     if p.dtype == BF16:
         return p.detach()
     cached = getattr(p, "_fm_shadow", None)
-    if cached is not None and cached[1] == p._version and cached[0].device == p.device:
-        return cached[0]
-    shadow = torch.empty(p.shape, dtype=BF16, device=p.device)
+    if cached is not None and cached[0].device == p.device and cached[0].shape == p.shape:
+        if cached[1] == p._version:
+            return cached[0]
+        shadow = cached[0]          # refresh in place: the buffer may be a view owned by a flat store
+    else:
+        shadow = torch.empty(p.shape, dtype=BF16, device=p.device)
     src = p.detach()
     if src.dtype == torch.float32 and src.is_contiguous():
         require().scale_cast(src, shadow, 1.0)
@@ -201,6 +204,121 @@ class _LinearMulti(torch.autograd.Function):
 
 def linear_multi(x, weights):
     return _LinearMulti.apply(x, *weights)
+
+
+def _weight_grads(ctx_needs, weights, dy2, x2):
+    """Weight gradient of a (fused) projection: accumulate into main-grad buffers when the
+    parameters carry them, otherwise hand fp32 slices back to autograd."""
+    grads = [None] * len(weights)
+    if not any(ctx_needs):
+        return grads
+    main = fused_main_grad(weights)
+    if main is not None:
+        gemm(dy2, x2, a_mn=True, b_mn=True, out=main, c=main, beta=1.0, allow_split=True)
+        return grads
+    dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32, allow_split=True)
+    lo = 0
+    for i, wt in enumerate(weights):
+        piece = dw[lo: lo + wt.shape[0]]
+        lo += wt.shape[0]
+        own = getattr(wt, "_fm_main_grad", None)
+        if own is not None:
+            own.add_(piece)
+        elif ctx_needs[i]:
+            grads[i] = piece if piece.dtype == wt.dtype else piece.to(wt.dtype)
+    return grads
+
+
+class _NormLinearMulti(torch.autograd.Function):
+    """``rms_norm(x) @ cat(weights).T``. Only ``x`` and the per-row ``rstd`` are kept; the normalised
+    activations are recomputed in the backward (one extra pass over ``x`` instead of a saved tensor)."""
+
+    @staticmethod
+    def forward(ctx, x, norm_w, eps, *weights):
+        C = require()
+        w = fused_bf16(weights)
+        x2 = _rows(x)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        nw = norm_w.detach()
+        if nw.dtype not in (torch.float32, x2.dtype):
+            nw = nw.to(x2.dtype)
+        nw = nw.contiguous()
+        h, rstd = C.rmsnorm_fwd(x2, nw, eps)
+        y = gemm(h, w)
+        ctx.save_for_backward(x2, nw, rstd, w)
+        ctx.weights, ctx.eps, ctx.x_shape, ctx.nw_dtype = weights, eps, x.shape, norm_w.dtype
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dy):
+        C = require()
+        x2, nw, rstd, w = ctx.saved_tensors
+        dy2 = _rows(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        h, _ = C.rmsnorm_fwd(x2, nw, ctx.eps)                       # recompute
+        grads = _weight_grads(ctx.needs_input_grad[3:], ctx.weights, dy2, h)
+        dx = dnw = None
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            dh = gemm(dy2, w, b_mn=True)
+            dx, dnw = C.rmsnorm_bwd(dh, x2, nw, rstd, None, ctx.needs_input_grad[1])
+            dx = dx.view(ctx.x_shape)
+            if dnw is not None and dnw.dtype != ctx.nw_dtype:
+                dnw = dnw.to(ctx.nw_dtype)
+        return (dx, dnw, None, *grads)
+
+
+def norm_linear_multi(x, norm_w, eps, weights):
+    return _NormLinearMulti.apply(x, norm_w, eps, *weights)
+
+
+class _SwiGLULinear(torch.autograd.Function):
+    """``(silu(gate) * up) @ W.T + residual`` from the fused gate|up projection output. Only ``gu``
+    is kept; the activation is recomputed in the backward."""
+
+    @staticmethod
+    def forward(ctx, gu, weight, residual):
+        C = require()
+        w = bf16_of(weight)
+        g2 = _rows(gu)
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        h = g2.shape[1] // 2
+        act = C.swiglu_fwd(g2[:, :h], g2[:, h:])
+        res2 = None
+        if residual is not None:
+            res2 = _rows(residual)
+            if not res2.is_contiguous():
+                res2 = res2.contiguous()
+        y = gemm(act, w, c=res2, beta=1.0 if res2 is not None else 0.0)
+        ctx.save_for_backward(g2, w)
+        ctx.weight, ctx.gu_shape, ctx.has_res = weight, gu.shape, residual is not None
+        return y.view(*gu.shape[:-1], w.shape[0])
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dy):
+        C = require()
+        g2, w = ctx.saved_tensors
+        h = g2.shape[1] // 2
+        dy2 = _rows(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        act = C.swiglu_fwd(g2[:, :h], g2[:, h:])                     # recompute
+        (dw,) = _weight_grads(ctx.needs_input_grad[1:2], (ctx.weight,), dy2, act)
+        dgu = None
+        if ctx.needs_input_grad[0]:
+            dact = gemm(dy2, w, b_mn=True)
+            dgu = torch.empty_like(g2)
+            C.swiglu_bwd(g2[:, :h], g2[:, h:], dact, dgu[:, :h], dgu[:, h:])
+            dgu = dgu.view(ctx.gu_shape)
+        return dgu, dw, (dy if ctx.has_res else None)
+
+
+def swiglu_linear(gu, weight, residual=None):
+    return _SwiGLULinear.apply(gu, weight, residual)
 
 
 class _Embedding(torch.autograd.Function):

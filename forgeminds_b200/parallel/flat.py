@@ -1,0 +1,285 @@
+"""Flat parameter store and the fused optimizer that runs on it.
+
+:class:`FlatParamStore` re-homes a model's parameters into three flat device buffers --
+fp32 master weights, fp32 gradients ("main grads") and bf16 working weights -- laid out bucket by
+bucket in module order (one bucket per transformer block, plus one for everything outside the
+blocks). Every ``nn.Parameter`` keeps its name and shape and becomes a view of the master buffer;
+its ``.grad`` is a view of the gradient buffer and never goes back to ``None``; its bf16 shadow
+(used by the GEMMs) is a view of the working buffer. Because the q|k|v and the gate|up weights of a
+block are neighbours in these buffers, the fused projections need no concatenation at all.
+
+What this buys on a B200:
+
+* the weight-gradient GEMMs accumulate straight into the main-grad buffer (no ``grad +=`` pass);
+* zeroing gradients is one memset, the global norm one reduction, AdamW one kernel per bucket that
+  also refreshes the bf16 weights (no per-forward casts) and takes the clip coefficient and the
+  skip flag from device memory (no host round trip);
+* data-parallel reduction works on whole buckets: ``all_reduce`` (replicated) or
+  ``reduce_scatter`` + sharded update + ``all_gather`` of the bf16 weights (sharded), each bucket on a
+  side stream as soon as its block has finished its last backward.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+
+ALIGN = 256          # elements; keeps every parameter 512-byte aligned in all three buffers
+
+
+@dataclass
+class Bucket:
+    name: str
+    start: int                  # offset of the bucket in the flat buffers (elements)
+    size: int                   # padded size, a multiple of ALIGN * shard world
+    params: list = field(default_factory=list)
+    decay: list = field(default_factory=list)     # (offset_in_bucket, numel, weight_decay on/off)
+    ready: "torch.cuda.Event | None" = None
+
+
+def _round_up(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+class FlatParamStore:
+    def __init__(self, model, device, shard_world: int = 1, block_attr: str = "layers"):
+        self.device = torch.device(device)
+        self.shard_world = max(1, int(shard_world))
+        groups: list = []
+        seen = set()
+        blocks = getattr(model, block_attr, None)
+        block_list = list(blocks.values()) if hasattr(blocks, "values") else list(blocks or [])
+        in_block = set()
+        for i, blk in enumerate(block_list):
+            ps = [p for p in blk.parameters() if p.requires_grad and id(p) not in seen]
+            for p in ps:
+                seen.add(id(p))
+                in_block.add(id(p))
+            if ps:
+                groups.append((f"block{i}", ps))
+        rest = [p for p in model.parameters() if p.requires_grad and id(p) not in seen]
+        if rest:
+            groups.append(("rest", rest))
+        self.buckets: list = []
+        cursor = 0
+        for name, ps in groups:
+            b = Bucket(name=name, start=cursor, size=0, params=ps)
+            off = 0
+            for p in ps:
+                b.decay.append((off, p.numel(), p.ndim >= 2))
+                off += _round_up(p.numel(), ALIGN)
+            b.size = _round_up(off, ALIGN * self.shard_world)
+            cursor += b.size
+            self.buckets.append(b)
+        self.total = cursor
+        self.master = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+        self.grad = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+        self.shadow = torch.zeros(self.total, dtype=torch.bfloat16, device=self.device)
+        self.params: list = []
+        self._offset: dict = {}
+        with torch.no_grad():
+            for b in self.buckets:
+                for p, (off, n, _) in zip(b.params, b.decay):
+                    lo = b.start + off
+                    self.master[lo:lo + n].copy_(p.detach().reshape(-1).to(torch.float32))
+                    p.data = self.master[lo:lo + n].view(p.shape)
+                    g = self.grad[lo:lo + n].view(p.shape)
+                    p.grad = g
+                    p._fm_main_grad = g
+                    p._fm_shadow = (self.shadow[lo:lo + n].view(p.shape), p._version)
+                    self._offset[p] = lo
+                    self.params.append(p)
+            self.refresh_shadow()
+        self._scratch = torch.empty(1024, dtype=torch.float32, device=self.device)
+
+    # ------------------------------------------------------------------ views
+    def bucket_view(self, buf: torch.Tensor, b: Bucket) -> torch.Tensor:
+        return buf[b.start:b.start + b.size]
+
+    def refresh_shadow(self) -> None:
+        """bf16 working weights <- fp32 masters (after a load_state_dict or any external edit)."""
+        if self.device.type == "cuda" and ops.available():
+            ops.require().scale_cast(self.master, self.shadow, 1.0)
+        else:
+            self.shadow.copy_(self.master)
+        for p in self.params:
+            p._fm_shadow = (p._fm_shadow[0], p._version)
+
+    def rebind(self) -> None:
+        """Re-attach ``.grad`` views (something set them to ``None``)."""
+        for p in self.params:
+            if p.grad is None or p.grad.data_ptr() != p._fm_main_grad.data_ptr():
+                p.grad = p._fm_main_grad
+
+    def zero_grad(self) -> None:
+        self.grad.zero_()
+        self.rebind()
+
+    def grad_sq_norm(self, out: torch.Tensor, view: "torch.Tensor | None" = None) -> torch.Tensor:
+        """``out[0] = sum(grad^2)`` over the whole buffer (or ``view``), on the device."""
+        g = self.grad if view is None else view
+        if self.device.type == "cuda" and ops.available():
+            ops.require().sqnorm(g, self._scratch, out, False)
+        else:
+            out.copy_(g.float().square().sum().reshape(1))
+        return out
+
+
+class FlatAdamW(torch.optim.Optimizer):
+    """AdamW over a :class:`FlatParamStore`: one fused kernel per (bucket, decay class).
+
+    ``ctl`` is a 2-float device tensor ``[clip coefficient, apply flag]`` read by the kernel, so the
+    global-norm clipping and the unanimous skip decision never need the host. Weight decay is applied
+    to parameters with ``ndim >= 2`` only (``forgemind/trainer.py:103-107``). The per-parameter state
+    (``exp_avg``, ``exp_avg_sq``, ``step``) is exposed as views, so ``state_dict()`` has the layout of
+    ``torch.optim.AdamW``.
+    """
+
+    def __init__(self, store: FlatParamStore, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
+                 shard_rank: int = 0, shard_world: int = 1):
+        self.store = store
+        decay = [p for p in store.params if p.ndim >= 2]
+        rest = [p for p in store.params if p.ndim < 2]
+        groups = [g for g in ({"params": decay, "weight_decay": weight_decay},
+                              {"params": rest, "weight_decay": 0.0}) if g["params"]]
+        super().__init__(groups, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        self.shard_rank, self.shard_world = shard_rank, shard_world
+        n = store.total // shard_world if shard_world > 1 else store.total
+        dev = store.device
+        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.ctl = torch.tensor([1.0, 1.0], dtype=torch.float32, device=dev)
+        self.steps = 0
+        self._step_t = torch.zeros((), dtype=torch.float32)
+        if shard_world == 1:
+            for p in store.params:
+                lo = store._offset[p]
+                self.state[p] = {"step": self._step_t,
+                                 "exp_avg": self.exp_avg[lo:lo + p.numel()].view(p.shape),
+                                 "exp_avg_sq": self.exp_avg_sq[lo:lo + p.numel()].view(p.shape)}
+
+    def _segments(self, b: Bucket):
+        """Runs of equal weight-decay class inside a bucket: (offset, length, decay?)."""
+        runs = []
+        for off, n, dec in b.decay:
+            padded = _round_up(n, ALIGN)
+            if runs and runs[-1][2] == dec and runs[-1][0] + runs[-1][1] == off:
+                runs[-1] = (runs[-1][0], runs[-1][1] + padded, dec)
+            else:
+                runs.append((off, padded, dec))
+        return runs
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        st = self.store
+        self.steps += 1
+        self._step_t.fill_(self.steps)
+        lr = self.param_groups[0]["lr"]
+        b1, b2 = self.defaults["betas"]
+        eps = self.defaults["eps"]
+        wd = max(float(g["weight_decay"]) for g in self.param_groups)
+        bc1, bc2 = 1 - b1 ** self.steps, 1 - b2 ** self.steps
+        native = st.device.type == "cuda" and ops.available()
+        C = ops.require() if native else None
+        for b in st.buckets:
+            for off, n, dec in self._segments(b):
+                lo = b.start + off
+                p, g = st.master[lo:lo + n], st.grad[lo:lo + n]
+                m, v = self.exp_avg[lo:lo + n], self.exp_avg_sq[lo:lo + n]
+                sh = st.shadow[lo:lo + n]
+                w = wd if dec else 0.0
+                if native:
+                    C.adamw_flat(p, g, m, v, sh, lr, b1, b2, eps, w, bc1, bc2, self.ctl)
+                else:
+                    _adamw_reference(p, g, m, v, sh, lr, b1, b2, eps, w, bc1, bc2, self.ctl)
+        return None
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        self.store.zero_grad()
+
+    def load_state_dict(self, state_dict) -> None:
+        """Loads like ``torch.optim.AdamW`` and then moves the moments back into the flat buffers
+        (``Optimizer.load_state_dict`` replaces the state tensors by copies)."""
+        super().load_state_dict(state_dict)
+        if self.shard_world != 1:
+            return
+        steps = 0
+        with torch.no_grad():
+            for p in self.store.params:
+                st = self.state.get(p)
+                if not st:
+                    continue
+                lo, n = self.store._offset[p], p.numel()
+                for key, flat in (("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
+                    view = flat[lo:lo + n].view(p.shape)
+                    if key in st and st[key].data_ptr() != view.data_ptr():
+                        view.copy_(st[key])
+                    st[key] = view
+                if "step" in st:
+                    steps = max(steps, int(float(st["step"])))
+                st["step"] = self._step_t
+        self.steps = steps
+        self._step_t.fill_(steps)
+
+
+def _adamw_reference(p, g, m, v, shadow, lr, b1, b2, eps, wd, bc1, bc2, ctl):
+    """PyTorch statement of the fused kernel (CPU path and test oracle)."""
+    clip, ok = ctl[0], ctl[1]
+    if float(ok) < 0.5:
+        return
+    gg = g * clip
+    m.lerp_(gg, 1 - b1)
+    v.mul_(b2).addcmul_(gg, gg, value=1 - b2)
+    denom = v.sqrt() / math.sqrt(bc2) + eps
+    p.mul_(1 - lr * wd).addcdiv_(m, denom, value=-lr / bc1)
+    shadow.copy_(p)
+
+
+class BucketReducer:
+    """Averages gradient buckets over the data-parallel group on a side stream.
+
+    ``launch(bucket)`` is called when a block has finished its last backward of the step (module
+    backward hook): the reduction of that bucket then overlaps the backward of the earlier blocks.
+    ``finish()`` makes the compute stream wait for all of them. Uses NCCL/Gloo ``all_reduce``; the
+    peer-memory kernels of :mod:`forgeminds_b200.parallel.symm` replace it when symmetric buffers
+    are available.
+    """
+
+    def __init__(self, store: FlatParamStore, group, world: int):
+        self.store, self.group, self.world = store, group, world
+        self.cuda = store.device.type == "cuda"
+        self.stream = torch.cuda.Stream(device=store.device) if self.cuda else None
+        self._launched: list = []
+        self.enabled = True
+
+    def launch(self, b: Bucket) -> None:
+        if not self.enabled or self.world <= 1:
+            return
+        view = self.store.bucket_view(self.store.grad, b)
+        if self.cuda:
+            self.stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.stream):
+                dist.all_reduce(view, op=dist.ReduceOp.AVG, group=self.group)
+        else:
+            dist.all_reduce(view, group=self.group)
+            view.div_(self.world)
+        self._launched.append(b.name)
+
+    def finish(self) -> None:
+        if self.cuda and self._launched:
+            torch.cuda.current_stream().wait_stream(self.stream)
+        done = set(self._launched)
+        self._launched.clear()
+        if self.enabled and self.world > 1:
+            for b in self.store.buckets:         # anything whose hook did not fire (unused parameters)
+                if b.name not in done:
+                    view = self.store.bucket_view(self.store.grad, b)
+                    if self.cuda:
+                        dist.all_reduce(view, op=dist.ReduceOp.AVG, group=self.group)
+                    else:
+                        dist.all_reduce(view, group=self.group)
+                        view.div_(self.world)
