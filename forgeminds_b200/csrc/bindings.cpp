@@ -18,6 +18,11 @@ int fmb_router_bwd(const float* probs, const int* idx, const float* weights, con
                    int k, cudaStream_t stream);
 int fmb_moe_plan(const int* idx, int* chunk_counts, int* region, int* meta, int* slot_of_entry, int* token_of_slot,
                  long long entries, int E, int k, int align, int cap, int mode, cudaStream_t stream);
+int fmb_moe_tile_groups(const int* region, int* tile_group, int n_tiles, int E, cudaStream_t stream);
+int fmb_gemm_bf16_grouped(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int a_mn, int b_mn,
+                          long long lda, long long ldb, long long ldd, long long ldc, int d_f32, int c_f32, float alpha,
+                          float beta, int mode, int n_groups, const int* tile_group, const int* region,
+                          long long group_stride_b, long long group_stride_d, int* status, cudaStream_t stream);
 int fmb_moe_combine_bwd(const void* dout, const void* ys, const int* slot_of_entry, const float* w, void* dys, float* dw,
                         long long entries, int k, int d, cudaStream_t stream);
 }
@@ -386,6 +391,55 @@ std::vector<Tensor> moe_combine_bwd(const Tensor& dout, const Tensor& ys, const 
   return {dys, dw};
 }
 
+// Row-grouped product: out[rows, N] = a[rows, K] @ B[group(row)]^T where `b` is [G, N, K] (b_mn=false)
+// or [G, K, N] (b_mn=true) and `tile_group[rows / 128]` names the group of each 128-row tile (-1: skip).
+void gemm_grouped_rows(const Tensor& a, const Tensor& b, Tensor& out, const Tensor& tile_group, bool b_mn,
+                       bool accumulate, const c10::optional<Tensor>& status) {
+  TORCH_CHECK(a.is_cuda() && a.dim() == 2 && b.dim() == 3 && out.dim() == 2 && a.stride(1) == 1 && b.is_contiguous() &&
+              out.stride(1) == 1 && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16);
+  const int64_t M = a.size(0), K = a.size(1), G = b.size(0);
+  const int64_t N = b_mn ? b.size(2) : b.size(1);
+  TORCH_CHECK((b_mn ? b.size(1) : b.size(2)) == K && out.size(0) == M && out.size(1) == N && M % 128 == 0);
+  TORCH_CHECK(tile_group.numel() >= M / 128 && tile_group.scalar_type() == at::kInt);
+  c10::cuda::CUDAGuard guard(a.device());
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  const bool f32 = out.scalar_type() == at::kFloat;
+  ok(fmb_gemm_bf16_grouped(a.data_ptr(), b.data_ptr(), out.data_ptr(), accumulate ? out.data_ptr() : nullptr,
+                           static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), 0, b_mn, a.stride(0),
+                           b.stride(1), out.stride(0), out.stride(0), f32, f32, 1.f, accumulate ? 1.f : 0.f, 1,
+                           static_cast<int>(G),
+                           tile_group.data_ptr<int>(), nullptr, b.stride(0), 0, st, cur_stream()), "gemm_grouped_rows");
+}
+
+// Per-group weight gradient: out[g] [M, N] (+)= a[rows_g, M]^T @ b[rows_g, N]; `region` is [G, 3] int32
+// {first row, used, padded rows}. `accumulate` adds to `out` (fp32) instead of overwriting it.
+void gemm_grouped_wgrad(const Tensor& a, const Tensor& b, Tensor& out, const Tensor& region, bool accumulate,
+                        const c10::optional<Tensor>& status) {
+  TORCH_CHECK(a.is_cuda() && a.dim() == 2 && b.dim() == 2 && out.dim() == 3 && out.is_contiguous() && a.stride(1) == 1 &&
+              b.stride(1) == 1 && a.size(0) == b.size(0) && a.scalar_type() == at::kBFloat16 &&
+              b.scalar_type() == at::kBFloat16);
+  const int64_t rows = a.size(0), M = a.size(1), N = b.size(1), G = out.size(0);
+  TORCH_CHECK(out.size(1) == M && out.size(2) == N && region.numel() >= 3 * G && region.scalar_type() == at::kInt);
+  c10::cuda::CUDAGuard guard(a.device());
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  const bool f32 = out.scalar_type() == at::kFloat;
+  if (!accumulate) out.zero_();           // groups without rows are skipped by the kernel
+  ok(fmb_gemm_bf16_grouped(a.data_ptr(), b.data_ptr(), out.data_ptr(), accumulate ? out.data_ptr() : nullptr,
+                           static_cast<int>(M), static_cast<int>(N), static_cast<int>(rows), 1, 1, a.stride(0),
+                           b.stride(0), out.stride(1), out.stride(1), f32, f32, 1.f, accumulate ? 1.f : 0.f, 2,
+                           static_cast<int>(G), nullptr, region.data_ptr<int>(), 0, out.stride(0), st, cur_stream()),
+     "gemm_grouped_wgrad");
+}
+
+Tensor moe_tile_groups(const Tensor& region, int64_t n_tiles) {
+  cuda_contig(region, "region");
+  c10::cuda::CUDAGuard guard(region.device());
+  Tensor tg = torch::empty({n_tiles}, region.options());
+  ok(fmb_moe_tile_groups(region.data_ptr<int>(), tg.data_ptr<int>(), static_cast<int>(n_tiles),
+                         static_cast<int>(region.numel() / 3), cur_stream()), "moe_tile_groups");
+  return tg;
+}
+
 #ifdef FMB_WITH_ATTENTION
 // q [B,T,Hq,hd], k/v [B,T,Hkv,hd] (rows may be views into one fused qkv buffer): returns (o, lse)
 std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale, bool causal,
@@ -451,6 +505,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("router_fwd", &router_fwd);
   m.def("router_bwd", &router_bwd);
   m.def("moe_plan", &moe_plan);
+  m.def("gemm_grouped_rows", &gemm_grouped_rows);
+  m.def("gemm_grouped_wgrad", &gemm_grouped_wgrad);
+  m.def("moe_tile_groups", &moe_tile_groups);
   m.def("moe_gather", &moe_gather);
   m.def("moe_combine", &moe_combine);
   m.def("moe_combine_bwd", &moe_combine_bwd);

@@ -16,6 +16,8 @@
 
 namespace fmb {
 
+constexpr int GEMM_BK_C = 64;
+
 struct GemmParams {
   int M, N;
   int tiles_m, tiles_n, splits;
@@ -28,7 +30,52 @@ struct GemmParams {
   float alpha, beta;
   const float* alpha_ptr;   // optional device scalar multiplied into alpha
   int* status;
+  // grouped modes (0 = plain)
+  //   1: rows of A/D are partitioned into groups; `tile_group[m_blk]` names the B matrix (z coordinate of
+  //      the 3-D B map) used by that row tile, or -1 for a tile that holds only padding (skipped).
+  //   2: one output matrix per group, reduced over that group's rows: `region[3g] = {first row, used,
+  //      padded rows}` gives the K range, `group_stride_d` the distance between output matrices.
+  int mode;
+  int n_groups;
+  const int* tile_group;
+  const int* region;
+  long long group_stride_d;
 };
+
+struct TileInfo {
+  int m_blk, n_blk, k0, k1, zb;
+  long long d_off;
+  bool valid;
+};
+
+__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
+  TileInfo t;
+  t.zb = 0;
+  t.d_off = 0;
+  t.valid = true;
+  if (p.mode == 2) {
+    const int per = p.tiles_m * p.tiles_n;
+    const int g = tile / per, mn = tile % per;
+    t.m_blk = mn % p.tiles_m;
+    t.n_blk = mn / p.tiles_m;
+    t.k0 = __ldg(p.region + 3 * g) / GEMM_BK_C;
+    t.k1 = t.k0 + __ldg(p.region + 3 * g + 2) / GEMM_BK_C;
+    t.d_off = static_cast<long long>(g) * p.group_stride_d;
+    t.valid = t.k1 > t.k0;
+    return t;
+  }
+  const int ks = tile % p.splits;
+  const int mn = tile / p.splits;
+  t.m_blk = mn % p.tiles_m;
+  t.n_blk = mn / p.tiles_m;
+  t.k0 = ks * p.kblocks_per_split;
+  t.k1 = min(p.kblocks_total, t.k0 + p.kblocks_per_split);
+  if (p.mode == 1) {
+    t.zb = __ldg(p.tile_group + t.m_blk);
+    t.valid = t.zb >= 0;
+  }
+  return t;
+}
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
@@ -90,7 +137,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_tiles = p.tiles_m * p.tiles_n * p.splits;
+  const int total_tiles = p.tiles_m * p.tiles_n * (p.mode == 2 ? p.n_groups : p.splits);
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
@@ -99,12 +146,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t armed = 0, armed_parity = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const int ks = tile % p.splits;
-        const int mn = tile / p.splits;
-        const int m_blk = mn % p.tiles_m;
-        const int n_blk = mn / p.tiles_m;
-        const int k0 = ks * p.kblocks_per_split;
-        const int k1 = min(p.kblocks_total, k0 + p.kblocks_per_split);
+        const TileInfo ti = decode_tile(p, tile);
+        if (!ti.valid) continue;
+        const int m_blk = ti.m_blk, n_blk = ti.n_blk, k0 = ti.k0, k1 = ti.k1;
         for (int kb = k0; kb < k1; ++kb) {
           if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, ab, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t sA = smem_base + stage * L::STAGE_BYTES;
@@ -120,11 +164,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tma_load_2d(sA + j * (BK * 128), &tmA, full_bar(stage), m_blk * BM + j * 64, kb * BK);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sB, &tmB, full_bar(stage), kb * BK, n_blk * BN);
+            tma_load_3d(sB, &tmB, full_bar(stage), kb * BK, n_blk * BN, ti.zb);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sB + j * (BK * 128), &tmB, full_bar(stage), n_blk * BN + j * 64, kb * BK);
+              tma_load_3d(sB + j * (BK * 128), &tmB, full_bar(stage), n_blk * BN + j * 64, kb * BK, ti.zb);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -148,9 +192,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const int ks = tile % p.splits;
-        const int k0 = ks * p.kblocks_per_split;
-        const int k1 = min(p.kblocks_total, k0 + p.kblocks_per_split);
+        const TileInfo ti = decode_tile(p, tile);
+        if (!ti.valid) continue;
+        const int k0 = ti.k0, k1 = ti.k1;
         if (!mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, ab, p.status, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -181,9 +225,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const float alpha = p.alpha_ptr != nullptr ? p.alpha * __ldg(p.alpha_ptr) : p.alpha;
     const float beta = p.beta;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      const int mn = tile / p.splits;
-      const int m_blk = mn % p.tiles_m;
-      const int n_blk = mn / p.tiles_m;
+      const TileInfo ti = decode_tile(p, tile);
+      if (!ti.valid) continue;
+      const int m_blk = ti.m_blk, n_blk = ti.n_blk;
       if (!mbar_wait_bounded(tfull_bar(acc), acc_phase, ab, p.status, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const int row = m_blk * BM + quarter * 32 + lane;
@@ -203,7 +247,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const bool full = col0 + 32 <= p.N;
         if (p.C != nullptr && beta != 0.f) {
           if (p.c_f32) {
-            const float* cp = reinterpret_cast<const float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+            const float* cp = reinterpret_cast<const float*>(p.C) + ti.d_off + static_cast<long long>(row) * p.ldc + col0;
             if (full) {
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
@@ -216,7 +260,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           } else {
             const __nv_bfloat16* cp =
-                reinterpret_cast<const __nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+                reinterpret_cast<const __nv_bfloat16*>(p.C) + ti.d_off + static_cast<long long>(row) * p.ldc + col0;
             if (full) {
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
@@ -233,7 +277,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
         if (p.d_f32) {
-          float* dp = reinterpret_cast<float*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+          float* dp = reinterpret_cast<float*>(p.D) + ti.d_off + static_cast<long long>(row) * p.ldd + col0;
           if (p.atomic) {
             if (full) {
 #pragma unroll
@@ -249,7 +293,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             _Pragma("unroll") for (int i = 0; i < 32; ++i) if (col0 + i < p.N) dp[i] = v[i];
           }
         } else {
-          __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+          __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + ti.d_off + static_cast<long long>(row) * p.ldd + col0;
           if (full) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -304,12 +348,24 @@ static double wave_eff(long long work, int sms) {
 
 }  // namespace fmb
 
-extern "C" int fmb_gemm_bf16(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int a_mn,
-                             int b_mn, long long lda, long long ldb, long long ldd, long long ldc, int d_f32,
-                             int c_f32, float alpha, float beta, const float* alpha_ptr, int allow_split, int* status,
-                             int force_bn, cudaStream_t stream) {
+namespace fmb {
+struct GroupSpec {
+  int mode = 0;                  // 0 plain, 1 row groups (B per group), 2 one output per group (K ranges)
+  int n_groups = 1;
+  const int* tile_group = nullptr;
+  const int* region = nullptr;
+  long long group_stride_b = 0;  // elements between the B matrices of consecutive groups (mode 1)
+  long long group_stride_d = 0;  // elements between the D (and C) matrices of consecutive groups (mode 2)
+};
+}  // namespace fmb
+
+static int run_gemm(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int a_mn,
+                    int b_mn, long long lda, long long ldb, long long ldd, long long ldc, int d_f32,
+                    int c_f32, float alpha, float beta, const float* alpha_ptr, int allow_split, int* status,
+                    int force_bn, const fmb::GroupSpec& gs, cudaStream_t stream) {
   using namespace fmb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (gs.mode != 0) allow_split = 0;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(D) & 15) || (ldd % (d_f32 ? 4 : 8)))
     return -2;   // TMA needs 16-byte aligned bases and pitches; the vector epilogue needs an aligned D
@@ -354,6 +410,11 @@ extern "C" int fmb_gemm_bf16(const void* A, const void* B, void* D, const void* 
   p.alpha = alpha; p.beta = beta;
   p.alpha_ptr = alpha_ptr;
   p.status = status;
+  p.mode = gs.mode;
+  p.n_groups = gs.n_groups;
+  p.tile_group = gs.tile_group;
+  p.region = gs.region;
+  p.group_stride_d = gs.group_stride_d;
   if (splits > 1) {
     // Every split adds alpha*partial into D, which already holds the C term (C == D) or zeros.
     if (C == D && beta == 1.f) { p.C = nullptr; }
@@ -365,11 +426,22 @@ extern "C" int fmb_gemm_bf16(const void* A, const void* B, void* D, const void* 
   bool ok = true;
   if (!a_mn) ok = ok && make_tmap_2d(&ta, A, M, K, lda, GEMM_BM, GEMM_BK, 2, TmapSwizzle::B128);
   else       ok = ok && make_tmap_2d(&ta, A, K, M, lda, GEMM_BK, 64, 2, TmapSwizzle::B128);
-  if (!b_mn) ok = ok && make_tmap_2d(&tb, B, N, K, ldb, best_bn, GEMM_BK, 2, TmapSwizzle::B128);
-  else       ok = ok && make_tmap_2d(&tb, B, K, N, ldb, GEMM_BK, 64, 2, TmapSwizzle::B128);
+  {
+    // B is always described by a 3-D map (inner, rows, group); plain products have one group.
+    const int nb = gs.mode == 1 ? gs.n_groups : 1;
+    const uint64_t gstride = gs.mode == 1 ? static_cast<uint64_t>(gs.group_stride_b)
+                                          : static_cast<uint64_t>(b_mn ? K : N) * static_cast<uint64_t>(ldb);
+    uint64_t dims[3], strides[3];
+    uint32_t box[3];
+    if (!b_mn) { dims[0] = K; dims[1] = N; box[0] = GEMM_BK; box[1] = best_bn; }
+    else       { dims[0] = N; dims[1] = K; box[0] = 64; box[1] = GEMM_BK; }
+    dims[2] = nb; box[2] = 1;
+    strides[0] = 2; strides[1] = static_cast<uint64_t>(ldb) * 2; strides[2] = gstride * 2;
+    ok = ok && make_tmap_nd(&tb, B, 3, dims, strides, box, 2, TmapSwizzle::B128);
+  }
   if (!ok) return -5;
 
-  const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.splits;
+  const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * (gs.mode == 2 ? gs.n_groups : p.splits);
   const int grid = static_cast<int>(total < sms ? total : sms);
   cudaError_t e;
 #define FMB_DISPATCH(BN, ST)                                                                   \
@@ -380,4 +452,35 @@ extern "C" int fmb_gemm_bf16(const void* A, const void* B, void* D, const void* 
   if (best_bn == 256) { FMB_DISPATCH(256, 4) } else { FMB_DISPATCH(128, 6) }
 #undef FMB_DISPATCH
   return e == cudaSuccess ? 0 : -10 - static_cast<int>(e);
+}
+
+extern "C" int fmb_gemm_bf16(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int a_mn,
+                             int b_mn, long long lda, long long ldb, long long ldd, long long ldc, int d_f32,
+                             int c_f32, float alpha, float beta, const float* alpha_ptr, int allow_split, int* status,
+                             int force_bn, cudaStream_t stream) {
+  fmb::GroupSpec gs;
+  return run_gemm(A, B, D, C, M, N, K, a_mn, b_mn, lda, ldb, ldd, ldc, d_f32, c_f32, alpha, beta, alpha_ptr,
+                  allow_split, status, force_bn, gs, stream);
+}
+
+// Grouped products over rows that are partitioned into expert regions (see GemmParams::mode).
+//   mode 1: D[rows, N] = A[rows, K] * B[g(row)]^T          (M = padded rows; K = reduction)
+//   mode 2: D[g][M, N] (+)= A[rows_g, M]^T * B[rows_g, N]    (K = total padded rows; operands MN-major)
+extern "C" int fmb_gemm_bf16_grouped(const void* A, const void* B, void* D, const void* C, int M, int N, int K,
+                                     int a_mn, int b_mn, long long lda, long long ldb, long long ldd, long long ldc,
+                                     int d_f32, int c_f32, float alpha, float beta, int mode, int n_groups,
+                                     const int* tile_group, const int* region, long long group_stride_b,
+                                     long long group_stride_d, int* status, cudaStream_t stream) {
+  fmb::GroupSpec gs;
+  gs.mode = mode;
+  gs.n_groups = n_groups;
+  gs.tile_group = tile_group;
+  gs.region = region;
+  gs.group_stride_b = group_stride_b;
+  gs.group_stride_d = group_stride_d;
+  if (mode != 1 && mode != 2) return -2;
+  if (mode == 1 && tile_group == nullptr) return -2;
+  if (mode == 2 && (region == nullptr || !a_mn || !b_mn)) return -2;
+  return run_gemm(A, B, D, C, M, N, K, a_mn, b_mn, lda, ldb, ldd, ldc, d_f32, c_f32, alpha, beta, nullptr, 0,
+                  status, 0, gs, stream);
 }

@@ -328,6 +328,19 @@ __global__ void __launch_bounds__(256) moe_combine_bwd_kernel(const uint4* __res
   if (lane == 0 && dw != nullptr) dw[en] = dot;
 }
 
+// tile_group[t] = expert whose region holds row tile t (128 rows) and has live rows there, else -1
+__global__ void tile_group_kernel(const int* __restrict__ region, int* __restrict__ tile_group, int n_tiles, int E) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_tiles) return;
+  const int row = t * 128;
+  int g = -1;
+  for (int e = 0; e < E; ++e) {
+    const int start = region[3 * e], used = region[3 * e + 1];
+    if (row >= start && row < start + used) { g = e; break; }
+  }
+  tile_group[t] = g;
+}
+
 static int grid_cap(long long items, int threads) {
   long long b = (items + threads - 1) / threads;
   const long long cap = static_cast<long long>(sm_count()) * 16;
@@ -408,5 +421,11 @@ extern "C" int fmb_moe_combine_bwd(const void* dout, const void* ys, const int* 
   if (d % 8) return -2;
   const unsigned blocks = static_cast<unsigned>((entries * 32 + 255) / 256);
   moe_combine_bwd_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(dout), static_cast<const uint4*>(ys), slot_of_entry, w, static_cast<uint4*>(dys), dw, entries, k, d / 8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int fmb_moe_tile_groups(const int* region, int* tile_group, int n_tiles, int E, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  tile_group_kernel<<<(n_tiles + 127) / 128, 128, 0, stream>>>(region, tile_group, n_tiles, E);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -190,6 +190,8 @@ class MoE(nn.Module):
     def _use_native(self, flat) -> bool:
         if not (flat.is_cuda and flat.dtype == torch.bfloat16) or self.experts.offload:
             return False
+        if self.ep_size > 1 and self.ep_engine is None:
+            return False
         from . import ops
         return ops.available() and self.dim % 64 == 0 and self.hidden % 64 == 0 and self.n_experts <= 256 \
             and self.top_k <= 8

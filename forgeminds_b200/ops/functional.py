@@ -64,6 +64,14 @@ def _rows(x):
     return x.reshape(-1, x.shape[-1])
 
 
+def _gemm_like(x, x2, w, **kw):
+    """``x2 @ w.T`` written into a freshly allocated tensor shaped like ``x`` with the last dim
+    replaced (the autograd output is then an owning tensor, not a view, and may be updated in place)."""
+    y = torch.empty((*x.shape[:-1], w.shape[0]), dtype=BF16, device=x.device)
+    gemm(x2, w, out=y.view(-1, w.shape[0]), **kw)
+    return y
+
+
 # ------------------------------------------------------------------------------ linear
 class _Linear(torch.autograd.Function):
     @staticmethod
@@ -77,12 +85,12 @@ class _Linear(torch.autograd.Function):
             res2 = _rows(residual)
             if not res2.is_contiguous():
                 res2 = res2.contiguous()
-        y = gemm(x2, w, c=res2, beta=1.0 if res2 is not None else 0.0)
+        y = _gemm_like(x, x2, w, c=res2, beta=1.0 if res2 is not None else 0.0)
         ctx.save_for_backward(x2, w)
         ctx.weight = weight
         ctx.x_shape = x.shape
         ctx.has_res = residual is not None
-        return y.view(*x.shape[:-1], w.shape[0])
+        return y
 
     @staticmethod
     @once_differentiable
@@ -168,11 +176,11 @@ class _LinearMulti(torch.autograd.Function):
         x2 = _rows(x)
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        y = gemm(x2, w)
+        y = _gemm_like(x, x2, w)
         ctx.save_for_backward(x2, w)
         ctx.weights = weights
         ctx.x_shape = x.shape
-        return y.view(*x.shape[:-1], w.shape[0])
+        return y
 
     @staticmethod
     @once_differentiable
@@ -245,10 +253,10 @@ class _NormLinearMulti(torch.autograd.Function):
             nw = nw.to(x2.dtype)
         nw = nw.contiguous()
         h, rstd = C.rmsnorm_fwd(x2, nw, eps)
-        y = gemm(h, w)
+        y = _gemm_like(x, h, w)
         ctx.save_for_backward(x2, nw, rstd, w)
         ctx.weights, ctx.eps, ctx.x_shape, ctx.nw_dtype = weights, eps, x.shape, norm_w.dtype
-        return y.view(*x.shape[:-1], w.shape[0])
+        return y
 
     @staticmethod
     @once_differentiable
@@ -292,10 +300,10 @@ class _SwiGLULinear(torch.autograd.Function):
             res2 = _rows(residual)
             if not res2.is_contiguous():
                 res2 = res2.contiguous()
-        y = gemm(act, w, c=res2, beta=1.0 if res2 is not None else 0.0)
+        y = _gemm_like(gu, act, w, c=res2, beta=1.0 if res2 is not None else 0.0)
         ctx.save_for_backward(g2, w)
         ctx.weight, ctx.gu_shape, ctx.has_res = weight, gu.shape, residual is not None
-        return y.view(*gu.shape[:-1], w.shape[0])
+        return y
 
     @staticmethod
     @once_differentiable

@@ -192,7 +192,7 @@ class Trainer:
     def _flat_ok(self, oc, cfg) -> bool:
         tc, pc = cfg.train, cfg.parallel
         return not (oc.optimizer or cfg.quant.optimizer_8bit or pc.fsdp_cpu_offload or tc.compile) \
-            and cfg.quant.mode in ("none", "fp8", "int8") and pc.tp == 1
+            and cfg.quant.mode in ("none", "fp8", "int8") and pc.tp == 1 and pc.ep == 1
 
     def _setup_native(self, model, tc, pc, dp: bool) -> None:
         from .parallel.flat import BucketReducer, FlatAdamW, FlatParamStore

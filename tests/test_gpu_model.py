@@ -74,3 +74,41 @@ def test_native_step_has_one_host_sync(cuda_status):
             tr.train_step()
     tr.close()
     assert c.own <= 3, c.report()
+
+
+def test_moe_native_matches_torch_path(cuda_status):
+    import forgeminds_b200 as fm
+    from forgeminds_b200.moe import MoE
+    torch.manual_seed(0)
+    moe = MoE(256, 512, 8, 2, grouped_mm=True).cuda()
+    ref = copy.deepcopy(moe)
+    x = (torch.randn(1000, 256, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    xr = x.detach().clone().requires_grad_()
+    out = moe(x)                               # bf16 CUDA input -> kernels
+    assert moe.last_aux is not None
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        want = ref._dispatch_torch(xr, *ref.router(xr)[:2])
+        _, _, aux_r, z_r = ref.router(xr)
+    assert (out.float() - want.float()).abs().max() < 0.05
+    assert abs(moe.last_aux.item() - (ref.aux_coef * aux_r + ref.z_coef * z_r).item()) < 2e-3
+    g = torch.randn_like(out)
+    (out.float() * g.float()).sum().backward()
+    (want.float() * g.float()).sum().backward()
+    assert (x.grad.float() - xr.grad.float()).norm() / xr.grad.float().norm() < 0.08
+    for name in ("w1", "w3", "w2"):
+        a, b = getattr(moe.experts, name).grad.float(), getattr(ref.experts, name).grad.float()
+        assert (a - b).norm() / b.norm() < 0.08, name
+
+
+def test_moe_capacity_drops_overflow(cuda_status):
+    from forgeminds_b200.moe import MoE
+    torch.manual_seed(1)
+    moe = MoE(128, 256, 4, 2, grouped_mm=True, capacity_factor=1.0).cuda()
+    ref = copy.deepcopy(moe)
+    ref.capacity = lambda n: (moe.capacity(n) + 127) // 128 * 128       # regions are whole 128-row tiles
+    x = (torch.randn(2048, 128, device="cuda")).to(torch.bfloat16)
+    out = moe(x)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        w, idx, _, _ = ref.router(x)
+        want = ref._dispatch_torch(x, w, idx)
+    assert (out.float() - want.float()).abs().max() < 0.06
