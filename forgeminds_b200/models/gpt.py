@@ -94,7 +94,7 @@ def _native_ok(x: torch.Tensor, flag: Optional[bool]) -> bool:
     if flag is False or not x.is_cuda:
         return False
     bf16 = x.dtype == torch.bfloat16 or (torch.is_autocast_enabled() and
-                                         torch.get_autocast_gpu_dtype() == torch.bfloat16)
+                                         torch.get_autocast_dtype("cuda") == torch.bfloat16)
     if not bf16:
         return False
     from .. import ops

@@ -121,9 +121,14 @@ def linear(x, weight, residual=None):
 
 def _adjacent(views) -> bool:
     """True when the tensors are contiguous row blocks lying back to back in one storage."""
-    nxt = None
+    nxt = base = None
     for v in views:
         if v is None or not v.is_contiguous():
+            return False
+        store = v.untyped_storage().data_ptr()
+        if base is None:
+            base = store
+        if store != base:                  # neighbours by accident of the allocator do not count
             return False
         if nxt is not None and v.data_ptr() != nxt:
             return False

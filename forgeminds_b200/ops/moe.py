@@ -145,7 +145,11 @@ def moe_forward_native(moe, x):
         if moe.ep_engine is None:
             raise RuntimeError("expert parallelism on the native path needs parallel.ep.attach(model, ctx)")
         return moe.ep_engine.forward(moe, x)
-    logits = linear(x, moe.router.gate.weight)
+    gate = moe.router.gate.weight
+    if gate.shape[0] % 8 == 0:
+        logits = linear(x, gate)
+    else:       # the GEMM epilogue stores 16-byte vectors: an odd expert count takes the library matmul
+        logits = torch.nn.functional.linear(x, gate.to(x.dtype))
     route_w, idx, aux, _counts = _Route.apply(logits, moe.top_k, moe.aux_coef, moe.z_coef)
     moe.last_aux = aux
     slot_of, token_of, region, tile_group = plan(idx, moe.n_experts, moe.capacity(x.shape[0]))
