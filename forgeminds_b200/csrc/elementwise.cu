@@ -741,3 +741,41 @@ extern "C" int fmb_topk(const void* x, void* values, long long* indices, long lo
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
   });
 }
+
+// ------------------------------------------------------------------ allocation-free RMSNorm backward
+// See fmb_noalloc.h for who this is for and for the rules of use. The scratch for the per-block
+// weight-gradient partial sums is this file-scope device array. Host code must not pass the symbol
+// itself to a kernel: in host code the name is only a handle. Its device address is fetched once per
+// device with cudaGetSymbolAddress and that pointer is what the launcher receives.
+#include "fmb_noalloc.h"
+#include <cstdio>
+
+static __device__ __align__(256) float g_noalloc_scratch[FMB_NOALLOC_MAX_D * FMB_NOALLOC_MAX_BLOCKS];
+
+extern "C" int fmb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                                       float* dw, long long rows, int d, int dtype, int w_dtype, cudaStream_t stream) {
+  static float* scratch_of_device[64] = {nullptr};
+  if (rows <= 0) return 0;
+  const int nblocks = fmb_rmsnorm_bwd_blocks(rows, d);
+  if (d > FMB_NOALLOC_MAX_D || nblocks > FMB_NOALLOC_MAX_BLOCKS ||
+      static_cast<long long>(nblocks) * d > static_cast<long long>(FMB_NOALLOC_MAX_D) * FMB_NOALLOC_MAX_BLOCKS) {
+    std::fprintf(stderr, "fmb_rmsnorm_bwd_noalloc: row width %d (x %d blocks) exceeds the built-in scratch "
+                         "(max width %d); use fmb_rmsnorm_bwd with your own buffer\n", d, nblocks, FMB_NOALLOC_MAX_D);
+    return FMB_NOALLOC_TOO_LARGE;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FMB_NOALLOC_SETUP_FAILED;
+  if (scratch_of_device[dev] == nullptr) {
+    // first call on this device (it is the current one): resolve the array's device address
+    float* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      std::fprintf(stderr, "fmb_rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+      return FMB_NOALLOC_SETUP_FAILED;
+    }
+    scratch_of_device[dev] = ptr;
+  }
+  // every block writes its whole row of partial sums before the column sum reads it: nothing to clear
+  return fmb_rmsnorm_bwd(dy, x, w, rstd, nullptr, dx, scratch_of_device[dev], dw, 0, rows, d, dtype, w_dtype, nblocks,
+                         stream);
+}
