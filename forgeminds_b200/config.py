@@ -36,7 +36,7 @@ class ParallelConfig:
     # ---- additions of this library
     fused_comm: bool = True            # use the peer-memory kernels (falls back to torch.distributed when unavailable)
     fsdp_resident_bytes: int = 64 << 30  # keep gathered bf16 weights resident when the model is smaller than this
-    comm_timeout_ms: int = 2000        # bound of every device-side wait on a peer flag
+    comm_timeout_ms: int = 10000       # bound of every device-side wait on a peer flag
 
 
 @dataclass

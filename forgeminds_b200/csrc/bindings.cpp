@@ -313,6 +313,126 @@ void ns_axpby(const Tensor& x, const Tensor& y, Tensor& out, double a, double b)
                   dt(x), cur_stream()), "ns_axpby");
 }
 
+// ---- collectives over peer memory. Pointer tables are Python lists of ints (one device address per rank).
+struct PtrTable {
+  const void* p[FMB_MAX_PEERS];
+  int world;
+  explicit PtrTable(const std::vector<int64_t>& v) : world(static_cast<int>(v.size())) {
+    TORCH_CHECK(world >= 1 && world <= FMB_MAX_PEERS, "peer table: 1..", FMB_MAX_PEERS, " ranks, got ", v.size());
+    for (int r = 0; r < FMB_MAX_PEERS; ++r) p[r] = r < world ? reinterpret_cast<const void*>(v[r]) : nullptr;
+  }
+};
+
+unsigned long long to_ns(double ms) { return static_cast<unsigned long long>(ms * 1e6); }
+
+void comm_rs_reduce(const std::vector<int64_t>& grad_ptrs, int64_t lo, int64_t n, double scale, Tensor& partial,
+                    const std::vector<int64_t>& flag_ptrs, int64_t slot, int64_t epoch, int64_t rank, double timeout_ms,
+                    Tensor& status) {
+  PtrTable g(grad_ptrs), f(flag_ptrs);
+  TORCH_CHECK(g.world == f.world && partial.is_cuda() && partial.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(partial.device());
+  ok(fmb_comm_rs_reduce(g.p, lo, n, static_cast<float>(scale), partial.data_ptr<float>(),
+                        static_cast<int>(partial.numel()), f.p, static_cast<int>(slot), static_cast<unsigned>(epoch),
+                        static_cast<int>(rank), g.world, to_ns(timeout_ms), status.data_ptr<int>(), cur_stream()),
+     "comm_rs_reduce");
+}
+
+void comm_step_reduce(const Tensor& partial, const c10::optional<Tensor>& extra_sq, const c10::optional<Tensor>& loss,
+                      const std::vector<int64_t>& xchg_ptrs, const std::vector<int64_t>& flag_ptrs, int64_t slot,
+                      int64_t epoch, int64_t rank, double max_norm, bool skip_nonfinite, Tensor& stats, Tensor& ctl,
+                      double timeout_ms, Tensor& status) {
+  PtrTable x(xchg_ptrs), f(flag_ptrs);
+  TORCH_CHECK(x.world == f.world && partial.is_cuda() && partial.scalar_type() == at::kFloat);
+  TORCH_CHECK(stats.scalar_type() == at::kFloat && stats.numel() >= 3 && ctl.scalar_type() == at::kFloat &&
+              ctl.numel() >= 2);
+  if (loss.has_value() && loss->defined()) TORCH_CHECK(loss->scalar_type() == at::kFloat && loss->is_cuda());
+  c10::cuda::CUDAGuard guard(partial.device());
+  ok(fmb_comm_step_reduce(partial.data_ptr<float>(), static_cast<int>(partial.numel()),
+                          static_cast<const float*>(cptr(extra_sq)), static_cast<const float*>(cptr(loss)), x.p, f.p,
+                          static_cast<int>(slot), static_cast<unsigned>(epoch), static_cast<int>(rank), x.world,
+                          static_cast<float>(max_norm), skip_nonfinite ? 1 : 0, stats.data_ptr<float>(),
+                          ctl.data_ptr<float>(), to_ns(timeout_ms), status.data_ptr<int>(), cur_stream()),
+     "comm_step_reduce");
+}
+
+void comm_adamw_push(Tensor& master, const Tensor& grad, Tensor& m, Tensor& v, const std::vector<int64_t>& shadow_ptrs,
+                     const Tensor& off, const Tensor& soff, const Tensor& len, const Tensor& wd, double lr,
+                     double beta1, double beta2, double eps, double bc1, double bc2, const Tensor& ctl) {
+  PtrTable s(shadow_ptrs);
+  TORCH_CHECK(master.scalar_type() == at::kFloat && grad.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat &&
+              v.scalar_type() == at::kFloat, "adamw_push: fp32 state required");
+  TORCH_CHECK(off.scalar_type() == at::kLong && soff.scalar_type() == at::kLong && len.scalar_type() == at::kInt &&
+              wd.scalar_type() == at::kFloat && off.is_cuda() && soff.is_cuda() && len.is_cuda() && wd.is_cuda());
+  TORCH_CHECK(soff.numel() == off.numel() && len.numel() == off.numel() && wd.numel() == off.numel());
+  c10::cuda::CUDAGuard guard(master.device());
+  ok(fmb_comm_adamw_push(master.data_ptr<float>(), grad.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+                         s.p, s.world, reinterpret_cast<const long long*>(off.data_ptr<int64_t>()),
+                         reinterpret_cast<const long long*>(soff.data_ptr<int64_t>()), len.data_ptr<int>(),
+                         wd.data_ptr<float>(), static_cast<int>(off.numel()), static_cast<float>(lr),
+                         static_cast<float>(beta1), static_cast<float>(beta2), static_cast<float>(eps),
+                         static_cast<float>(bc1), static_cast<float>(bc2), ctl.data_ptr<float>(), cur_stream()),
+     "comm_adamw_push");
+}
+
+// Product with operands / output spread over the ranks (see fmb_gemm_bf16_peer). `a`, `b`, `d` are
+// this rank's tensors: a shard when the matching pointer list is non-empty, the whole matrix otherwise.
+void gemm_peer(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, double alpha, int64_t rank,
+               int64_t world, const std::vector<int64_t>& a_ptrs, const std::vector<int64_t>& b_ptrs,
+               const std::vector<int64_t>& d_ptrs, const Tensor& flags, int64_t a_slot, int64_t a_epoch,
+               int64_t b_slot, int64_t b_epoch, double timeout_ms, Tensor& status) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && d.is_cuda() && a.dim() == 2 && b.dim() == 2 && d.dim() == 2);
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm_peer: bf16 operands required");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && d.stride(1) == 1, "gemm_peer: innermost dimension must be contiguous");
+  TORCH_CHECK(world >= 1 && world <= FMB_MAX_PEERS);
+  const bool a_sh = !a_ptrs.empty(), b_sh = !b_ptrs.empty(), d_sh = !d_ptrs.empty();
+  TORCH_CHECK((!a_sh || static_cast<int64_t>(a_ptrs.size()) == world) && (!b_sh || static_cast<int64_t>(b_ptrs.size()) == world) &&
+              (!d_sh || static_cast<int64_t>(d_ptrs.size()) == world), "gemm_peer: one pointer per rank");
+  int64_t M = a_mn ? a.size(1) : a.size(0) * (a_sh ? world : 1);
+  int64_t K = a_mn ? a.size(0) * (a_sh ? world : 1) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  const int64_t Kb = b_mn ? b.size(0) * (b_sh ? world : 1) : b.size(1);
+  TORCH_CHECK(K == Kb, "gemm_peer: inner dimensions differ: ", K, " vs ", Kb);
+  TORCH_CHECK(d.size(1) == N && d.size(0) * (d_sh ? world : 1) == M, "gemm_peer: output shape mismatch");
+  const bool d_f32 = d.scalar_type() == at::kFloat;
+  TORCH_CHECK(d_f32 || d.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(flags.scalar_type() == at::kInt && flags.is_cuda());
+  const void* ap[FMB_MAX_PEERS];
+  const void* bp[FMB_MAX_PEERS];
+  void* dp[FMB_MAX_PEERS];
+  for (int r = 0; r < FMB_MAX_PEERS; ++r) {
+    ap[r] = a_sh && r < world ? reinterpret_cast<const void*>(a_ptrs[r]) : nullptr;
+    bp[r] = b_sh && r < world ? reinterpret_cast<const void*>(b_ptrs[r]) : nullptr;
+    dp[r] = d_sh && r < world ? reinterpret_cast<void*>(d_ptrs[r]) : nullptr;
+  }
+  c10::cuda::CUDAGuard guard(a.device());
+  ok(fmb_gemm_bf16_peer(a.data_ptr(), b.data_ptr(), d.data_ptr(), static_cast<int>(M), static_cast<int>(N),
+                        static_cast<int>(K), a_mn, b_mn, a.stride(0), b.stride(0), d.stride(0), d_f32,
+                        static_cast<float>(alpha), static_cast<int>(rank), static_cast<int>(world),
+                        a_sh ? ap : nullptr, a_sh ? static_cast<int>(a.size(0)) : 0, b_sh ? bp : nullptr,
+                        b_sh ? static_cast<int>(b.size(0)) : 0, d_sh ? dp : nullptr,
+                        d_sh ? static_cast<int>(d.size(0)) : 0,
+                        reinterpret_cast<const unsigned*>(flags.data_ptr<int>()), static_cast<int>(a_slot),
+                        static_cast<unsigned>(a_epoch), static_cast<int>(b_slot), static_cast<unsigned>(b_epoch),
+                        to_ns(timeout_ms), status.data_ptr<int>(), cur_stream()),
+     "gemm_bf16_peer");
+}
+
+// Post this rank's epoch on a flag slot of every rank (no wait): "my shard is ready".
+void comm_signal(const std::vector<int64_t>& flag_ptrs, int64_t slot, int64_t epoch, int64_t rank, Tensor& status) {
+  PtrTable f(flag_ptrs);
+  c10::cuda::CUDAGuard guard(status.device());
+  ok(fmb_comm_signal(f.p, static_cast<int>(slot), static_cast<unsigned>(epoch), static_cast<int>(rank), f.world,
+                     cur_stream()), "comm_signal");
+}
+
+void comm_barrier(const std::vector<int64_t>& flag_ptrs, int64_t slot, int64_t epoch, int64_t rank, double timeout_ms,
+                  Tensor& status) {
+  PtrTable f(flag_ptrs);
+  c10::cuda::CUDAGuard guard(status.device());
+  ok(fmb_comm_barrier(f.p, static_cast<int>(slot), static_cast<unsigned>(epoch), static_cast<int>(rank), f.world,
+                      to_ns(timeout_ms), status.data_ptr<int>(), cur_stream()), "comm_barrier");
+}
+
 // ---- router / MoE
 std::vector<Tensor> router_fwd(const Tensor& logits, int64_t k) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
@@ -500,6 +620,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sum_f32", &sum_f32);
   m.def("adamw_flat", &adamw_flat);
   m.def("sqnorm", &sqnorm);
+  m.def("comm_rs_reduce", &comm_rs_reduce);
+  m.def("comm_step_reduce", &comm_step_reduce);
+  m.def("comm_adamw_push", &comm_adamw_push);
+  m.def("comm_barrier", &comm_barrier);
+  m.def("comm_signal", &comm_signal);
+  m.def("gemm_peer", &gemm_peer);
+  m.def("comm_adam_chunk", []() { return fmb_comm_adam_chunk(); });
+  m.attr("MAX_PEERS") = FMB_MAX_PEERS;
   m.def("scale_cast", &scale_cast);
   m.def("ns_axpby", &ns_axpby);
   m.def("router_fwd", &router_fwd);

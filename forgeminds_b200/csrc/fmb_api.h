@@ -14,6 +14,8 @@ extern "C" {
 // dtype codes used across the API
 #define FMB_BF16 0
 #define FMB_F32 1
+// ranks of one NVSwitch domain that the peer-memory kernels address
+#define FMB_MAX_PEERS 8
 
 // ---- GEMM (gemm_sm100.cu)
 int fmb_gemm_bf16(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int a_mn, int b_mn,
@@ -86,6 +88,32 @@ int fmb_attn_bwd(const void* q, const void* k, const void* v, const void* o, con
                  void* dq, void* dk, void* dv, float* delta, float* dq_acc, int B, int T, int Hq, int Hkv, int hd,
                  long long q_stride_t, long long kv_stride_t, long long o_stride_t, long long dq_stride_t,
                  long long dkv_stride_t, float scale, int causal, int* status, cudaStream_t stream);
+
+// ---- collectives over peer memory, fused with what follows them (comm.cu)
+// `*_ptrs` are HOST arrays of `world` device pointers: the same symmetric buffer as mapped for each
+// rank. Flags are uint32 epochs, FMB_MAX_PEERS per slot, zero before first use; `epoch` must grow by
+// one per use of a slot on every rank. A wait that exceeds `timeout_ns` sets *status to ERR_WAIT_PEER.
+int fmb_comm_rs_reduce(const void* const* grad_ptrs, long long lo, long long n, float scale, float* partial,
+                       int n_partial, const void* const* flag_ptrs, int slot, unsigned epoch, int rank, int world,
+                       unsigned long long timeout_ns, int* status, cudaStream_t stream);
+int fmb_comm_step_reduce(const float* partial, int n_partial, const float* extra_sq, const float* loss,
+                         const void* const* xchg_ptrs, const void* const* flag_ptrs, int slot, unsigned epoch,
+                         int rank, int world, float max_norm, int skip_nonfinite, float* stats, float* ctl,
+                         unsigned long long timeout_ns, int* status, cudaStream_t stream);
+int fmb_comm_adamw_push(float* master, const float* grad, float* m, float* v, const void* const* shadow_ptrs,
+                        int world, const long long* off, const long long* soff, const int* len, const float* wd,
+                        int n_chunks, float lr, float beta1, float beta2, float eps, float bc1, float bc2,
+                        const float* ctl, cudaStream_t stream);
+int fmb_comm_adam_chunk(void);
+int fmb_comm_signal(const void* const* flag_ptrs, int slot, unsigned epoch, int rank, int world, cudaStream_t stream);
+// Product whose operands / output are spread over the ranks (gemm_sm100.cu): see the comment at the definition.
+int fmb_gemm_bf16_peer(const void* A, const void* B, void* D, int M, int N, int K, int a_mn, int b_mn, long long lda,
+                       long long ldb, long long ldd, int d_f32, float alpha, int rank, int world,
+                       const void* const* a_ptrs, int a_rows_per_src, const void* const* b_ptrs, int b_rows_per_src,
+                       void* const* d_ptrs, int d_rows_per_rank, const unsigned* flags, int a_slot, unsigned a_epoch,
+                       int b_slot, unsigned b_epoch, unsigned long long timeout_ns, int* status, cudaStream_t stream);
+int fmb_comm_barrier(const void* const* flag_ptrs, int slot, unsigned epoch, int rank, int world,
+                     unsigned long long timeout_ns, int* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

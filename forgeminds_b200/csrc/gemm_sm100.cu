@@ -11,6 +11,7 @@
 // without a transpose pass. Split-K (fp32 atomic accumulation) fills the machine when the output
 // has fewer tiles than SMs, which is the usual case for weight gradients.
 #include "ptx_sm100.cuh"
+#include "peer.cuh"
 #include "tensormap.h"
 #include "fmb_api.h"
 
@@ -40,6 +41,29 @@ struct GemmParams {
   const int* tile_group;
   const int* region;
   long long group_stride_d;
+  // peer modes (PEER instantiations only). An operand whose rows (the y coordinate of its TMA map:
+  // the M rows of a K-major A, the reduction rows of an MN-major A or B) are spread over the ranks
+  // is read shard by shard through one tensor map per rank ("all-gather fused into the product");
+  // `*_rows_per_src` is the shard height (0 = operand is local). Before the first load from rank r
+  // the producer waits for flags[slot * MAX_PEERS + r] to reach `epoch` (slot < 0: no wait).
+  // With `d_rows_per_rank` > 0 the output rows belong to the rank that owns them and every rank
+  // adds its partial product into the owner's fp32 buffer ("reduce-scatter fused into the epilogue").
+  int rank, world;
+  int a_rows_per_src, b_rows_per_src;
+  const uint32_t* flags;
+  int a_slot, b_slot;
+  uint32_t a_epoch, b_epoch;
+  unsigned long long timeout_ns;
+  int d_rows_per_rank;
+  void* d_peer[FMB_MAX_PEERS];
+  int rot_m;                // row tiles are visited starting from this one (own shard first / remote first)
+  int rot_k;                // reduction blocks are visited starting from this one (own shard first)
+};
+
+// One tensor map per source rank (PEER) or a single one.
+template <bool PEER>
+struct MapSet {
+  CUtensorMap m[PEER ? FMB_MAX_PEERS : 1];
 };
 
 struct TileInfo {
@@ -67,6 +91,7 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
   const int ks = tile % p.splits;
   const int mn = tile / p.splits;
   t.m_blk = mn % p.tiles_m;
+  if (p.rot_m) t.m_blk = (t.m_blk + p.rot_m) % p.tiles_m;
   t.n_blk = mn / p.tiles_m;
   t.k0 = ks * p.kblocks_per_split;
   t.k1 = min(p.kblocks_total, t.k0 + p.kblocks_per_split);
@@ -95,9 +120,9 @@ __device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, flo
                : "memory");
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool PEER>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant__ MapSet<PEER> tmB, GemmParams p) {
   using L = GemmSmem<BN, STAGES>;
   constexpr int BM = GEMM_BM, BK = GEMM_BK;
   extern __shared__ uint8_t smem_raw[];
@@ -125,8 +150,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     ab->flag = 0;
     mbar_fence_init();
-    tma_prefetch_desc(&tmA);
-    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmA.m[0]);
+    tma_prefetch_desc(&tmB.m[0]);
   }
   if (warp == 1) {
     tmem_alloc<2 * BN>(smem_u32(tmem_slot));
@@ -144,31 +169,63 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       uint32_t armed = 0, armed_parity = 0;
+      uint32_t a_ready = 0, b_ready = 0;        // peers whose shard is known to be complete
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const TileInfo ti = decode_tile(p, tile);
         if (!ti.valid) continue;
         const int m_blk = ti.m_blk, n_blk = ti.n_blk, k0 = ti.k0, k1 = ti.k1;
-        for (int kb = k0; kb < k1; ++kb) {
+        for (int kq = k0; kq < k1; ++kq) {
+          int kb = kq;
+          if (PEER && p.rot_k) { kb = kq + p.rot_k; if (kb >= k1) kb -= (k1 - k0); }
+          // source rank and shard-local row of each operand
+          int a_src = 0, a_y = A_MN ? kb * BK : m_blk * BM;
+          int b_src = 0, b_y = B_MN ? kb * BK : n_blk * BN;
+          if constexpr (PEER) {
+            if (p.a_rows_per_src > 0) { a_src = a_y / p.a_rows_per_src; a_y -= a_src * p.a_rows_per_src; }
+            if (p.b_rows_per_src > 0) { b_src = b_y / p.b_rows_per_src; b_y -= b_src * p.b_rows_per_src; }
+            if (p.a_rows_per_src > 0 && p.a_slot >= 0 && !(a_ready & (1u << a_src))) {
+              if (a_src != p.rank &&
+                  !wait_epoch(p.flags + p.a_slot * MAX_PEERS + a_src, p.a_epoch, p.timeout_ns, p.status)) {
+                raise_abort(ab, p.status, ERR_WAIT_PEER);
+                ok = false;
+                break;
+              }
+              a_ready |= 1u << a_src;
+              fence_proxy_async_all();
+            }
+            if (p.b_rows_per_src > 0 && p.b_slot >= 0 && !(b_ready & (1u << b_src))) {
+              if (b_src != p.rank &&
+                  !wait_epoch(p.flags + p.b_slot * MAX_PEERS + b_src, p.b_epoch, p.timeout_ns, p.status)) {
+                raise_abort(ab, p.status, ERR_WAIT_PEER);
+                ok = false;
+                break;
+              }
+              b_ready |= 1u << b_src;
+              fence_proxy_async_all();
+            }
+          }
           if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, ab, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t sA = smem_base + stage * L::STAGE_BYTES;
           const uint32_t sB = sA + L::A_BYTES;
           mbar_expect_tx(full_bar(stage), L::STAGE_BYTES);
           armed |= 1u << stage;
           armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+          const CUtensorMap* ma = &tmA.m[PEER ? a_src : 0];
+          const CUtensorMap* mb = &tmB.m[PEER ? b_src : 0];
           if constexpr (!A_MN) {
-            tma_load_2d(sA, &tmA, full_bar(stage), kb * BK, m_blk * BM);
+            tma_load_2d(sA, ma, full_bar(stage), kb * BK, a_y);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d(sA + j * (BK * 128), &tmA, full_bar(stage), m_blk * BM + j * 64, kb * BK);
+              tma_load_2d(sA + j * (BK * 128), ma, full_bar(stage), m_blk * BM + j * 64, a_y);
           }
           if constexpr (!B_MN) {
-            tma_load_3d(sB, &tmB, full_bar(stage), kb * BK, n_blk * BN, ti.zb);
+            tma_load_3d(sB, mb, full_bar(stage), kb * BK, b_y, ti.zb);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(sB + j * (BK * 128), &tmB, full_bar(stage), n_blk * BN + j * 64, kb * BK, ti.zb);
+              tma_load_3d(sB + j * (BK * 128), mb, full_bar(stage), n_blk * BN + j * 64, b_y, ti.zb);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -278,6 +335,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         if (p.d_f32) {
           float* dp = reinterpret_cast<float*>(p.D) + ti.d_off + static_cast<long long>(row) * p.ldd + col0;
+          if constexpr (PEER) {
+            if (p.d_rows_per_rank > 0) {          // the row's owner accumulates every rank's partial product
+              const int owner = row / p.d_rows_per_rank;
+              dp = reinterpret_cast<float*>(p.d_peer[owner]) +
+                   static_cast<long long>(row - owner * p.d_rows_per_rank) * p.ldd + col0;
+            }
+          }
           if (p.atomic) {
             if (full) {
 #pragma unroll
@@ -326,10 +390,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------ host side
-template <int BN, int STAGES, bool A_MN, bool B_MN>
-static cudaError_t launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool PEER>
+static cudaError_t launch_cfg(const MapSet<PEER>& ta, const MapSet<PEER>& tb, const GemmParams& p, int grid,
                               cudaStream_t stream) {
-  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, PEER>;
   static bool attr_set = false;
   constexpr int smem = GemmSmem<BN, STAGES>::TOTAL;
   if (!attr_set) {
@@ -357,15 +421,48 @@ struct GroupSpec {
   long long group_stride_b = 0;  // elements between the B matrices of consecutive groups (mode 1)
   long long group_stride_d = 0;  // elements between the D (and C) matrices of consecutive groups (mode 2)
 };
+
+// Operands / output spread over the ranks of one NVSwitch domain (see GemmParams).
+struct PeerSpec {
+  int rank = 0, world = 1;
+  const void* const* a_ptrs = nullptr;   // rank r's shard of A as mapped here (null: A is local)
+  int a_rows_per_src = 0;
+  const void* const* b_ptrs = nullptr;   // likewise for an MN-major B
+  int b_rows_per_src = 0;
+  void* const* d_ptrs = nullptr;         // fp32 reduce-scatter destinations (null: D is local)
+  int d_rows_per_rank = 0;
+  const uint32_t* flags = nullptr;       // this rank's flag words
+  int a_slot = -1, b_slot = -1;
+  uint32_t a_epoch = 0, b_epoch = 0;
+  unsigned long long timeout_ns = 2000000000ull;
+};
 }  // namespace fmb
 
 static int run_gemm(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int a_mn,
                     int b_mn, long long lda, long long ldb, long long ldd, long long ldc, int d_f32,
                     int c_f32, float alpha, float beta, const float* alpha_ptr, int allow_split, int* status,
-                    int force_bn, const fmb::GroupSpec& gs, cudaStream_t stream) {
+                    int force_bn, const fmb::GroupSpec& gs, cudaStream_t stream,
+                    const fmb::PeerSpec* ps = nullptr) {
   using namespace fmb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (gs.mode != 0) allow_split = 0;
+  if (gs.mode != 0 || ps != nullptr) allow_split = 0;
+  if (ps != nullptr) {
+    if (gs.mode != 0 || ps->world < 1 || ps->world > FMB_MAX_PEERS || ps->rank < 0 || ps->rank >= ps->world) return -2;
+    if (ps->a_ptrs != nullptr) {
+      const int unit = a_mn ? GEMM_BK_C : 128;
+      if (ps->a_rows_per_src <= 0 || ps->a_rows_per_src % unit) return -2;
+      if (static_cast<long long>(ps->a_rows_per_src) * ps->world != (a_mn ? K : M)) return -2;
+    }
+    if (ps->b_ptrs != nullptr) {
+      if (!b_mn || ps->b_rows_per_src <= 0 || ps->b_rows_per_src % GEMM_BK_C) return -2;
+      if (static_cast<long long>(ps->b_rows_per_src) * ps->world != K) return -2;
+    }
+    if (ps->d_ptrs != nullptr) {
+      if (!d_f32 || C != nullptr || ps->d_rows_per_rank <= 0 || ps->d_rows_per_rank % 128) return -2;
+      if (static_cast<long long>(ps->d_rows_per_rank) * ps->world != M) return -2;
+    }
+    if ((ps->a_slot >= 0 || ps->b_slot >= 0) && ps->flags == nullptr) return -2;
+  }
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(D) & 15) || (ldd % (d_f32 ? 4 : 8)))
     return -2;   // TMA needs 16-byte aligned bases and pitches; the vector epilogue needs an aligned D
@@ -415,6 +512,36 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
   p.tile_group = gs.tile_group;
   p.region = gs.region;
   p.group_stride_d = gs.group_stride_d;
+  p.rank = 0; p.world = 1;
+  p.a_rows_per_src = p.b_rows_per_src = p.d_rows_per_rank = 0;
+  p.flags = nullptr;
+  p.a_slot = p.b_slot = -1;
+  p.a_epoch = p.b_epoch = 0;
+  p.timeout_ns = 0;
+  p.rot_m = p.rot_k = 0;
+  for (int r = 0; r < FMB_MAX_PEERS; ++r) p.d_peer[r] = nullptr;
+  if (ps != nullptr) {
+    p.rank = ps->rank; p.world = ps->world;
+    p.flags = ps->flags;
+    p.a_slot = ps->a_slot; p.b_slot = ps->b_slot;
+    p.a_epoch = ps->a_epoch; p.b_epoch = ps->b_epoch;
+    p.timeout_ns = ps->timeout_ns;
+    if (ps->a_ptrs != nullptr) {
+      p.a_rows_per_src = ps->a_rows_per_src;
+      if (a_mn) p.rot_k = ps->rank * (ps->a_rows_per_src / GEMM_BK);
+      else      p.rot_m = ps->rank * (ps->a_rows_per_src / GEMM_BM);
+    }
+    if (ps->b_ptrs != nullptr) {
+      p.b_rows_per_src = ps->b_rows_per_src;
+      p.rot_k = ps->rank * (ps->b_rows_per_src / GEMM_BK);
+    }
+    if (ps->d_ptrs != nullptr) {
+      p.d_rows_per_rank = ps->d_rows_per_rank;
+      p.atomic = 1;                       // partial products of all ranks meet in the owner's buffer
+      for (int r = 0; r < ps->world; ++r) p.d_peer[r] = ps->d_ptrs[r];
+      if (p.rot_m == 0) p.rot_m = ((ps->rank + 1) % ps->world) * (ps->d_rows_per_rank / GEMM_BM);   // remote rows first
+    }
+  }
   if (splits > 1) {
     // Every split adds alpha*partial into D, which already holds the C term (C == D) or zeros.
     if (C == D && beta == 1.f) { p.C = nullptr; }
@@ -422,35 +549,60 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
     else return -4;
   }
 
-  CUtensorMap ta, tb;
+  const int n_src = ps != nullptr ? ps->world : 1;
+  MapSet<true> ta, tb;
   bool ok = true;
-  if (!a_mn) ok = ok && make_tmap_2d(&ta, A, M, K, lda, GEMM_BM, GEMM_BK, 2, TmapSwizzle::B128);
-  else       ok = ok && make_tmap_2d(&ta, A, K, M, lda, GEMM_BK, 64, 2, TmapSwizzle::B128);
-  {
+  for (int r = 0; r < n_src && ok; ++r) {
+    const bool a_sharded = ps != nullptr && ps->a_ptrs != nullptr;
+    const void* abase = a_sharded ? ps->a_ptrs[r] : A;
+    if (a_sharded && (abase == nullptr || (reinterpret_cast<uintptr_t>(abase) & 15))) return -2;
+    if (!a_mn) ok = make_tmap_2d(&ta.m[r], abase, a_sharded ? ps->a_rows_per_src : M, K, lda, GEMM_BM, GEMM_BK, 2,
+                                 TmapSwizzle::B128);
+    else       ok = make_tmap_2d(&ta.m[r], abase, a_sharded ? ps->a_rows_per_src : K, M, lda, GEMM_BK, 64, 2,
+                                 TmapSwizzle::B128);
+    if (!ok) break;
     // B is always described by a 3-D map (inner, rows, group); plain products have one group.
+    const bool b_sharded = ps != nullptr && ps->b_ptrs != nullptr;
+    const void* bbase = b_sharded ? ps->b_ptrs[r] : B;
+    if (b_sharded && (bbase == nullptr || (reinterpret_cast<uintptr_t>(bbase) & 15))) return -2;
     const int nb = gs.mode == 1 ? gs.n_groups : 1;
+    const uint64_t brows = b_mn ? (b_sharded ? ps->b_rows_per_src : K) : N;
     const uint64_t gstride = gs.mode == 1 ? static_cast<uint64_t>(gs.group_stride_b)
-                                          : static_cast<uint64_t>(b_mn ? K : N) * static_cast<uint64_t>(ldb);
+                                          : brows * static_cast<uint64_t>(ldb);
     uint64_t dims[3], strides[3];
     uint32_t box[3];
     if (!b_mn) { dims[0] = K; dims[1] = N; box[0] = GEMM_BK; box[1] = best_bn; }
-    else       { dims[0] = N; dims[1] = K; box[0] = 64; box[1] = GEMM_BK; }
+    else       { dims[0] = N; dims[1] = brows; box[0] = 64; box[1] = GEMM_BK; }
     dims[2] = nb; box[2] = 1;
     strides[0] = 2; strides[1] = static_cast<uint64_t>(ldb) * 2; strides[2] = gstride * 2;
-    ok = ok && make_tmap_nd(&tb, B, 3, dims, strides, box, 2, TmapSwizzle::B128);
+    ok = make_tmap_nd(&tb.m[r], bbase, 3, dims, strides, box, 2, TmapSwizzle::B128);
   }
   if (!ok) return -5;
+  for (int r = n_src; r < FMB_MAX_PEERS; ++r) { ta.m[r] = ta.m[0]; tb.m[r] = tb.m[0]; }
 
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * (gs.mode == 2 ? gs.n_groups : p.splits);
   const int grid = static_cast<int>(total < sms ? total : sms);
   cudaError_t e;
-#define FMB_DISPATCH(BN, ST)                                                                   \
-  if (a_mn && b_mn)       e = launch_cfg<BN, ST, true, true>(ta, tb, p, grid, stream);          \
-  else if (a_mn)          e = launch_cfg<BN, ST, true, false>(ta, tb, p, grid, stream);         \
-  else if (b_mn)          e = launch_cfg<BN, ST, false, true>(ta, tb, p, grid, stream);         \
-  else                    e = launch_cfg<BN, ST, false, false>(ta, tb, p, grid, stream);
-  if (best_bn == 256) { FMB_DISPATCH(256, 4) } else { FMB_DISPATCH(128, 6) }
+  if (ps != nullptr) {
+#define FMB_DISPATCH(BN, ST)                                                                         \
+  if (a_mn && b_mn)       e = launch_cfg<BN, ST, true, true, true>(ta, tb, p, grid, stream);          \
+  else if (a_mn)          e = launch_cfg<BN, ST, true, false, true>(ta, tb, p, grid, stream);         \
+  else if (b_mn)          e = launch_cfg<BN, ST, false, true, true>(ta, tb, p, grid, stream);         \
+  else                    e = launch_cfg<BN, ST, false, false, true>(ta, tb, p, grid, stream);
+    if (best_bn == 256) { FMB_DISPATCH(256, 4) } else { FMB_DISPATCH(128, 6) }
 #undef FMB_DISPATCH
+  } else {
+    MapSet<false> sa, sb;
+    sa.m[0] = ta.m[0];
+    sb.m[0] = tb.m[0];
+#define FMB_DISPATCH(BN, ST)                                                                         \
+  if (a_mn && b_mn)       e = launch_cfg<BN, ST, true, true, false>(sa, sb, p, grid, stream);         \
+  else if (a_mn)          e = launch_cfg<BN, ST, true, false, false>(sa, sb, p, grid, stream);        \
+  else if (b_mn)          e = launch_cfg<BN, ST, false, true, false>(sa, sb, p, grid, stream);        \
+  else                    e = launch_cfg<BN, ST, false, false, false>(sa, sb, p, grid, stream);
+    if (best_bn == 256) { FMB_DISPATCH(256, 4) } else { FMB_DISPATCH(128, 6) }
+#undef FMB_DISPATCH
+  }
   return e == cudaSuccess ? 0 : -10 - static_cast<int>(e);
 }
 
@@ -483,4 +635,32 @@ extern "C" int fmb_gemm_bf16_grouped(const void* A, const void* B, void* D, cons
   if (mode == 2 && (region == nullptr || !a_mn || !b_mn)) return -2;
   return run_gemm(A, B, D, C, M, N, K, a_mn, b_mn, lda, ldb, ldd, ldc, d_f32, c_f32, alpha, beta, nullptr, 0,
                   status, 0, gs, stream);
+}
+
+// Products whose operands or output are spread over the ranks of one NVSwitch domain.
+//   a_ptrs / b_ptrs   `world` device pointers: rank r's shard as mapped into this process (null: local)
+//   d_ptrs            fp32 reduce-scatter destinations, [d_rows_per_rank, N] on each rank (null: local D)
+//   flags             this rank's flag words; slot < 0 means "do not wait"
+extern "C" int fmb_gemm_bf16_peer(const void* A, const void* B, void* D, int M, int N, int K, int a_mn, int b_mn,
+                                  long long lda, long long ldb, long long ldd, int d_f32, float alpha, int rank,
+                                  int world, const void* const* a_ptrs, int a_rows_per_src,
+                                  const void* const* b_ptrs, int b_rows_per_src, void* const* d_ptrs,
+                                  int d_rows_per_rank, const unsigned* flags, int a_slot, unsigned a_epoch,
+                                  int b_slot, unsigned b_epoch, unsigned long long timeout_ns, int* status,
+                                  cudaStream_t stream) {
+  fmb::GroupSpec gs;
+  fmb::PeerSpec ps;
+  ps.rank = rank; ps.world = world;
+  ps.a_ptrs = a_ptrs; ps.a_rows_per_src = a_rows_per_src;
+  ps.b_ptrs = b_ptrs; ps.b_rows_per_src = b_rows_per_src;
+  ps.d_ptrs = d_ptrs; ps.d_rows_per_rank = d_rows_per_rank;
+  ps.flags = flags;
+  ps.a_slot = a_slot; ps.a_epoch = a_epoch;
+  ps.b_slot = b_slot; ps.b_epoch = b_epoch;
+  ps.timeout_ns = timeout_ns;
+  const void* a0 = a_ptrs != nullptr ? a_ptrs[rank] : A;
+  const void* b0 = b_ptrs != nullptr ? b_ptrs[rank] : B;
+  void* d0 = d_ptrs != nullptr ? d_ptrs[rank] : D;
+  return run_gemm(a0, b0, d0, nullptr, M, N, K, a_mn, b_mn, lda, ldb, ldd, 0, d_f32, 0, alpha, 0.f, nullptr, 0, status,
+                  0, gs, stream, &ps);
 }

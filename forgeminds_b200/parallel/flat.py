@@ -46,9 +46,13 @@ def _round_up(n: int, m: int) -> int:
 
 
 class FlatParamStore:
-    def __init__(self, model, device, shard_world: int = 1, block_attr: str = "layers"):
+    def __init__(self, model, device, shard_world: int = 1, block_attr: str = "layers", symm=None):
+        """``symm`` (a :class:`~forgeminds_b200.parallel.symm.SymmGroup`) puts the gradient and the bf16
+        buffers into symmetric memory so that the peer-memory kernels can read / write them on every
+        rank; the buckets are then padded so that they split evenly over the group."""
         self.device = torch.device(device)
-        self.shard_world = max(1, int(shard_world))
+        self.symm = symm
+        self.shard_world = max(1, int(symm.world if symm is not None else shard_world))
         groups: list = []
         seen = set()
         blocks = getattr(model, block_attr, None)
@@ -77,8 +81,13 @@ class FlatParamStore:
             self.buckets.append(b)
         self.total = cursor
         self.master = torch.zeros(self.total, dtype=torch.float32, device=self.device)
-        self.grad = torch.zeros(self.total, dtype=torch.float32, device=self.device)
-        self.shadow = torch.zeros(self.total, dtype=torch.bfloat16, device=self.device)
+        if symm is not None:
+            self.grad_symm = symm.alloc(self.total, torch.float32)
+            self.shadow_symm = symm.alloc(self.total, torch.bfloat16)
+            self.grad, self.shadow = self.grad_symm.local, self.shadow_symm.local
+        else:
+            self.grad = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+            self.shadow = torch.zeros(self.total, dtype=torch.bfloat16, device=self.device)
         self.params: list = []
         self._offset: dict = {}
         with torch.no_grad():
@@ -108,6 +117,24 @@ class FlatParamStore:
             self.shadow.copy_(self.master)
         for p in self.params:
             p._fm_shadow = (p._fm_shadow[0], p._version)
+
+    def shard_range(self, b: Bucket, rank: int):
+        """(flat offset, length) of ``rank``'s part of bucket ``b``."""
+        n = b.size // self.shard_world
+        return b.start + rank * n, n
+
+    def sync_master(self) -> None:
+        """Make the fp32 masters whole again on every rank. With a sharded optimizer each rank only
+        updates its own part of every bucket (the bf16 working weights are complete everywhere); call
+        this before reading parameters as fp32: checkpoints, ``state_dict``, evaluation on the
+        PyTorch path."""
+        sg = self.symm
+        if sg is None or sg.world == 1:
+            return
+        for b in self.buckets:
+            lo, n = self.shard_range(b, sg.rank)
+            dist.all_gather_into_tensor(self.bucket_view(self.master, b), self.master[lo:lo + n].clone(),
+                                        group=sg.group)
 
     def rebind(self) -> None:
         """Re-attach ``.grad`` views (something set them to ``None``)."""

@@ -1,0 +1,150 @@
+"""Symmetric memory for the peer-memory kernels: buffers of equal size on every rank of a group,
+each mapped into every rank's address space, plus the flag words the kernels synchronise on.
+
+One process drives one GPU. Allocation goes through ``torch.distributed._symmetric_memory`` (cuMem
+allocations exchanged between the ranks of one NVLink/NVSwitch domain); when that is not available
+the buffers are ordinary CUDA allocations shared through CUDA IPC handles. A group of one rank needs
+neither and uses plain tensors, so the same kernels also run on a single GPU.
+
+The kernels never load a peer's memory through a multicast TMA copy: they use plain loads/stores
+(and tiled TMA loads without multicast) on the peer pointers handed out here. NVLink multicast
+binding of the buffers is left off unless ``nvls=True`` is asked for, because a rank that dies while
+its memory is bound to a multicast object can disturb the other GPUs of the node.
+
+The reference has no counterpart: its collectives are NCCL calls issued by FSDP2 / DDP / DTensor
+(``forgemind/parallel/native.py:52-79``).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+
+N_SLOTS = 128           # flag slots per group; slot s uses flags[s * MAX_PEERS + source_rank]
+
+
+@dataclass
+class SymmTensor:
+    """``local`` is this rank's buffer; ``ptrs[r]`` is the address of rank r's buffer as mapped here."""
+    local: torch.Tensor
+    ptrs: list
+    keep: object = None         # whatever owns the mappings
+
+    def peer_ptrs(self, offset_elems: int = 0) -> list:
+        step = offset_elems * self.local.element_size()
+        return [p + step for p in self.ptrs]
+
+
+def max_peers() -> int:
+    return int(ops.require().MAX_PEERS) if ops.available() else 8
+
+
+class SymmGroup:
+    """Allocator and flag bookkeeping for one process group on one device."""
+
+    def __init__(self, group, device, timeout_ms: float = 5000.0, nvls: bool = False):
+        self.group = group
+        self.device = torch.device(device)
+        self.world = dist.get_world_size(group) if (group is not None or dist.is_initialized()) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        if self.world > max_peers():
+            raise ValueError(f"peer-memory kernels address at most {max_peers()} ranks (one NVSwitch domain), "
+                             f"got a group of {self.world}")
+        self.timeout_ms = float(timeout_ms)
+        self.nvls = bool(nvls)
+        self.backend = "single" if self.world == 1 else None
+        self._epochs = [0] * N_SLOTS
+        self._reserved = 0
+        self.flags = self.alloc(N_SLOTS * max_peers(), torch.int32)
+        self.xchg = self.alloc(max_peers() * 4, torch.float32)
+        self.status = ops.status_word(self.device)
+        if self.world > 1:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)          # every rank's flags are zero before any kernel signals
+
+    # ------------------------------------------------------------------ allocation
+    def alloc(self, numel: int, dtype) -> SymmTensor:
+        numel = int(numel)
+        if self.world == 1:
+            t = torch.zeros(numel, dtype=dtype, device=self.device)
+            return SymmTensor(t, [t.data_ptr()])
+        if self.backend in (None, "torch"):
+            try:
+                st = self._alloc_torch(numel, dtype)
+                self.backend = "torch"
+                return st
+            except Exception as e:                   # noqa: BLE001 - any failure means "try the other way"
+                if self.backend == "torch":
+                    raise
+                self._why_not_torch = repr(e)
+        st = self._alloc_ipc(numel, dtype)
+        self.backend = "ipc"
+        return st
+
+    def _alloc_torch(self, numel, dtype) -> SymmTensor:
+        import torch.distributed._symmetric_memory as sm
+        if not self.nvls:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        group = self.group if self.group is not None else dist.group.WORLD
+        name = group.group_name
+        try:
+            sm.enable_symm_mem_for_group(name)
+        except Exception:                            # noqa: BLE001 - newer torch needs no enabling
+            pass
+        t = sm.empty(numel, dtype=dtype, device=self.device)
+        hdl = sm.rendezvous(t, name)
+        t.zero_()
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        if len(ptrs) != self.world or ptrs[self.rank] != t.data_ptr():
+            raise RuntimeError("symmetric memory handle does not describe this buffer")
+        return SymmTensor(t, ptrs, keep=hdl)
+
+    def _alloc_ipc(self, numel, dtype) -> SymmTensor:
+        """CUDA IPC: every rank exports its allocation, the others open it."""
+        t = torch.zeros(numel, dtype=dtype, device=self.device)
+        storage = t.untyped_storage()
+        handle = storage._share_cuda_()
+        offset_in_block = handle[3]
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, (handle, t.storage_offset() * t.element_size()), group=self.group)
+        ptrs, keep = [], [t]
+        for r, (h, off) in enumerate(gathered):
+            if r == self.rank:
+                ptrs.append(t.data_ptr())
+                continue
+            h = list(h)
+            h[0] = self.device.index if self.device.index is not None else torch.cuda.current_device()
+            remote = torch.UntypedStorage._new_shared_cuda(*h)
+            keep.append(remote)
+            ptrs.append(remote.data_ptr() + off)
+        del offset_in_block
+        return SymmTensor(t, ptrs, keep=keep)
+
+    # ------------------------------------------------------------------ flags
+    def reserve_slots(self, n: int) -> int:
+        """First index of ``n`` flag slots nobody else uses."""
+        first = self._reserved
+        if first + n > N_SLOTS:
+            raise RuntimeError("out of flag slots")
+        self._reserved += n
+        return first
+
+    def next_epoch(self, slot: int) -> int:
+        self._epochs[slot] += 1
+        return self._epochs[slot] & 0x7FFFFFFF
+
+    def barrier(self, slot: int) -> None:
+        """All ranks have reached this point of their current streams (enqueued, not waited for)."""
+        if self.world == 1:
+            return
+        ops.require().comm_barrier(self.flags.ptrs, slot, self.next_epoch(slot), self.rank, self.timeout_ms,
+                                   self.status)
+
+    def check(self, sync_value=None) -> None:
+        """Raise :class:`ops.CommTimeout` if one of the bounded waits ran out. Reads the status word
+        (a host synchronisation) unless the caller already has its value."""
+        ops.check_status(self.device, sync_value)

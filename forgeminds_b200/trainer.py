@@ -197,14 +197,28 @@ class Trainer:
     def _setup_native(self, model, tc, pc, dp: bool) -> None:
         from .parallel.flat import BucketReducer, FlatAdamW, FlatParamStore
         ctx = self.ctx
-        self.store = FlatParamStore(model, ctx.device)
-        self.opt = FlatAdamW(self.store, lr=tc.lr, betas=tc.betas, eps=tc.eps, weight_decay=tc.weight_decay)
-        self._muon_opt = self._muon(model, tc) if tc.optimizer == "muon" else None
+        # Peer-memory step (parallel/peer.py): one data-parallel dimension inside one NVSwitch domain,
+        # AdamW, no pipeline stages. Everything else reduces whole buckets with all_reduce.
+        self.peer = bool(pc.fused_comm) and tc.optimizer != "muon" and pc.pp == 1 and ctx.dp_world <= 8 \
+            and not (pc.dp_replicate > 1 and pc.dp_shard > 1)
+        if self.peer:
+            from .parallel.peer import PeerAdamW, PeerReducer
+            from .parallel.symm import SymmGroup
+            sg = SymmGroup(ctx.dp_group if dp else None, ctx.device, timeout_ms=pc.comm_timeout_ms)
+            self.store = FlatParamStore(model, ctx.device, symm=sg)
+            self.opt = PeerAdamW(self.store, lr=tc.lr, betas=tc.betas, eps=tc.eps, weight_decay=tc.weight_decay)
+            self.reducer = PeerReducer(self.store)
+            self._muon_opt = None
+        else:
+            self.store = FlatParamStore(model, ctx.device)
+            self.opt = FlatAdamW(self.store, lr=tc.lr, betas=tc.betas, eps=tc.eps, weight_decay=tc.weight_decay)
+            self._muon_opt = self._muon(model, tc) if tc.optimizer == "muon" else None
         self._norm_sq = torch.zeros(1, dtype=torch.float32, device=ctx.device)
-        if dp:
-            if pc.ep > 1:
-                raise NotImplementedError("native engine + expert parallelism: handled by parallel.ep")
+        if dp and pc.ep > 1:
+            raise NotImplementedError("native engine + expert parallelism: handled by parallel.ep")
+        if dp and not self.peer:
             self.reducer = BucketReducer(self.store, ctx.dp_group, ctx.dp_world)
+        if self.reducer is not None:
             blocks = list(model.layers.values())
             by_name = {b.name: b for b in self.store.buckets}
             for i, blk in enumerate(blocks):
@@ -385,21 +399,32 @@ class Trainer:
         else:
             if self.reducer is not None:
                 self.reducer.finish()
-            native.sync_expert_grads(self.model, ctx, self._expert_params)
-            gn = self._clip().to(ctx.device)
-            loss = self._reduce_loss(loss)
-            if tc.skip_nonfinite:
-                finite = (torch.isfinite(gn) & torch.isfinite(loss)).to(torch.int32)
+            peer = getattr(self, "peer", False)
+            if peer:
+                # one kernel exchanges norm, loss and the finite flag with the peers and fills `ctl`
+                stats = self.opt.reduce_step(self.reducer, loss, tc.grad_clip, tc.skip_nonfinite)
+                gn, loss, flag = stats[0], stats[1], stats[2]
             else:
-                finite = torch.ones((), dtype=torch.int32, device=loss.device)
-            flag = ctx.all_min_int(finite)
+                native.sync_expert_grads(self.model, ctx, self._expert_params)
+                gn = self._clip().to(ctx.device)
+                loss = self._reduce_loss(loss)
+                if tc.skip_nonfinite:
+                    finite = (torch.isfinite(gn) & torch.isfinite(loss)).to(torch.int32)
+                else:
+                    finite = torch.ones((), dtype=torch.int32, device=loss.device)
+                flag = ctx.all_min_int(finite)
             early = self.store is not None and not (tc.skip_spike_factor > 0)
             if early:
                 # the fused kernel reads the flag on the device: enqueue the update before the host read
-                self.opt.ctl[1:2].copy_(flag.to(torch.float32).reshape(1))
+                if not peer:
+                    self.opt.ctl[1:2].copy_(flag.to(torch.float32).reshape(1))
                 self._apply_update()
             # the single host synchronisation of the step
-            flag_v, gn_v, lv = torch.stack([flag.to(torch.float32), gn.to(torch.float32), loss]).tolist()
+            if peer:
+                gn_v, lv, flag_v, st_v = torch.cat([stats, self.store.symm.status.to(torch.float32)]).tolist()
+                self.store.symm.check(int(st_v))
+            else:
+                flag_v, gn_v, lv = torch.stack([flag.to(torch.float32), gn.to(torch.float32), loss]).tolist()
             ok = flag_v > 0.5
             if tc.skip_spike_factor > 0 and self.loss_ema is not None and lv > tc.skip_spike_factor * self.loss_ema:
                 ok = False
@@ -503,6 +528,7 @@ class Trainer:
                 self.save()
         if tc.ckpt_every:
             self.save()
+        self.sync_params()
         return self.history
 
     # ------------------------------------------------------------------ checkpoints
@@ -513,7 +539,17 @@ class Trainer:
     def _dcp_state(self):
         from torch.distributed.checkpoint.state_dict import get_state_dict
         opt = () if self.off_opt is not None or self.use_ds else self.opt
+        if getattr(self, "peer", False):
+            # sharded optimizer: every rank presents the whole state, as a replicated run would
+            self.store.sync_master()
+            self.opt.gather_full()
         return get_state_dict(self.model, opt)
+
+    def sync_params(self) -> None:
+        """Make the fp32 parameters complete on every rank (they are sharded between optimizer steps
+        on the peer-memory engine; the bf16 working weights are always complete)."""
+        if getattr(self, "peer", False):
+            self.store.sync_master()
 
     def save(self, keep_last: int = 3) -> None:
         import torch.distributed.checkpoint as dcp
@@ -529,6 +565,8 @@ class Trainer:
             target = os.path.join(path, "dcp")
             shutil.rmtree(target, ignore_errors=True)
             dcp.save(state, checkpoint_id=target)
+            if getattr(self, "peer", False):
+                self.opt.release_full()
             if self.off_opt is not None:
                 torch.save(self.off_opt.state_dict(), os.path.join(path, f"offopt_rank{self.ctx.rank}.pt"))
         meta = {"step": self.step, "epoch": self.epoch, "batches_in_epoch": self.batches_in_epoch,
@@ -568,6 +606,8 @@ class Trainer:
                                                         map_location="cpu", weights_only=False))
             else:
                 set_state_dict(self.model, self.opt, model_state_dict=state["model"], optim_state_dict=state["optim"])
+            if getattr(self, "peer", False):
+                self.opt.scatter_full()
             if self.store is not None:
                 self.store.refresh_shadow()
         with open(os.path.join(path, f"meta_rank{self.ctx.rank}.json")) as f:

@@ -1,0 +1,194 @@
+"""Multi-GPU scenarios, one process per GPU, started by tests/test_gpu_multi.py through torchrun.
+
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 tests/mp_gpu_check.py <scenario>
+
+Every scenario prints ``OK <scenario>`` on rank 0 when all ranks agree with the single-process
+expectation. NVLink multicast stays off (plain peer loads and stores only).
+"""
+import os
+import sys
+
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+import forgeminds_b200 as fm
+
+
+def _init():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    return rank, world, torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+
+
+def _tiny(device):
+    torch.manual_seed(0)
+    cfg = fm.GPTConfig(vocab_size=512, dim=128, n_layers=2, n_heads=4, n_kv_heads=2, max_seq=128, ffn_hidden=384)
+    return fm.GPT(cfg).to(device)
+
+
+def peer_kernels():
+    """reduce-scatter + norm exchange + sharded AdamW + push against all_reduce + the PyTorch AdamW."""
+    from forgeminds_b200.parallel.flat import FlatParamStore, _adamw_reference
+    from forgeminds_b200.parallel.peer import PeerAdamW, PeerReducer
+    from forgeminds_b200.parallel.symm import SymmGroup
+    rank, world, dev = _init()
+    model = _tiny(dev)
+    sg = SymmGroup(None, dev, timeout_ms=5000)
+    store = FlatParamStore(model, dev, symm=sg)
+    opt = PeerAdamW(store, lr=1e-2, weight_decay=0.1)
+    red = PeerReducer(store)
+    master0 = store.master.clone()
+    exp_m = torch.zeros_like(master0)
+    exp_v = torch.zeros_like(master0)
+    exp_p = master0.clone()
+    exp_sh = torch.zeros_like(store.shadow)
+    for step in range(3):
+        g = torch.Generator(device=dev).manual_seed(100 * step + rank)
+        store.grad.copy_(torch.randn(store.total, device=dev, generator=g))
+        want_g = store.grad.clone()
+        dist.all_reduce(want_g)
+        want_g /= world
+        loss = torch.tensor(float(rank + step), device=dev)
+        for b in store.buckets[:1]:
+            red.launch(b)
+        red.finish()
+        stats = opt.reduce_step(red, loss, max_norm=1.0, skip_nonfinite=True)
+        opt.param_groups[0]["lr"] = 1e-2
+        opt.step()
+        torch.cuda.synchronize()
+        sg.check()
+        norm = want_g.norm()
+        coef = torch.clamp(1.0 / (norm + 1e-6), max=1.0)
+        assert abs(stats[0].item() - norm.item()) < 1e-3 * norm.item(), (stats, norm)
+        assert abs(stats[1].item() - (sum(range(world)) / world + step)) < 1e-5
+        assert stats[2].item() == 1.0
+        ctl = torch.stack([coef, torch.ones((), device=dev)])
+        b1, b2 = 0.9, 0.95
+        for b in store.buckets:
+            for off, n, dec in opt._segments(b):
+                lo = b.start + off
+                _adamw_reference(exp_p[lo:lo + n], want_g[lo:lo + n], exp_m[lo:lo + n], exp_v[lo:lo + n],
+                                 exp_sh[lo:lo + n], 1e-2, b1, b2, 1e-8, 0.1 if dec else 0.0, 1 - b1 ** (step + 1),
+                                 1 - b2 ** (step + 1), ctl)
+        # bf16 working weights are complete on every rank
+        assert (store.shadow.float() - exp_sh.float()).abs().max() < 1e-3
+        store.sync_master()
+        assert (store.master - exp_p).abs().max() < 2e-5, (store.master - exp_p).abs().max()
+    # the gathered optimizer state equals the replicated one
+    opt.gather_full()
+    full_m, full_v = opt._full
+    assert (full_m - exp_m).abs().max() < 1e-5 and (full_v - exp_v).abs().max() < 1e-5
+    sd = opt.state_dict()
+    opt.release_full()
+    opt.exp_avg.zero_()
+    opt.load_state_dict(sd)
+    opt.gather_full()
+    for p in store.params:                     # the padding between parameters is not part of the state
+        lo = store._offset[p]
+        assert (opt._full[0][lo:lo + p.numel()] - exp_m[lo:lo + p.numel()]).abs().max() < 1e-5
+    opt.release_full()
+    dist.barrier()
+    if rank == 0:
+        print("OK peer_kernels", flush=True)
+
+
+def peer_trainer():
+    """The peer-memory engine follows the all_reduce engine step for step."""
+    rank, world, dev = _init()
+    losses = {}
+    for fused in (True, False):
+        cfg = fm.ForgeConfig()
+        cfg.parallel.dp_shard = world
+        cfg.parallel.fused_comm = fused
+        cfg.train.__dict__.update(max_steps=12, grad_accum=2, lr=3e-3, warmup_steps=3, bf16=True, resume=False,
+                                  log_every=1000, prefetch=False, ckpt_every=0)
+        mc = fm.GPTConfig(vocab_size=512, dim=128, n_layers=2, n_heads=4, n_kv_heads=2, max_seq=128, ffn_hidden=384)
+        tr = fm.Trainer(lambda ctx: fm.GPT(mc), cfg, fm.SyntheticLM(512, 128, n=512), micro_batch=4)
+        assert tr.store is not None and bool(getattr(tr, "peer", False)) == fused
+        hist = tr.fit()
+        tr.close()
+        losses[fused] = [h["loss"] for h in hist]
+        norms = [h["grad_norm"] for h in hist]
+        assert all(n > 0 for n in norms)
+    a, b = losses[True], losses[False]
+    assert a[-1] < 0.8 * a[0], a
+    assert max(abs(x - y) for x, y in zip(a, b)) < 0.05, (a, b)
+    if rank == 0:
+        print("OK peer_trainer", flush=True)
+
+
+def gemm_peer():
+    """All-gather fused into the GEMM's operand loads, reduce-scatter fused into its epilogue."""
+    from forgeminds_b200 import ops
+    from forgeminds_b200.parallel.symm import SymmGroup
+    rank, world, dev = _init()
+    C = ops.require()
+    sg = SymmGroup(None, dev, timeout_ms=5000)
+    slot = sg.reserve_slots(4)
+    Ms, K, N = 256, 512, 384                       # per-rank rows, inner, output columns
+    M = Ms * world
+
+    def rand(shape, seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        return (torch.randn(shape, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+
+    # every rank can rebuild every shard from its seed
+    x_sh = sg.alloc(Ms * K, torch.bfloat16)
+    x_sh.local.copy_(rand((Ms, K), 10 + rank).reshape(-1))
+    x_full = torch.cat([rand((Ms, K), 10 + r) for r in range(world)])
+    w = rand((N, K), 99 + rank)                    # this rank's column shard of the weight
+    # 1. AG -> GEMM (A K-major, rows spread over the ranks): y = gather(x) @ w.T
+    C.comm_signal(sg.flags.ptrs, slot, sg.next_epoch(slot), rank, sg.status)
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    C.gemm_peer(x_sh.local.view(Ms, K), w, y, False, False, 1.0, rank, world, x_sh.ptrs, [], [], sg.flags.local,
+                slot, sg._epochs[slot], -1, 0, sg.timeout_ms, sg.status)
+    want = x_full.float() @ w.float().T
+    torch.cuda.synchronize()
+    sg.check()
+    assert (y.float() - want).abs().max() < 0.02 * want.abs().max(), (y.float() - want).abs().max()
+    # 2. wgrad with the gathered operand on the B side (MN-major, reduction rows spread over the ranks):
+    #    dw[N, K] = dy[M, N].T @ gather(x)[M, K]
+    dy = rand((M, N), 7 + rank)
+    dw = torch.empty(N, K, dtype=torch.float32, device=dev)
+    C.gemm_peer(dy, x_sh.local.view(Ms, K), dw, True, True, 1.0, rank, world, [], x_sh.ptrs, [], sg.flags.local,
+                -1, 0, slot, sg._epochs[slot], sg.timeout_ms, sg.status)
+    want = dy.float().T @ x_full.float()
+    torch.cuda.synchronize()
+    sg.check()
+    assert (dw - want).abs().max() < 0.02 * want.abs().max()
+    # 3. the same with the gathered operand on the A side: dw2[K, N] = gather(x).T @ dy
+    dw2 = torch.empty(K, N, dtype=torch.float32, device=dev)
+    C.gemm_peer(x_sh.local.view(Ms, K), dy, dw2, True, True, 1.0, rank, world, x_sh.ptrs, [], [], sg.flags.local,
+                slot, sg._epochs[slot], -1, 0, sg.timeout_ms, sg.status)
+    torch.cuda.synchronize()
+    sg.check()
+    assert (dw2 - want.T).abs().max() < 0.02 * want.abs().max()
+    # 4. GEMM -> RS: every rank holds h[M, K] and a row shard w_r[N, K] of different content; the sum of
+    #    the partial products over the ranks lands, row block by row block, on the rank that owns it.
+    h = rand((M, K), 50 + rank)
+    acc = sg.alloc(Ms * N, torch.float32)
+    sg.barrier(slot + 1)                           # everybody's accumulator is zero
+    C.gemm_peer(h, w, acc.local.view(Ms, N), False, False, 1.0, rank, world, [], [], acc.ptrs, sg.flags.local,
+                -1, 0, -1, 0, sg.timeout_ms, sg.status)
+    sg.barrier(slot + 2)                           # all partial products have landed
+    torch.cuda.synchronize()
+    sg.check()
+    want = sum(rand((M, K), 50 + r).float() @ rand((N, K), 99 + r).float().T for r in range(world))
+    got = acc.local.view(Ms, N)
+    ref = want[rank * Ms:(rank + 1) * Ms]
+    assert (got - ref).abs().max() < 0.02 * ref.abs().max(), (got - ref).abs().max()
+    dist.barrier()
+    if rank == 0:
+        print("OK gemm_peer", flush=True)
+
+
+if __name__ == "__main__":
+    name = sys.argv[1]
+    globals()[name]()
+    if dist.is_initialized():
+        dist.destroy_process_group()
