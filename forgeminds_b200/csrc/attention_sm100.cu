@@ -14,6 +14,7 @@
 //
 // Head dims that are not a multiple of 64 are padded by TMA out-of-bounds fill (zeros).
 #include "ptx_sm100.cuh"
+#include "launch.cuh"
 #include "tensormap.h"
 #include "fmb_api.h"
 #include <math_constants.h>
@@ -128,6 +129,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();
+  pdl_launch_dependents();
   const uint32_t tmem = *tmem_slot;
 
   if (warp == 0) {
@@ -434,6 +437,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();
+  pdl_launch_dependents();
   const uint32_t tmem = *tmem_slot;
 
   if (warp == 0) {
@@ -689,6 +694,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
                   int B, int T, int Hq, int hd, long long o_stride_t) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const long long item = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;   // (b, t, h)
   if (item >= static_cast<long long>(B) * T * Hq) return;
@@ -718,6 +725,8 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
 __global__ void __launch_bounds__(256)
 attn_dq_store_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long rows, int width,
                      long long dq_stride_t) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int wv = width >> 3;
   const long long total = rows * wv;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -772,15 +781,13 @@ extern "C" int fmb_attn_fwd(const void* q, const void* k, const void* v, void* o
     constexpr int sm = FwdSmem<64>::TOTAL;
     static bool done = false;
     if (!done) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sm) != cudaSuccess) return -6; done = true; }
-    kern<<<grid, ATT_FWD_THREADS, sm, stream>>>(tq, tk, tv, p);
-    e = cudaGetLastError();
+    e = launch_pdl(kern, dim3(grid), dim3(ATT_FWD_THREADS), sm, stream, tq, tk, tv, p);
   } else {
     auto kern = attn_fwd_kernel<128>;
     constexpr int sm = FwdSmem<128>::TOTAL;
     static bool done = false;
     if (!done) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sm) != cudaSuccess) return -6; done = true; }
-    kern<<<grid, ATT_FWD_THREADS, sm, stream>>>(tq, tk, tv, p);
-    e = cudaGetLastError();
+    e = launch_pdl(kern, dim3(grid), dim3(ATT_FWD_THREADS), sm, stream, tq, tk, tv, p);
   }
   return e == cudaSuccess ? 0 : -10 - static_cast<int>(e);
 }
@@ -800,8 +807,9 @@ extern "C" int fmb_attn_bwd(const void* q, const void* k, const void* v, const v
     return -5;
   {
     const long long items = static_cast<long long>(B) * T * Hq;
-    attn_delta_kernel<<<static_cast<unsigned>((items * 32 + 255) / 256), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, B, T, Hq, hd, o_stride_t);
+    launch_pdl(attn_delta_kernel, dim3(static_cast<unsigned>((items * 32 + 255) / 256)), dim3(256), 0, stream,
+               static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, B, T, Hq, hd,
+               o_stride_t);
   }
   AttnBwdParams p;
   p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.hd = hd;
@@ -817,13 +825,13 @@ extern "C" int fmb_attn_bwd(const void* q, const void* k, const void* v, const v
     constexpr int sm = BwdSmem<64>::TOTAL;
     static bool done = false;
     if (!done) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sm) != cudaSuccess) return -6; done = true; }
-    kern<<<grid, ATT_BWD_THREADS, sm, stream>>>(tq, tk, tv, tdo, p);
+    if (launch_pdl(kern, dim3(grid), dim3(ATT_BWD_THREADS), sm, stream, tq, tk, tv, tdo, p) != cudaSuccess) return -7;
   } else {
     auto kern = attn_bwd_kernel<128>;
     constexpr int sm = BwdSmem<128>::TOTAL;
     static bool done = false;
     if (!done) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sm) != cudaSuccess) return -6; done = true; }
-    kern<<<grid, ATT_BWD_THREADS, sm, stream>>>(tq, tk, tv, tdo, p);
+    if (launch_pdl(kern, dim3(grid), dim3(ATT_BWD_THREADS), sm, stream, tq, tk, tv, tdo, p) != cudaSuccess) return -7;
   }
   if (cudaGetLastError() != cudaSuccess) return -7;
   {
@@ -831,7 +839,8 @@ extern "C" int fmb_attn_bwd(const void* q, const void* k, const void* v, const v
     const int width = Hq * hd;
     long long blocks = (rows * (width / 8) + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    attn_dq_store_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), rows, width, dq_stride_t);
+    launch_pdl(attn_dq_store_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, dq_acc,
+               static_cast<__nv_bfloat16*>(dq), rows, width, dq_stride_t);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -8;
 }

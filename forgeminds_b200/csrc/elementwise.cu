@@ -5,6 +5,7 @@
 #include "ptx_sm100.cuh"
 #include "tensormap.h"
 #include "fmb_api.h"
+#include "launch.cuh"
 #include <math_constants.h>
 
 namespace fmb {
@@ -45,7 +46,7 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// Sum over the TPR threads that share a row. TPR = 32: a warp; TPR = 256: the whole block.
+// Sum over the TPR threads that share a row (TPR = 32: one warp ... 256: the whole block).
 template <int TPR>
 __device__ __forceinline__ float row_sum(float v, float* scratch) {
   v = warp_sum(v);
@@ -55,8 +56,9 @@ __device__ __forceinline__ float row_sum(float v, float* scratch) {
     if ((threadIdx.x & 31) == 0) scratch[w] = v;
     __syncthreads();
     v = 0.f;
+    const int first = (w / (TPR / 32)) * (TPR / 32);      // first warp of this thread's row
 #pragma unroll
-    for (int i = 0; i < TPR / 32; ++i) v += scratch[i];
+    for (int i = 0; i < TPR / 32; ++i) v += scratch[first + i];
   }
   return v;
 }
@@ -69,6 +71,8 @@ __global__ void __launch_bounds__(ROW_THREADS)
 rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ delta, const WT* __restrict__ w,
                    T* __restrict__ xn, T* __restrict__ y, float* __restrict__ rstd, long long rows, int d, float eps) {
   __shared__ float scratch[ROW_THREADS / 32];
+  pdl_wait();
+  pdl_launch_dependents();
   constexpr int RPB = ROW_THREADS / TPR;
   const int sub = threadIdx.x / TPR, t = threadIdx.x % TPR;
   const long long row = static_cast<long long>(blockIdx.x) * RPB + sub;
@@ -122,7 +126,9 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const WT* 
                    const float* __restrict__ rstd, const T* __restrict__ dres, T* __restrict__ dx,
                    float* __restrict__ dw_partial, long long rows, int d) {
   __shared__ float scratch[ROW_THREADS / 32];
-  extern __shared__ float dw_smem[];           // d floats, only used when TPR == 32
+  pdl_wait();
+  pdl_launch_dependents();
+  extern __shared__ float dw_smem[];           // d floats, only used when several rows share a block
   constexpr int RPB = ROW_THREADS / TPR;
   const int sub = threadIdx.x / TPR, t = threadIdx.x % TPR;
   const int nvec = d >> 3;
@@ -175,8 +181,8 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const WT* 
     }
   }
   if (dw_partial == nullptr) return;
-  if constexpr (TPR == 32) {
-    // the 8 warps of the block hold partial sums of the same columns: fold them in warp order
+  if constexpr (RPB > 1) {
+    // the RPB row groups of the block hold partial sums of the same columns: fold them in a fixed order
     for (int turn = 0; turn < RPB; ++turn) {
       if (sub == turn) {
 #pragma unroll
@@ -206,18 +212,32 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const WT* 
   }
 }
 
-__global__ void colsum_kernel(const float* __restrict__ part, float* __restrict__ out, int nrows, int d, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
+// Column sums of part[nrows, d] in a fixed order: block = 32 columns x 32 row groups.
+__global__ void __launch_bounds__(1024)
+colsum_kernel(const float* __restrict__ part, float* __restrict__ out, int nrows, int d, int accumulate) {
+  __shared__ float red[32][33];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int r = 0; r < nrows; ++r) s += part[static_cast<long long>(r) * d + c];
-  out[c] = accumulate ? out[c] + s : s;
+  if (c < d)
+    for (int r = threadIdx.y; r < nrows; r += 32) s += part[static_cast<long long>(r) * d + c];
+  red[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < d) {
+    float t = 0.f;
+#pragma unroll
+    for (int g = 0; g < 32; ++g) t += red[g][threadIdx.x];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 
 // ------------------------------------------------------------------ SwiGLU
 template <typename T>
 __global__ void swiglu_fwd_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out,
                                   long long rows, int h, long long ld_in) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int hv = h >> 3;
   const long long total = rows * hv;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -236,6 +256,8 @@ __global__ void swiglu_fwd_kernel(const T* __restrict__ gate, const T* __restric
 template <typename T>
 __global__ void swiglu_bwd_kernel(const T* __restrict__ gate, const T* __restrict__ up, const T* __restrict__ dy,
                                   T* __restrict__ dgate, T* __restrict__ dup, long long rows, int h, long long ld_in) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int hv = h >> 3;
   const long long total = rows * hv;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -263,6 +285,8 @@ template <typename T>
 __global__ void rope_kernel(const T* __restrict__ src, T* __restrict__ dst, const float* __restrict__ cs,
                             const float* __restrict__ sn, long long rows, int T_len, int n_rot, int heads_total, int hd,
                             float sign) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int half = hd >> 1;
   const int hv = half >> 3;
   const bool inplace = src == dst;
@@ -535,10 +559,9 @@ static int launch_rms_fwd(const void* x, const void* delta, const void* w, void*
   {                                                                                                   \
     constexpr int RPB = ROW_THREADS / TPR;                                                            \
     const unsigned blocks = static_cast<unsigned>((rows + RPB - 1) / RPB);                            \
-    rmsnorm_fwd_kernel<T, WT, TPR, VPL, ADD><<<blocks, ROW_THREADS, 0, st>>>(                         \
+    return launch_pdl(rmsnorm_fwd_kernel<T, WT, TPR, VPL, ADD>, dim3(blocks), dim3(ROW_THREADS), 0, st, \
         static_cast<const T*>(x), static_cast<const T*>(delta), static_cast<const WT*>(w),            \
-        static_cast<T*>(xn), static_cast<T*>(y), rstd, rows, d, eps);                                 \
-    return cudaGetLastError() == cudaSuccess ? 0 : -3;                                                \
+        static_cast<T*>(xn), static_cast<T*>(y), rstd, rows, d, eps) == cudaSuccess ? 0 : -3;         \
   }
   if (nvec <= 32) FMB_RMS_FWD(32, 1)
   if (nvec <= 64) FMB_RMS_FWD(32, 2)
@@ -557,16 +580,16 @@ static int launch_rms_bwd(const void* dy, const void* x, const void* w, const fl
   const int nvec = d / 8;
 #define FMB_RMS_BWD(TPR, VPL)                                                                         \
   {                                                                                                   \
-    const size_t sm = TPR == 32 ? sizeof(float) * d : 0;                                              \
-    rmsnorm_bwd_kernel<T, WT, TPR, VPL><<<nblocks, ROW_THREADS, sm, st>>>(                            \
+    const size_t sm = TPR < ROW_THREADS ? sizeof(float) * d : 0;                                      \
+    return launch_pdl(rmsnorm_bwd_kernel<T, WT, TPR, VPL>, dim3(nblocks), dim3(ROW_THREADS), sm, st,  \
         static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const WT*>(w), rstd,         \
-        static_cast<const T*>(dres), static_cast<T*>(dx), dwp, rows, d);                              \
-    return cudaGetLastError() == cudaSuccess ? 0 : -3;                                                \
+        static_cast<const T*>(dres), static_cast<T*>(dx), dwp, rows, d) == cudaSuccess ? 0 : -3;      \
   }
+  // few values per thread: the kernel keeps four of them (dy, x, w, dw) live per element
   if (nvec <= 32) FMB_RMS_BWD(32, 1)
-  if (nvec <= 64) FMB_RMS_BWD(32, 2)
-  if (nvec <= 128) FMB_RMS_BWD(32, 4)
-  if (nvec <= 256) FMB_RMS_BWD(32, 8)
+  if (nvec <= 64) FMB_RMS_BWD(64, 1)
+  if (nvec <= 128) FMB_RMS_BWD(128, 1)
+  if (nvec <= 256) FMB_RMS_BWD(256, 1)
   if (nvec <= 512) FMB_RMS_BWD(256, 2)
   if (nvec <= 1024) FMB_RMS_BWD(256, 4)
   if (nvec <= 2048) FMB_RMS_BWD(256, 8)
@@ -603,10 +626,11 @@ extern "C" int fmb_add_rmsnorm_fwd(const void* x, const void* delta, const void*
 }
 
 extern "C" int fmb_rmsnorm_bwd_blocks(long long rows, int d) {
-  const int tpr = (d / 8) <= 256 ? 32 : 256;
+  const int nvec = d / 8;
+  const int tpr = nvec <= 32 ? 32 : nvec <= 64 ? 64 : nvec <= 128 ? 128 : 256;
   const int rpb = ROW_THREADS / tpr;
   long long need = (rows + rpb - 1) / rpb;
-  long long cap = static_cast<long long>(sm_count()) * 2;
+  long long cap = static_cast<long long>(sm_count()) * (nvec <= 256 ? 4 : 2);
   return static_cast<int>(need < 1 ? 1 : (need > cap ? cap : need));
 }
 
@@ -622,8 +646,8 @@ extern "C" int fmb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
     return -1;
   });
   if (rc != 0 || dw_partial == nullptr || dw == nullptr) return rc;
-  colsum_kernel<<<(d + 127) / 128, 128, 0, stream>>>(dw_partial, dw, nblocks, d, dw_accumulate);
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  return launch_pdl(colsum_kernel, dim3((d + 31) / 32), dim3(32, 32), 0, stream, dw_partial, dw, nblocks, d,
+                    dw_accumulate) == cudaSuccess ? 0 : -3;
 }
 
 extern "C" int fmb_swiglu_fwd(const void* gate, const void* up, void* out, long long rows, int h, long long ld_in,
@@ -632,9 +656,9 @@ extern "C" int fmb_swiglu_fwd(const void* gate, const void* up, void* out, long 
   if (h % 8 || ld_in % 8) return -2;
   return by_dtype(dtype, [&](auto* tp) {
     using T = std::remove_pointer_t<decltype(tp)>;
-    swiglu_fwd_kernel<T><<<grid_for(rows * (h / 8), 256), 256, 0, stream>>>(
-        static_cast<const T*>(gate), static_cast<const T*>(up), static_cast<T*>(out), rows, h, ld_in);
-    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+    return launch_pdl(swiglu_fwd_kernel<T>, dim3(grid_for(rows * (h / 8), 256)), dim3(256), 0, stream,
+                      static_cast<const T*>(gate), static_cast<const T*>(up), static_cast<T*>(out), rows, h,
+                      ld_in) == cudaSuccess ? 0 : -3;
   });
 }
 
@@ -644,10 +668,9 @@ extern "C" int fmb_swiglu_bwd(const void* gate, const void* up, const void* dy, 
   if (h % 8 || ld_in % 8) return -2;
   return by_dtype(dtype, [&](auto* tp) {
     using T = std::remove_pointer_t<decltype(tp)>;
-    swiglu_bwd_kernel<T><<<grid_for(rows * (h / 8), 256), 256, 0, stream>>>(
-        static_cast<const T*>(gate), static_cast<const T*>(up), static_cast<const T*>(dy), static_cast<T*>(dgate),
-        static_cast<T*>(dup), rows, h, ld_in);
-    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+    return launch_pdl(swiglu_bwd_kernel<T>, dim3(grid_for(rows * (h / 8), 256)), dim3(256), 0, stream,
+                      static_cast<const T*>(gate), static_cast<const T*>(up), static_cast<const T*>(dy),
+                      static_cast<T*>(dgate), static_cast<T*>(dup), rows, h, ld_in) == cudaSuccess ? 0 : -3;
   });
 }
 
@@ -658,9 +681,9 @@ extern "C" int fmb_rope(const void* src, void* dst, const float* cos, const floa
   const int heads = src == dst ? n_rot_heads : heads_total;
   return by_dtype(dtype, [&](auto* tp) {
     using Tt = std::remove_pointer_t<decltype(tp)>;
-    rope_kernel<Tt><<<grid_for(rows * heads * (hd / 16), 256), 256, 0, stream>>>(
-        static_cast<const Tt*>(src), static_cast<Tt*>(dst), cos, sin, rows, T, n_rot_heads, heads_total, hd, sign);
-    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+    return launch_pdl(rope_kernel<Tt>, dim3(grid_for(rows * heads * (hd / 16), 256)), dim3(256), 0, stream,
+                      static_cast<const Tt*>(src), static_cast<Tt*>(dst), cos, sin, rows, T, n_rot_heads, heads_total,
+                      hd, sign) == cudaSuccess ? 0 : -3;
   });
 }
 
@@ -704,7 +727,7 @@ extern "C" int fmb_qk_norm_rope_bwd(const void* dy, const void* x, const void* w
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
   });
   if (rc != 0) return rc;
-  colsum_kernel<<<(hd + 127) / 128, 128, 0, stream>>>(dw_partial, dw, nblocks, hd, 0);
+  launch_pdl(colsum_kernel, dim3((hd + 31) / 32), dim3(32, 32), 0, stream, dw_partial, dw, nblocks, hd, 0);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -756,8 +779,9 @@ extern "C" int fmb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
                                        float* dw, long long rows, int d, int dtype, int w_dtype, cudaStream_t stream) {
   static float* scratch_of_device[64] = {nullptr};
   if (rows <= 0) return 0;
-  const int nblocks = fmb_rmsnorm_bwd_blocks(rows, d);
-  if (d > FMB_NOALLOC_MAX_D || nblocks > FMB_NOALLOC_MAX_BLOCKS ||
+  int nblocks = fmb_rmsnorm_bwd_blocks(rows, d);
+  if (nblocks > FMB_NOALLOC_MAX_BLOCKS) nblocks = FMB_NOALLOC_MAX_BLOCKS;   // the kernel strides over the rows
+  if (d > FMB_NOALLOC_MAX_D ||
       static_cast<long long>(nblocks) * d > static_cast<long long>(FMB_NOALLOC_MAX_D) * FMB_NOALLOC_MAX_BLOCKS) {
     std::fprintf(stderr, "fmb_rmsnorm_bwd_noalloc: row width %d (x %d blocks) exceeds the built-in scratch "
                          "(max width %d); use fmb_rmsnorm_bwd with your own buffer\n", d, nblocks, FMB_NOALLOC_MAX_D);

@@ -12,6 +12,7 @@
 // has fewer tiles than SMs, which is the usual case for weight gradients.
 #include "ptx_sm100.cuh"
 #include "peer.cuh"
+#include "launch.cuh"
 #include "tensormap.h"
 #include "fmb_api.h"
 
@@ -161,6 +162,8 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                      // everything above touched only this CTA's shared memory and TMEM
+  pdl_launch_dependents();
 
   const int total_tiles = p.tiles_m * p.tiles_n * (p.mode == 2 ? p.n_groups : p.splits);
 
@@ -401,8 +404,7 @@ static cudaError_t launch_cfg(const MapSet<PEER>& ta, const MapSet<PEER>& tb, co
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
-  return cudaGetLastError();
+  return launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), smem, stream, ta, tb, p);
 }
 
 static double wave_eff(long long work, int sms) {

@@ -26,7 +26,7 @@ import torch.distributed as dist
 from .. import ops
 from .flat import ALIGN, Bucket, FlatAdamW, FlatParamStore, _round_up
 
-BLOCKS_PER_BUCKET = 128          # grid of one bucket's pull-reduce (also its number of partial sums)
+BLOCKS_PER_BUCKET = 296          # grid of one bucket's pull-reduce (also its number of partial sums)
 
 
 class PeerReducer:

@@ -45,7 +45,7 @@ def test_matches_regular_entry_point_twice():
         assert torch.cuda.memory_allocated() == before
         torch.cuda.synchronize()
         assert torch.equal(dx, want_dx)
-        assert torch.allclose(dw, want_dw, rtol=1e-5, atol=1e-5)
+        assert torch.allclose(dw, want_dw, rtol=1e-4, atol=1e-4)     # the two sum the rows in different groupings
 
 
 def test_refuses_rows_wider_than_the_scratch():
