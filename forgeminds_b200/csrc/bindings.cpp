@@ -376,7 +376,7 @@ void comm_adamw_push(Tensor& master, const Tensor& grad, Tensor& m, Tensor& v, c
 
 // Product with operands / output spread over the ranks (see fmb_gemm_bf16_peer). `a`, `b`, `d` are
 // this rank's tensors: a shard when the matching pointer list is non-empty, the whole matrix otherwise.
-void gemm_peer(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, double alpha, int64_t rank,
+void gemm_peer(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, double alpha, bool accumulate, int64_t rank,
                int64_t world, const std::vector<int64_t>& a_ptrs, const std::vector<int64_t>& b_ptrs,
                const std::vector<int64_t>& d_ptrs, const Tensor& flags, int64_t a_slot, int64_t a_epoch,
                int64_t b_slot, int64_t b_epoch, double timeout_ms, Tensor& status) {
@@ -407,7 +407,7 @@ void gemm_peer(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn
   c10::cuda::CUDAGuard guard(a.device());
   ok(fmb_gemm_bf16_peer(a.data_ptr(), b.data_ptr(), d.data_ptr(), static_cast<int>(M), static_cast<int>(N),
                         static_cast<int>(K), a_mn, b_mn, a.stride(0), b.stride(0), d.stride(0), d_f32,
-                        static_cast<float>(alpha), static_cast<int>(rank), static_cast<int>(world),
+                        static_cast<float>(alpha), accumulate ? 1 : 0, static_cast<int>(rank), static_cast<int>(world),
                         a_sh ? ap : nullptr, a_sh ? static_cast<int>(a.size(0)) : 0, b_sh ? bp : nullptr,
                         b_sh ? static_cast<int>(b.size(0)) : 0, d_sh ? dp : nullptr,
                         d_sh ? static_cast<int>(d.size(0)) : 0,

@@ -644,8 +644,8 @@ extern "C" int fmb_gemm_bf16_grouped(const void* A, const void* B, void* D, cons
 //   d_ptrs            fp32 reduce-scatter destinations, [d_rows_per_rank, N] on each rank (null: local D)
 //   flags             this rank's flag words; slot < 0 means "do not wait"
 extern "C" int fmb_gemm_bf16_peer(const void* A, const void* B, void* D, int M, int N, int K, int a_mn, int b_mn,
-                                  long long lda, long long ldb, long long ldd, int d_f32, float alpha, int rank,
-                                  int world, const void* const* a_ptrs, int a_rows_per_src,
+                                  long long lda, long long ldb, long long ldd, int d_f32, float alpha, int accumulate,
+                                  int rank, int world, const void* const* a_ptrs, int a_rows_per_src,
                                   const void* const* b_ptrs, int b_rows_per_src, void* const* d_ptrs,
                                   int d_rows_per_rank, const unsigned* flags, int a_slot, unsigned a_epoch,
                                   int b_slot, unsigned b_epoch, unsigned long long timeout_ns, int* status,
@@ -663,6 +663,7 @@ extern "C" int fmb_gemm_bf16_peer(const void* A, const void* B, void* D, int M, 
   const void* a0 = a_ptrs != nullptr ? a_ptrs[rank] : A;
   const void* b0 = b_ptrs != nullptr ? b_ptrs[rank] : B;
   void* d0 = d_ptrs != nullptr ? d_ptrs[rank] : D;
-  return run_gemm(a0, b0, d0, nullptr, M, N, K, a_mn, b_mn, lda, ldb, ldd, 0, d_f32, 0, alpha, 0.f, nullptr, 0, status,
-                  0, gs, stream, &ps);
+  const bool acc = accumulate && d_ptrs == nullptr;      // D += product (local output only)
+  return run_gemm(a0, b0, d0, acc ? d0 : nullptr, M, N, K, a_mn, b_mn, lda, ldb, ldd, acc ? ldd : 0, d_f32,
+                  acc ? d_f32 : 0, alpha, acc ? 1.f : 0.f, nullptr, 0, status, 0, gs, stream, &ps);
 }

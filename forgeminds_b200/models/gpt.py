@@ -164,7 +164,8 @@ class Attention(nn.Module):
         B, T, _ = x.shape
         hd = self.hd
         n_q, n_kv = self.wq.weight.shape[0] // hd, self.wk.weight.shape[0] // hd
-        qkv = Fn.norm_linear_multi(x, norm.weight, norm.eps, (self.wq.weight, self.wk.weight, self.wv.weight))
+        qkv, x = Fn.norm_linear_multi(x, norm.weight, norm.eps, (self.wq.weight, self.wk.weight, self.wv.weight),
+                                      passthrough=True)
         cos, sin = rope_tables(T, hd, self.theta, x.device, torch.float32)
         qkv = Fn.rope_qkv_(qkv, cos.reshape(T, hd // 2), sin.reshape(T, hd // 2), n_q, n_kv, hd)
         o = Fn.attention_qkv(qkv, n_q, n_kv, hd, True)
@@ -184,7 +185,7 @@ class SwiGLU(nn.Module):
     def forward_native(self, x, norm):
         """``x + mlp(norm(x))``; the norm output and the activation are recomputed in the backward."""
         from ..ops import functional as Fn
-        gu = Fn.norm_linear_multi(x, norm.weight, norm.eps, (self.w1.weight, self.w3.weight))
+        gu, x = Fn.norm_linear_multi(x, norm.weight, norm.eps, (self.w1.weight, self.w3.weight), passthrough=True)
         return Fn.swiglu_linear(gu, self.w2.weight, x)
 
 
@@ -261,10 +262,16 @@ class GPT(nn.Module):
         else:
             h = self.tok_emb(tokens)
         aux = None
-        for blk in self.layers.values():
-            h = blk(h)
-            if blk.is_moe and blk.ffn.last_aux is not None:
-                aux = blk.ffn.last_aux if aux is None else aux + blk.ffn.last_aux
+        tp_state = getattr(self, "_fm_tp", None)
+        if tp_state is not None and not isinstance(tp_state, str):
+            # sequence-parallel blocks over peer memory (parallel/tp.py); weights are this rank's slices
+            from ..parallel import tp as fused_tp
+            h = fused_tp.stack_forward(self, h)
+        else:
+            for blk in self.layers.values():
+                h = blk(h)
+                if blk.is_moe and blk.ffn.last_aux is not None:
+                    aux = blk.ffn.last_aux if aux is None else aux + blk.ffn.last_aux
         if self.lm_head is None:
             return h
         if h.is_cuda and h.dtype == torch.bfloat16 and _native_ok(h, self.cfg.native):

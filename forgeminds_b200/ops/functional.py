@@ -23,24 +23,45 @@ BF16 = torch.bfloat16
 
 
 # ------------------------------------------------------------------------------ helpers
+_weights_epoch = 0
+
+
+def _optimizer_stepped(*_args, **_kw) -> None:
+    global _weights_epoch
+    _weights_epoch += 1
+
+
+# torch's fused optimizers update parameters without touching their version counters, so a cached
+# bf16 copy cannot rely on ``_version`` alone: every optimizer step (of any optimizer) starts a new epoch.
+from torch.optim.optimizer import register_optimizer_step_post_hook as _register_step_hook  # noqa: E402
+
+_register_step_hook(_optimizer_stepped)
+
+
 def bf16_of(p: torch.Tensor) -> torch.Tensor:
-    """bf16 view of a parameter: itself when already bf16, else a cached shadow copy."""
+    """bf16 view of a parameter: itself when already bf16, else a cached shadow copy.
+
+    A cache entry is ``(shadow, version)`` when a flat store owns the shadow and keeps it current
+    itself, or ``(shadow, version, epoch)`` when it was made here; the latter is refreshed when the
+    parameter's version changed or any optimizer has stepped since."""
     if p.dtype == BF16:
         return p.detach()
     cached = getattr(p, "_fm_shadow", None)
     if cached is not None and cached[0].device == p.device and cached[0].shape == p.shape:
-        if cached[1] == p._version:
+        if cached[1] == p._version and (len(cached) == 2 or cached[2] == _weights_epoch):
             return cached[0]
         shadow = cached[0]          # refresh in place: the buffer may be a view owned by a flat store
+        managed = len(cached) == 2
     else:
         shadow = torch.empty(p.shape, dtype=BF16, device=p.device)
+        managed = False
     src = p.detach()
     if src.dtype == torch.float32 and src.is_contiguous():
         require().scale_cast(src, shadow, 1.0)
     else:
         shadow.copy_(src)
     try:
-        p._fm_shadow = (shadow, p._version)
+        p._fm_shadow = (shadow, p._version) if managed else (shadow, p._version, _weights_epoch)
     except Exception:
         pass
     return shadow
@@ -244,10 +265,14 @@ def _weight_grads(ctx_needs, weights, dy2, x2):
 
 class _NormLinearMulti(torch.autograd.Function):
     """``rms_norm(x) @ cat(weights).T``. Only ``x`` and the per-row ``rstd`` are kept; the normalised
-    activations are recomputed in the backward (one extra pass over ``x`` instead of a saved tensor)."""
+    activations are recomputed in the backward (one extra pass over ``x`` instead of a saved tensor).
+
+    With ``passthrough`` the Function also returns ``x`` itself as a second output. A block uses that
+    output for its residual connection, so the gradient of the residual stream arrives here and is
+    added inside the RMSNorm backward kernel instead of by a separate elementwise add."""
 
     @staticmethod
-    def forward(ctx, x, norm_w, eps, *weights):
+    def forward(ctx, x, norm_w, eps, passthrough, *weights):
         C = require()
         w = fused_bf16(weights)
         x2 = _rows(x)
@@ -261,30 +286,41 @@ class _NormLinearMulti(torch.autograd.Function):
         y = _gemm_like(x, h, w)
         ctx.save_for_backward(x2, nw, rstd, w)
         ctx.weights, ctx.eps, ctx.x_shape, ctx.nw_dtype = weights, eps, x.shape, norm_w.dtype
+        if passthrough:
+            return y, x.view_as(x)
         return y
 
     @staticmethod
     @once_differentiable
-    def backward(ctx, dy):
+    def backward(ctx, dy, dres=None):
         C = require()
         x2, nw, rstd, w = ctx.saved_tensors
         dy2 = _rows(dy)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         h, _ = C.rmsnorm_fwd(x2, nw, ctx.eps)                       # recompute
-        grads = _weight_grads(ctx.needs_input_grad[3:], ctx.weights, dy2, h)
+        grads = _weight_grads(ctx.needs_input_grad[4:], ctx.weights, dy2, h)
         dx = dnw = None
         if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
             dh = gemm(dy2, w, b_mn=True)
-            dx, dnw = C.rmsnorm_bwd(dh, x2, nw, rstd, None, ctx.needs_input_grad[1])
+            if dres is not None:
+                dres = _rows(dres)
+                if dres.dtype != dh.dtype:
+                    dres = dres.to(dh.dtype)
+                if not dres.is_contiguous():
+                    dres = dres.contiguous()
+            dx, dnw = C.rmsnorm_bwd(dh, x2, nw, rstd, dres, ctx.needs_input_grad[1])
             dx = dx.view(ctx.x_shape)
             if dnw is not None and dnw.dtype != ctx.nw_dtype:
                 dnw = dnw.to(ctx.nw_dtype)
-        return (dx, dnw, None, *grads)
+        elif dres is not None:
+            dx = dres
+        return (dx, dnw, None, None, *grads)
 
 
-def norm_linear_multi(x, norm_w, eps, weights):
-    return _NormLinearMulti.apply(x, norm_w, eps, *weights)
+def norm_linear_multi(x, norm_w, eps, weights, passthrough: bool = False):
+    """``passthrough=True`` returns ``(y, x)``: use the returned ``x`` for the residual connection."""
+    return _NormLinearMulti.apply(x, norm_w, eps, passthrough, *weights)
 
 
 class _SwiGLULinear(torch.autograd.Function):

@@ -1,6 +1,314 @@
-"""Fused tensor parallelism (all-gather -> GEMM, GEMM -> reduce-scatter over peer memory)."""
+"""Tensor parallelism with sequence-parallel activations, fused with its collectives.
+
+Inside the stack of blocks the residual stream is split by rows (tokens) over the ``tp`` ranks:
+rank r holds rows ``[r * Ms, (r + 1) * Ms)`` of the ``[M, d]`` activations. Every linear layer of a
+block is then one kernel that does its collective while it computes (``csrc/gemm_sm100.cu``, PEER
+instantiations):
+
+* column-parallel ``wq|wk|wv`` and ``w1|w3``: **all-gather -> GEMM**. Each rank publishes its
+  normalised rows in a symmetric buffer; the GEMM's TMA producer reads every row tile from the rank
+  that owns it (one tensor map per rank, no multicast), after a bounded wait on that rank's flag,
+  starting with its own rows so that the remote tiles arrive while the local ones are multiplied.
+* row-parallel ``wo`` and ``w2``: **GEMM -> reduce-scatter**. The epilogue adds each 128-row tile of
+  the partial product into the fp32 buffer of the rank that owns those rows (``red.global.add.v4.f32``
+  on the peer pointer), remote rows first.
+
+The backward uses the same two kernels: the input gradient of a column-parallel layer is a
+GEMM -> reduce-scatter, its weight gradient an all-gather -> GEMM with the gathered operand on the
+reduction side; for a row-parallel layer the roles swap.
+
+Buffer protocol (one :class:`TPState` per group). Two publish buffers (activations, gradients) and
+one fp32 accumulator, each ``[Ms, d]``. A publish is always separated from the previous product
+that read the same buffer by a full flag barrier (every reduce-scatter ends with one), and an
+accumulator is zeroed by its owner right after it has been read, before the owner's next publish,
+which every peer waits for before it can reach its next reduce-scatter into that accumulator.
+
+The reference expresses the same layout with DTensor ``ColwiseParallel`` / ``RowwiseParallel`` and
+NCCL all-reduces (``forgemind/parallel/native.py:21-49``); that path remains the fallback
+(:func:`usable` false: CPU, Gloo, ``fused_comm=False``, shapes that do not tile).
+"""
 from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch.autograd.function import once_differentiable
+
+from .. import ops
+
+BF16 = torch.bfloat16
 
 
 def usable(ctx) -> bool:
-    return False
+    pc = ctx.pc
+    return bool(getattr(pc, "fused_comm", True)) and ctx.device.type == "cuda" and ops.available() \
+        and 1 < pc.tp <= 8 and pc.pp == 1 and pc.ep == 1
+
+
+class TPState:
+    """Symmetric buffers, flag slots and epochs of one tensor-parallel group."""
+
+    def __init__(self, group, device, timeout_ms: float = 10000.0):
+        from .symm import SymmGroup
+        self.sg = SymmGroup(group, device, timeout_ms=timeout_ms)
+        self.group = group
+        self.rank, self.world = self.sg.rank, self.sg.world
+        self.slot_act, self.slot_grad, self.slot_bar = (self.sg.reserve_slots(1) for _ in range(3))
+        self._bufs: dict = {}
+
+    def buffers(self, rows: int, width: int):
+        """(publish-activations, publish-gradients, accumulator) for shards of ``[rows, width]``."""
+        key = (rows, width)
+        if key not in self._bufs:
+            sg = self.sg
+            self._bufs[key] = (sg.alloc(rows * width, BF16), sg.alloc(rows * width, BF16),
+                               sg.alloc(rows * width, torch.float32))
+        return self._bufs[key]
+
+    def publish(self, buf, slot: int, shard: torch.Tensor) -> int:
+        """Copy ``shard`` into the symmetric buffer and tell the peers; returns the epoch to wait for."""
+        buf.local.view(shard.shape).copy_(shard)
+        epoch = self.sg.next_epoch(slot)
+        ops.require().comm_signal(self.sg.flags.ptrs, slot, epoch, self.rank, self.sg.status)
+        return epoch
+
+    def gemm(self, a, b, out, a_mn=False, b_mn=False, accumulate=False, a_buf=None, b_buf=None, d_buf=None,
+             a_wait=(-1, 0), b_wait=(-1, 0)):
+        sg = self.sg
+        ops.require().gemm_peer(a, b, out, a_mn, b_mn, 1.0, accumulate, self.rank, self.world,
+                                a_buf.ptrs if a_buf is not None else [], b_buf.ptrs if b_buf is not None else [],
+                                d_buf.ptrs if d_buf is not None else [], sg.flags.local, a_wait[0], a_wait[1],
+                                b_wait[0], b_wait[1], sg.timeout_ms, sg.status)
+        return out
+
+    def barrier(self):
+        self.sg.barrier(self.slot_bar)
+
+
+def _main_grad_or_new(param, shape, device):
+    main = getattr(param, "_fm_main_grad", None)
+    if main is not None:
+        return main, True
+    return torch.empty(shape, dtype=torch.float32, device=device), False
+
+
+class _GatherLinear(torch.autograd.Function):
+    """``all_gather_rows(x_shard) @ W_local.T`` -> ``[M, N_local]`` (column-parallel layer)."""
+
+    @staticmethod
+    def forward(ctx, x_shard, weight, tp: TPState):
+        from ..ops.functional import bf16_of
+        w = bf16_of(weight)
+        ms, k = x_shard.shape
+        act, _, _ = tp.buffers(ms, k)
+        epoch = tp.publish(act, tp.slot_act, x_shard)
+        y = torch.empty((ms * tp.world, w.shape[0]), dtype=BF16, device=x_shard.device)
+        tp.gemm(act.local.view(ms, k), w, y, a_buf=act, a_wait=(tp.slot_act, epoch))
+        ctx.save_for_backward(x_shard, w)
+        ctx.tp, ctx.weight = tp, weight
+        return y
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dy):
+        x_shard, w = ctx.saved_tensors
+        tp, weight = ctx.tp, ctx.weight
+        ms, k = x_shard.shape
+        act, _, acc = tp.buffers(ms, k)
+        dy = dy.contiguous()
+        dw = None
+        if ctx.needs_input_grad[1]:
+            # dW[N_l, K] = dy[M, N_l].T @ gather(x)[M, K]: the gathered operand is on the reduction side
+            epoch = tp.publish(act, tp.slot_act, x_shard)
+            out, is_main = _main_grad_or_new(weight, w.shape, dy.device)
+            tp.gemm(dy, act.local.view(ms, k), out, a_mn=True, b_mn=True, accumulate=is_main, b_buf=act,
+                    b_wait=(tp.slot_act, epoch))
+            dw = None if is_main else out.to(weight.dtype)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            # dx_shard = reduce_scatter_rows(dy @ W_local)
+            tp.gemm(dy, w, acc.local.view(ms, k), b_mn=True, d_buf=acc)
+            tp.barrier()
+            dx = acc.local.view(ms, k).to(BF16)
+            acc.local.zero_()
+        return dx, dw, None
+
+
+class _LinearScatter(torch.autograd.Function):
+    """``reduce_scatter_rows(h @ W_local.T) (+ residual_shard)`` -> ``[Ms, N]`` (row-parallel layer)."""
+
+    @staticmethod
+    def forward(ctx, h, weight, residual, tp: TPState):
+        from ..ops.functional import bf16_of
+        w = bf16_of(weight)
+        m, n = h.shape[0], w.shape[0]
+        ms = m // tp.world
+        _, _, acc = tp.buffers(ms, n)
+        h = h.contiguous()
+        tp.gemm(h, w, acc.local.view(ms, n), d_buf=acc)
+        tp.barrier()
+        out = acc.local.view(ms, n).to(BF16)
+        acc.local.zero_()
+        if residual is not None:
+            out += residual
+        ctx.save_for_backward(h, w)
+        ctx.tp, ctx.weight, ctx.has_res = tp, weight, residual is not None
+        return out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dout):
+        h, w = ctx.saved_tensors
+        tp, weight = ctx.tp, ctx.weight
+        ms, n = dout.shape
+        _, grad, _ = tp.buffers(ms, n)
+        dout = dout.contiguous()
+        epoch = tp.publish(grad, tp.slot_grad, dout)
+        dh = dw = None
+        if ctx.needs_input_grad[0]:
+            # dh[M, K_l] = gather(dout)[M, N] @ W_local[N, K_l]
+            dh = torch.empty_like(h)
+            tp.gemm(grad.local.view(ms, n), w, dh, b_mn=True, a_buf=grad, a_wait=(tp.slot_grad, epoch))
+        if ctx.needs_input_grad[1]:
+            # dW[N, K_l] = gather(dout)[M, N].T @ h[M, K_l]
+            out, is_main = _main_grad_or_new(weight, w.shape, dout.device)
+            tp.gemm(grad.local.view(ms, n), h, out, a_mn=True, b_mn=True, accumulate=is_main, a_buf=grad,
+                    a_wait=(tp.slot_grad, epoch))
+            dw = None if is_main else out.to(weight.dtype)
+        return dh, dw, (dout if ctx.has_res else None), None
+
+
+def gather_linear(x_shard, weight, tp: TPState):
+    return _GatherLinear.apply(x_shard, weight, tp)
+
+
+def linear_scatter(h, weight, residual, tp: TPState):
+    return _LinearScatter.apply(h, weight, residual, tp)
+
+
+class _TakeShard(torch.autograd.Function):
+    """Rows ``[r * Ms, (r + 1) * Ms)`` of a replicated ``[M, d]`` tensor; the gradient of the other rows
+    is produced by the ranks that own them."""
+
+    @staticmethod
+    def forward(ctx, x, rank, world):
+        ms = x.shape[0] // world
+        ctx.meta = (rank, world, x.shape)
+        return x[rank * ms:(rank + 1) * ms].contiguous()
+
+    @staticmethod
+    def backward(ctx, dx):
+        rank, world, shape = ctx.meta
+        full = dx.new_zeros(shape)
+        ms = shape[0] // world
+        full[rank * ms:(rank + 1) * ms] = dx
+        return full, None, None
+
+
+class _GatherRows(torch.autograd.Function):
+    """All-gather of row shards (NCCL); the consumer runs replicated, so the backward keeps this rank's rows."""
+
+    @staticmethod
+    def forward(ctx, x_shard, group, rank, world):
+        out = x_shard.new_empty((x_shard.shape[0] * world,) + tuple(x_shard.shape[1:]))
+        dist.all_gather_into_tensor(out, x_shard.contiguous(), group=group)
+        ctx.meta = (rank, world)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        rank, world = ctx.meta
+        ms = dout.shape[0] // world
+        return dout[rank * ms:(rank + 1) * ms].contiguous(), None, None, None
+
+
+# ---------------------------------------------------------------------------------------------- model surgery
+def _shard_rows(linear, lo, hi):
+    w = linear.weight.data[lo:hi].clone()
+    linear.weight = torch.nn.Parameter(w)
+    linear.out_features = hi - lo
+    linear.weight._tp_shard_dim = 0
+
+
+def _shard_cols(linear, lo, hi):
+    w = linear.weight.data[:, lo:hi].clone()
+    linear.weight = torch.nn.Parameter(w)
+    linear.in_features = hi - lo
+    linear.weight._tp_shard_dim = 1
+
+
+def shard_model(model, ctx, plan=None):
+    """Give every block its slice of the attention heads and of the MLP width and switch the model
+    to the sequence-parallel forward. Parameters that stay replicated but see only this rank's rows
+    (block norms, embedding) are marked: their gradients are summed over the group before clipping
+    (:func:`sync_partial_grads`)."""
+    cfg = model.cfg
+    tp, rank = ctx.pc.tp, ctx.tp_rank
+    hd = cfg.dim // cfg.n_heads
+    state = TPState(ctx.tp_group, ctx.device, timeout_ms=float(getattr(ctx.pc, "comm_timeout_ms", 10000)))
+    for blk in model.layers.values():
+        at, ff = blk.attn, blk.ffn
+        if not hasattr(at, "wq") or not hasattr(ff, "w1"):
+            raise RuntimeError("fused tensor parallelism covers attention + SwiGLU blocks")
+        nq, nkv = cfg.n_heads // tp, cfg.n_kv_heads // tp
+        _shard_rows(at.wq, rank * nq * hd, (rank + 1) * nq * hd)
+        _shard_rows(at.wk, rank * nkv * hd, (rank + 1) * nkv * hd)
+        _shard_rows(at.wv, rank * nkv * hd, (rank + 1) * nkv * hd)
+        _shard_cols(at.wo, rank * nq * hd, (rank + 1) * nq * hd)
+        hidden = ff.w1.weight.shape[0]
+        if hidden % tp:
+            raise ValueError(f"MLP width {hidden} does not divide over tp={tp}")
+        hl = hidden // tp
+        _shard_rows(ff.w1, rank * hl, (rank + 1) * hl)
+        _shard_rows(ff.w3, rank * hl, (rank + 1) * hl)
+        _shard_cols(ff.w2, rank * hl, (rank + 1) * hl)
+        blk.attn_norm.weight._tp_partial = True
+        blk.ffn_norm.weight._tp_partial = True
+        blk._fm_tp = state
+    model.tok_emb.weight._tp_partial = True
+    model._fm_tp = state
+    return model
+
+
+def sync_partial_grads(model, state: TPState) -> None:
+    """Sum, over the tensor-parallel group, the gradients of replicated parameters that were computed
+    from this rank's rows only."""
+    grads = [p.grad for p in model.parameters() if getattr(p, "_tp_partial", False) and p.grad is not None]
+    for g in grads:
+        dist.all_reduce(g, group=state.group)
+
+
+def block_forward(blk, x_shard, state: TPState):
+    """One transformer block on a row shard ``[Ms, d]`` of the residual stream."""
+    from ..models.gpt import rope_tables
+    from ..ops import functional as Fn
+    at, ff = blk.attn, blk.ffn
+    hd = at.hd
+    nq, nkv = at.wq.weight.shape[0] // hd, at.wk.weight.shape[0] // hd
+    xn = Fn.rms_norm(x_shard, blk.attn_norm.weight, blk.attn_norm.eps)
+    wqkv = torch.cat([at.wq.weight, at.wk.weight, at.wv.weight], dim=0)     # autograd splits the gradient again
+    qkv = gather_linear(xn, wqkv, state)                       # [M, (nq + 2 nkv) * hd]
+    B, T = blk._fm_bt
+    qkv = qkv.view(B, T, -1)
+    cos, sin = rope_tables(T, hd, at.theta, qkv.device, torch.float32)
+    qkv = Fn.rope_qkv_(qkv, cos.reshape(T, hd // 2), sin.reshape(T, hd // 2), nq, nkv, hd)
+    o = Fn.attention_qkv(qkv, nq, nkv, hd, True)               # [B, T, nq * hd]
+    h = linear_scatter(o.reshape(B * T, nq * hd), at.wo.weight, x_shard, state)
+    hn = Fn.rms_norm(h, blk.ffn_norm.weight, blk.ffn_norm.eps)
+    w13 = torch.cat([ff.w1.weight, ff.w3.weight], dim=0)
+    gu = gather_linear(hn, w13, state)                         # [M, 2 * hidden_local]
+    act = Fn.swiglu_split(gu)
+    return linear_scatter(act, ff.w2.weight, h, state)
+
+
+def stack_forward(model, x):
+    """Blocks of ``model`` on ``x [B, T, d]`` (replicated): shard rows, run the blocks, gather."""
+    state = model._fm_tp
+    B, T, d = x.shape
+    if (B * T) % (128 * state.world):
+        raise ValueError(f"fused tensor parallelism needs B*T ({B * T}) to be a multiple of {128 * state.world}")
+    xs = _TakeShard.apply(x.reshape(B * T, d).to(BF16), state.rank, state.world)
+    for blk in model.layers.values():
+        blk._fm_bt = (B, T)
+        xs = block_forward(blk, xs, state)
+    full = _GatherRows.apply(xs, state.group, state.rank, state.world)
+    return full.view(B, T, d)

@@ -146,8 +146,11 @@ class Trainer:
             elif tc.optimizer == "muon":
                 self.opt = self._muon(self.model, tc)
             else:
+                kinds = {hasattr(p, "to_local") for p in trainable}
+                # the fused kernel refuses a mix of DTensor and plain parameters (tensor parallel blocks
+                # next to a replicated embedding): such models take the foreach implementation
                 self.opt = torch.optim.AdamW(groups, lr=tc.lr, betas=tc.betas, eps=tc.eps,
-                                             fused=ctx.device.type == "cuda")
+                                             fused=ctx.device.type == "cuda" and len(kinds) == 1)
         self.is_ddp = isinstance(self.model, nn.parallel.DistributedDataParallel)
         self.is_fsdp = hasattr(self.model, "set_requires_gradient_sync") and not self.is_ddp
         self._trainable = [p for p in self.model.parameters() if p.requires_grad]
@@ -336,6 +339,15 @@ class Trainer:
             norm = sq.sqrt()
         else:
             norm = torch.nn.utils.get_total_norm(grads).float()
+        tp_state = getattr(self.raw, "_fm_tp", None)
+        if tp_state is not None and not isinstance(tp_state, str):
+            # fused tensor parallelism keeps plain tensors: the sharded weights' share of the norm is
+            # spread over the tp ranks, everything else is replicated
+            mine = [p.grad for p in self._trainable if p.grad is not None and hasattr(p, "_tp_shard_dim")]
+            s_sq = torch.nn.utils.get_total_norm(mine).float().pow(2) if mine else torch.zeros((), device=norm.device)
+            rep_sq = norm.pow(2) - s_sq
+            dist.all_reduce(s_sq, group=ctx.tp_group)
+            norm = (rep_sq + s_sq).clamp(min=0).sqrt()
         if pc.ep > 1 and ctx.world > 1:      # expert gradients of the other ep ranks belong to the same model
             mine = [p.grad for p in self._expert_params if p.grad is not None]
             e_sq = torch.nn.utils.get_total_norm(mine).float().pow(2) if mine else torch.zeros((), device=norm.device)
@@ -406,6 +418,10 @@ class Trainer:
                 gn, loss, flag = stats[0], stats[1], stats[2]
             else:
                 native.sync_expert_grads(self.model, ctx, self._expert_params)
+                tp_state = getattr(self.raw, "_fm_tp", None)
+                if tp_state is not None and not isinstance(tp_state, str):
+                    from .parallel import tp as fused_tp
+                    fused_tp.sync_partial_grads(self.raw, tp_state)
                 gn = self._clip().to(ctx.device)
                 loss = self._reduce_loss(loss)
                 if tc.skip_nonfinite:

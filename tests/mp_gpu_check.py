@@ -145,7 +145,7 @@ def gemm_peer():
     # 1. AG -> GEMM (A K-major, rows spread over the ranks): y = gather(x) @ w.T
     C.comm_signal(sg.flags.ptrs, slot, sg.next_epoch(slot), rank, sg.status)
     y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-    C.gemm_peer(x_sh.local.view(Ms, K), w, y, False, False, 1.0, rank, world, x_sh.ptrs, [], [], sg.flags.local,
+    C.gemm_peer(x_sh.local.view(Ms, K), w, y, False, False, 1.0, False, rank, world, x_sh.ptrs, [], [], sg.flags.local,
                 slot, sg._epochs[slot], -1, 0, sg.timeout_ms, sg.status)
     want = x_full.float() @ w.float().T
     torch.cuda.synchronize()
@@ -155,7 +155,7 @@ def gemm_peer():
     #    dw[N, K] = dy[M, N].T @ gather(x)[M, K]
     dy = rand((M, N), 7 + rank)
     dw = torch.empty(N, K, dtype=torch.float32, device=dev)
-    C.gemm_peer(dy, x_sh.local.view(Ms, K), dw, True, True, 1.0, rank, world, [], x_sh.ptrs, [], sg.flags.local,
+    C.gemm_peer(dy, x_sh.local.view(Ms, K), dw, True, True, 1.0, False, rank, world, [], x_sh.ptrs, [], sg.flags.local,
                 -1, 0, slot, sg._epochs[slot], sg.timeout_ms, sg.status)
     want = dy.float().T @ x_full.float()
     torch.cuda.synchronize()
@@ -163,7 +163,7 @@ def gemm_peer():
     assert (dw - want).abs().max() < 0.02 * want.abs().max()
     # 3. the same with the gathered operand on the A side: dw2[K, N] = gather(x).T @ dy
     dw2 = torch.empty(K, N, dtype=torch.float32, device=dev)
-    C.gemm_peer(x_sh.local.view(Ms, K), dy, dw2, True, True, 1.0, rank, world, x_sh.ptrs, [], [], sg.flags.local,
+    C.gemm_peer(x_sh.local.view(Ms, K), dy, dw2, True, True, 1.0, False, rank, world, x_sh.ptrs, [], [], sg.flags.local,
                 slot, sg._epochs[slot], -1, 0, sg.timeout_ms, sg.status)
     torch.cuda.synchronize()
     sg.check()
@@ -173,7 +173,7 @@ def gemm_peer():
     h = rand((M, K), 50 + rank)
     acc = sg.alloc(Ms * N, torch.float32)
     sg.barrier(slot + 1)                           # everybody's accumulator is zero
-    C.gemm_peer(h, w, acc.local.view(Ms, N), False, False, 1.0, rank, world, [], [], acc.ptrs, sg.flags.local,
+    C.gemm_peer(h, w, acc.local.view(Ms, N), False, False, 1.0, False, rank, world, [], [], acc.ptrs, sg.flags.local,
                 -1, 0, -1, 0, sg.timeout_ms, sg.status)
     sg.barrier(slot + 2)                           # all partial products have landed
     torch.cuda.synchronize()
@@ -185,6 +185,72 @@ def gemm_peer():
     dist.barrier()
     if rank == 0:
         print("OK gemm_peer", flush=True)
+
+
+def tp_grads():
+    """Loss and every gradient of the sharded, sequence-parallel model equal those of the whole model."""
+    import copy
+    import types
+    from forgeminds_b200.parallel import tp as fused_tp
+    rank, world, dev = _init()
+    torch.manual_seed(0)
+    mc = fm.GPTConfig(vocab_size=512, dim=128, n_layers=2, n_heads=4, n_kv_heads=2, max_seq=128, ffn_hidden=384)
+    whole = fm.GPT(mc).to(dev)
+    part = copy.deepcopy(whole)
+    ctx = types.SimpleNamespace(pc=types.SimpleNamespace(tp=world, comm_timeout_ms=5000), tp_rank=rank,
+                                tp_group=dist.group.WORLD, device=dev)
+    fused_tp.shard_model(part, ctx)
+    g = torch.Generator(device=dev).manual_seed(5)
+    tok = torch.randint(0, 512, (4, 128), device=dev, generator=g)
+    lab = torch.randint(0, 512, (4, 128), device=dev, generator=g)
+    for step in range(2):                       # twice: buffers and flags are reused
+        for m in (whole, part):
+            m.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss, _ = m(tok, labels=lab)
+            loss.backward()
+            m._last = loss.item()
+        fused_tp.sync_partial_grads(part, part._fm_tp)
+        torch.cuda.synchronize()
+        part._fm_tp.sg.check()
+        assert abs(whole._last - part._last) < 2e-2, (whole._last, part._last)
+        full = dict(whole.named_parameters())
+        for name, p in part.named_parameters():
+            want = full[name].grad.float()
+            dim = getattr(p, "_tp_shard_dim", None)
+            if dim is not None:
+                n = p.shape[dim]
+                want = want.narrow(dim, rank * n, n)
+            got = p.grad.float()
+            rel = (got - want).norm() / want.norm().clamp(min=1e-6)
+            assert rel < 8e-2, f"step {step} {name}: relative gradient error {rel.item():.3f}"
+    dist.barrier()
+    if rank == 0:
+        print("OK tp_grads", flush=True)
+
+
+def tp_fused():
+    """Sequence-parallel blocks on the fused kernels follow the DTensor tensor-parallel run."""
+    rank, world, dev = _init()
+    losses = {}
+    for fused in (True, False):
+        cfg = fm.ForgeConfig()
+        cfg.parallel.tp = world
+        cfg.parallel.fused_comm = fused
+        cfg.train.__dict__.update(max_steps=10, grad_accum=2, lr=3e-3, warmup_steps=3, bf16=True, resume=False,
+                                  log_every=1000, prefetch=False, ckpt_every=0, native=None if fused else False)
+        mc = fm.GPTConfig(vocab_size=512, dim=128, n_layers=2, n_heads=4, n_kv_heads=2, max_seq=128, ffn_hidden=384)
+        tr = fm.Trainer(lambda ctx: fm.GPT(mc), cfg, fm.SyntheticLM(512, 128, n=512), micro_batch=4)
+        is_fused = not isinstance(getattr(tr.raw, "_fm_tp", "dtensor"), str)
+        assert is_fused == fused, getattr(tr.raw, "_fm_tp", None)
+        hist = tr.fit()
+        tr.close()
+        losses[fused] = [h["loss"] for h in hist]
+    a, b = losses[True], losses[False]
+    assert a[-1] < 0.85 * a[0], a
+    assert max(abs(x - y) for x, y in zip(a, b)) < 0.08, (a, b)
+    if rank == 0:
+        print("OK tp_fused", flush=True)
 
 
 if __name__ == "__main__":

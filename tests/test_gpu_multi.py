@@ -37,6 +37,16 @@ def test_gemm_with_gathered_operands_and_scattered_output_two_ranks():
     _run("gemm_peer", 2, 29613)
 
 
+@needs2
+def test_fused_tensor_parallel_gradients_two_ranks():
+    _run("tp_grads", 2, 29615)
+
+
+@needs2
+def test_fused_tensor_parallel_two_ranks():
+    _run("tp_fused", 2, 29614)
+
+
 def test_peer_step_single_rank(cuda_status):
     """World of one: the same kernels, peer tables of length one."""
     import forgeminds_b200 as fm
