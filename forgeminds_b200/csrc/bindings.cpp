@@ -313,6 +313,56 @@ void ns_axpby(const Tensor& x, const Tensor& y, Tensor& out, double a, double b)
                   dt(x), cur_stream()), "ns_axpby");
 }
 
+// ---- 8-bit products. kind: 0 = int8, 1 = fp8 e4m3. Quantised tensors travel as uint8.
+std::vector<Tensor> quant_rows(const Tensor& x, int64_t kind, int64_t block) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1, "quant_rows: 2-D CUDA tensor with contiguous rows");
+  const int64_t rows = x.size(0), cols = x.size(1);
+  TORCH_CHECK(cols % 16 == 0, "quant_rows: the row length must be a multiple of 16");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor q = torch::empty({rows, cols}, x.options().dtype(at::kByte));
+  const int64_t nb = block > 0 ? (cols + block - 1) / block : 1;
+  Tensor scale = block > 0 ? torch::empty({rows, nb}, x.options().dtype(at::kFloat))
+                           : torch::empty({rows}, x.options().dtype(at::kFloat));
+  ok(fmb_quant_rows(x.data_ptr(), q.data_ptr(), scale.data_ptr<float>(), rows, static_cast<int>(cols), x.stride(0),
+                    dt(x), static_cast<int>(kind), static_cast<int>(block), cur_stream()), "quant_rows");
+  return {q, scale};
+}
+
+std::vector<Tensor> quant_tiles_fp8(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1, "quant_tiles_fp8: 2-D CUDA tensor with contiguous rows");
+  const int64_t rows = x.size(0), cols = x.size(1);
+  TORCH_CHECK(cols % 16 == 0, "quant_tiles_fp8: the row length must be a multiple of 16");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor q = torch::empty({rows, cols}, x.options().dtype(at::kByte));
+  Tensor scale = torch::empty({(rows + 127) / 128, (cols + 127) / 128}, x.options().dtype(at::kFloat));
+  ok(fmb_quant_tiles_fp8(x.data_ptr(), q.data_ptr(), scale.data_ptr<float>(), static_cast<int>(rows),
+                         static_cast<int>(cols), x.stride(0), dt(x), cur_stream()), "quant_tiles_fp8");
+  return {q, scale};
+}
+
+// out[M, N] = (a_q[M, K] * sa) @ (b_q[N, K] * sb).T ; row scales when sa is 1-D, block scales (fp8) when 2-D.
+Tensor gemm8(const Tensor& a_q, const Tensor& b_q, const Tensor& sa, const Tensor& sb, int64_t kind, bool out_f32,
+             Tensor& status) {
+  TORCH_CHECK(a_q.is_cuda() && b_q.is_cuda() && a_q.scalar_type() == at::kByte && b_q.scalar_type() == at::kByte);
+  TORCH_CHECK(a_q.dim() == 2 && b_q.dim() == 2 && a_q.size(1) == b_q.size(1) && a_q.stride(1) == 1 && b_q.stride(1) == 1);
+  TORCH_CHECK(sa.scalar_type() == at::kFloat && sb.scalar_type() == at::kFloat && sa.is_contiguous() && sb.is_contiguous());
+  const int64_t M = a_q.size(0), N = b_q.size(0), K = a_q.size(1);
+  const bool blocked = sa.dim() == 2;
+  if (blocked) {
+    TORCH_CHECK(sb.dim() == 2 && sa.size(0) == M && sb.size(0) == (N + 127) / 128, "gemm8: block scale shapes");
+  } else {
+    TORCH_CHECK(sa.numel() == M && sb.numel() == N, "gemm8: row scale shapes");
+  }
+  c10::cuda::CUDAGuard guard(a_q.device());
+  Tensor out = torch::empty({M, N}, a_q.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
+  ok(fmb_gemm8(a_q.data_ptr(), b_q.data_ptr(), out.data_ptr(), static_cast<int>(M), static_cast<int>(N),
+               static_cast<int>(K), a_q.stride(0), b_q.stride(0), out.stride(0), out_f32 ? 1 : 0,
+               static_cast<int>(kind), sa.data_ptr<float>(), sb.data_ptr<float>(),
+               blocked ? static_cast<int>(sa.size(1)) : 0, blocked ? static_cast<int>(sb.size(1)) : 0,
+               status.data_ptr<int>(), cur_stream()), "gemm8");
+  return out;
+}
+
 // ---- collectives over peer memory. Pointer tables are Python lists of ints (one device address per rank).
 struct PtrTable {
   const void* p[FMB_MAX_PEERS];
@@ -624,6 +674,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("comm_step_reduce", &comm_step_reduce);
   m.def("comm_adamw_push", &comm_adamw_push);
   m.def("comm_barrier", &comm_barrier);
+  m.def("quant_rows", &quant_rows);
+  m.def("quant_tiles_fp8", &quant_tiles_fp8);
+  m.def("gemm8", &gemm8);
   m.def("comm_signal", &comm_signal);
   m.def("gemm_peer", &gemm_peer);
   m.def("comm_adam_chunk", []() { return fmb_comm_adam_chunk(); });

@@ -89,6 +89,15 @@ int fmb_attn_bwd(const void* q, const void* k, const void* v, const void* o, con
                  long long q_stride_t, long long kv_stride_t, long long o_stride_t, long long dq_stride_t,
                  long long dkv_stride_t, float scale, int causal, int* status, cudaStream_t stream);
 
+// ---- 8-bit GEMMs and their quantisers (gemm8_sm100.cu)
+int fmb_gemm8(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb, long long ldd,
+              int d_f32, int kind, const float* sa, const float* sb, int sa_ld, int sb_ld, int* status,
+              cudaStream_t stream);
+int fmb_quant_rows(const void* x, void* q, float* scale, long long rows, int cols, long long ldx, int dtype, int kind,
+                   int block, cudaStream_t stream);
+int fmb_quant_tiles_fp8(const void* x, void* q, float* scale, int rows, int cols, long long ldx, int dtype,
+                        cudaStream_t stream);
+
 // ---- collectives over peer memory, fused with what follows them (comm.cu)
 // `*_ptrs` are HOST arrays of `world` device pointers: the same symmetric buffer as mapped for each
 // rank. Flags are uint32 epochs, FMB_MAX_PEERS per slot, zero before first use; `epoch` must grow by

@@ -1,0 +1,417 @@
+// 8-bit GEMMs for sm_100a: D[M,N] = scale_a * scale_b * sum_k A(m,k) * B(n,k), A and B K-major,
+// int8 (tcgen05 kind::i8, int32 accumulation) or fp8 e4m3 (kind::f8f6f4, fp32 accumulation).
+//
+// Same machine as the bf16 kernel (gemm_sm100.cu): one persistent CTA per SM; warp 0 feeds a ring of
+// 128B-swizzled shared-memory stages with TMA, warp 1 issues tcgen05.mma into TMEM, warps 2-5 drain
+// TMEM. A stage holds 128 rows x 128 bytes of each operand, i.e. 128 elements of K, four MMAs of K=32.
+//
+// Two scaling schemes:
+//   row scales      one fp32 scale per row of A and per row of B (per token / per output channel).
+//                   The scales factor out of the sum, so the product accumulates in TMEM over all of
+//                   K and is scaled once in the epilogue.
+//   block scales    fp8 only: A has a scale per row and 128-wide K block, B a scale per 128 x 128
+//                   block. They do not factor out, so every K block is multiplied into its own TMEM
+//                   buffer (two alternate), and the epilogue warps add it, scaled, into fp32 registers
+//                   while the tensor core works on the next block.
+//
+// The reference reaches these products through torchao / Transformer Engine when they are installed
+// (forgemind/quant.py:93-154).
+#include <cuda_fp8.h>
+
+#include "ptx_sm100.cuh"
+#include "launch.cuh"
+#include "tensormap.h"
+#include "fmb_api.h"
+
+namespace fmb {
+
+constexpr int G8_BM = 128, G8_BN = 128, G8_BK = 128, G8_STAGES = 6, G8_THREADS = 192;
+
+struct G8Params {
+  int M, N;
+  int tiles_m, tiles_n, kblocks;
+  void* D;
+  long long ldd;
+  int d_f32;
+  const float* sa;      // row scales [M] or block scales [M, sa_ld]
+  const float* sb;      // row scales [N] or block scales [ceil(N/128), sb_ld]
+  int sa_ld, sb_ld;
+  int* status;
+};
+
+struct G8Smem {
+  static constexpr uint32_t A_BYTES = G8_BM * G8_BK;
+  static constexpr uint32_t B_BYTES = G8_BN * G8_BK;
+  static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr uint32_t BAR_OFFSET = G8_STAGES * STAGE_BYTES;
+  static constexpr uint32_t TOTAL = BAR_OFFSET + (2 * G8_STAGES + 4) * 8 + 16 + 1024;
+};
+
+// KIND: 0 = int8, 1 = fp8 e4m3.  BLOCKED: per-K-block scales (fp8 only).
+template <int KIND, bool BLOCKED>
+__global__ void __launch_bounds__(G8_THREADS, 1)
+gemm8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, G8Params p) {
+  using L = G8Smem;
+  constexpr int BM = G8_BM, BN = G8_BN, BK = G8_BK, STAGES = G8_STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::BAR_OFFSET + (2 * STAGES + 4) * 8);
+  AbortState* ab = reinterpret_cast<AbortState*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(tfull_bar(s), 1); mbar_init(tempty_bar(s), 4); }
+    ab->flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) { tmem_alloc<2 * BN>(smem_u32(tmem_slot)); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+  pdl_launch_dependents();
+
+  const int total_tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int m_blk = tile % p.tiles_m, n_blk = tile / p.tiles_m;
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, ab, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t sA = smem_base + stage * L::STAGE_BYTES, sB = sA + L::A_BYTES;
+          mbar_expect_tx(full_bar(stage), L::STAGE_BYTES);
+          armed |= 1u << stage;
+          armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+          tma_load_2d(sA, &tmA, full_bar(stage), kb * BK, m_blk * BM);
+          tma_load_2d(sB, &tmB, full_bar(stage), kb * BK, n_blk * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok || ab->flag) {
+        for (int s = 0; s < STAGES; ++s) {
+          if (!(armed & (1u << s))) continue;
+          const uint32_t par = (armed_parity >> s) & 1u;
+          for (int it = 0; it < 200000 && !mbar_try_wait(full_bar(s), par); ++it) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = KIND == 0 ? umma_idesc(BM, BN, 1, 1, 2, false, false)
+                                           : umma_idesc(BM, BN, 0, 0, 1, false, false);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        if constexpr (!BLOCKED) {
+          if (!mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, ab, p.status, ERR_WAIT_TMEM_EMPTY)) break;
+          tc_fence_after();
+        }
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if constexpr (BLOCKED) {
+            if (!mbar_wait_bounded(tempty_bar(acc), acc_phase ^ 1u, ab, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+            tc_fence_after();
+          }
+          if (!mbar_wait_bounded(full_bar(stage), phase, ab, p.status, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_base + stage * L::STAGE_BYTES, sB = sA + L::A_BYTES;
+          const uint32_t d_tmem = tmem_base + acc * BN;
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k) {
+            const uint64_t da = umma_smem_desc_sw128(sA + k * 32u, 16u, 1024u);
+            const uint64_t db = umma_smem_desc_sw128(sB + k * 32u, 16u, 1024u);
+            const uint32_t accumulate = BLOCKED ? (k > 0 ? 1u : 0u) : ((kb > 0 || k > 0) ? 1u : 0u);
+            if constexpr (KIND == 0) umma_i8_ss(d_tmem, da, db, idesc, accumulate);
+            else                     umma_f8_ss(d_tmem, da, db, idesc, accumulate);
+          }
+          umma_commit(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if constexpr (BLOCKED) {
+            umma_commit(tfull_bar(acc));
+            acc ^= 1u;
+            if (acc == 0) acc_phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        if constexpr (!BLOCKED) {
+          umma_commit(tfull_bar(acc));
+          acc ^= 1u;
+          if (acc == 0) acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    uint32_t acc = 0, acc_phase = 0;
+    bool ok = true;
+    // 32 finished output values of one row, columns [col0, col0 + 32)
+    auto store32 = [&](int row, int col0, const float (&v)[32]) {
+      if (col0 >= p.N) return;
+      const bool full = col0 + 32 <= p.N;
+      if (p.d_f32) {
+        float* dp = reinterpret_cast<float*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+        if (full) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            reinterpret_cast<float4*>(dp)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (col0 + i < p.N) dp[i] = v[i];
+        }
+      } else {
+        __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+        if (full) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 o;
+            o.x = pack_bf16(v[8 * i + 0], v[8 * i + 1]);
+            o.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
+            o.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]);
+            o.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
+            reinterpret_cast<uint4*>(dp)[i] = o;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (col0 + i < p.N) dp[i] = __float2bfloat16(v[i]);
+        }
+      }
+    };
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const int m_blk = tile % p.tiles_m, n_blk = tile / p.tiles_m;
+      const int row = m_blk * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      if constexpr (BLOCKED) {
+        float out[BN / 32][32];
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) out[c][i] = 0.f;
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if (!mbar_wait_bounded(tfull_bar(acc), acc_phase, ab, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const float s = (row_ok ? __ldg(p.sa + static_cast<long long>(row) * p.sa_ld + kb) : 0.f) *
+                          __ldg(p.sb + static_cast<long long>(n_blk) * p.sb_ld + kb);
+          const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_row + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) out[c][i] += __uint_as_float(r[i]) * s;
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(acc));
+          acc ^= 1u;
+          if (acc == 0) acc_phase ^= 1u;
+        }
+        if (!ok) break;
+        if (row_ok) {
+#pragma unroll
+          for (int c = 0; c < BN / 32; ++c) store32(row, n_blk * BN + c * 32, out[c]);
+        }
+      } else {
+        if (!mbar_wait_bounded(tfull_bar(acc), acc_phase, ab, p.status, ERR_WAIT_TMEM_FULL)) break;
+        tc_fence_after();
+        const float sa = row_ok ? __ldg(p.sa + row) : 0.f;
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n_blk * BN + c * 32;
+          if (col0 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_wait_ld();
+          if (!row_ok) continue;
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float x = KIND == 0 ? static_cast<float>(static_cast<int>(r[i])) : __uint_as_float(r[i]);
+            v[i] = x * sa * (col0 + i < p.N ? __ldg(p.sb + col0 + i) : 0.f);
+          }
+          store32(row, col0, v);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        acc ^= 1u;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<2 * BN>(tmem_base);
+  }
+}
+
+// ------------------------------------------------------------------ quantisers
+// One warp per row: q[r, c] = round(x[r, c] / scale[r]) with scale = amax(row) / 127 (int8) or
+// amax / 448 (e4m3). With `block` > 0 (fp8) there is one scale per row and `block`-wide column group.
+__device__ __forceinline__ uint8_t to_e4m3(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
+template <typename T, int KIND>
+__global__ void __launch_bounds__(256)
+quant_rows_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale, long long rows, int cols,
+                  long long ldx, int block, int n_blocks) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const T* xr = x + row * ldx;
+  uint8_t* qr = q + row * cols;
+  constexpr float QMAX = KIND == 0 ? 127.f : 448.f;
+  const int groups = block > 0 ? n_blocks : 1;
+  const int width = block > 0 ? block : cols;
+  for (int g = 0; g < groups; ++g) {
+    const int c0 = g * width, c1 = min(cols, c0 + width);
+    float amax = 0.f;
+    for (int c = c0 + lane; c < c1; c += 32) amax = fmaxf(amax, fabsf(static_cast<float>(xr[c])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float s = fmaxf(amax, 1e-12f) / QMAX;
+    const float inv = 1.f / s;
+    if (lane == 0) scale[row * groups + g] = s;
+    for (int c = c0 + lane; c < c1; c += 32) {
+      const float v = static_cast<float>(xr[c]) * inv;
+      if constexpr (KIND == 0) qr[c] = static_cast<uint8_t>(static_cast<int8_t>(fminf(fmaxf(rintf(v), -127.f), 127.f)));
+      else qr[c] = to_e4m3(v);
+    }
+  }
+}
+
+// fp8 weights with one scale per 128 x 128 block: one CTA per block.
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_tiles_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale, int rows, int cols,
+                   long long ldx, int n_col_blocks) {
+  __shared__ float red[8];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int br = blockIdx.y, bc = blockIdx.x;
+  const int r0 = br * 128, c0 = bc * 128;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < 128 * 128; i += 256) {
+    const int r = r0 + i / 128, c = c0 + i % 128;
+    if (r < rows && c < cols) amax = fmaxf(amax, fabsf(static_cast<float>(x[static_cast<long long>(r) * ldx + c])));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = 0.f;
+  for (int w = 0; w < 8; ++w) amax = fmaxf(amax, red[w]);
+  const float s = fmaxf(amax, 1e-12f) / 448.f;
+  const float inv = 1.f / s;
+  if (threadIdx.x == 0) scale[br * n_col_blocks + bc] = s;
+  for (int i = threadIdx.x; i < 128 * 128; i += 256) {
+    const int r = r0 + i / 128, c = c0 + i % 128;
+    if (r < rows && c < cols)
+      q[static_cast<long long>(r) * cols + c] = to_e4m3(static_cast<float>(x[static_cast<long long>(r) * ldx + c]) * inv);
+  }
+}
+
+}  // namespace fmb
+
+using namespace fmb;
+
+template <int KIND, bool BLOCKED>
+static int launch_gemm8(const CUtensorMap& ta, const CUtensorMap& tb, const G8Params& p, int grid, cudaStream_t stream) {
+  auto kern = gemm8_kernel<KIND, BLOCKED>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G8Smem::TOTAL) != cudaSuccess) return -6;
+    attr_set = true;
+  }
+  return launch_pdl(kern, dim3(grid), dim3(G8_THREADS), G8Smem::TOTAL, stream, ta, tb, p) == cudaSuccess ? 0 : -3;
+}
+
+// kind: 0 int8, 1 fp8 e4m3. A [M, K] and B [N, K] are 1-byte, K-major with pitches lda / ldb (bytes = elements,
+// multiples of 16). sa_ld == 0 selects row scales (sa[M], sb[N]); otherwise block scales (fp8): sa[M, sa_ld],
+// sb[ceil(N / 128), sb_ld] with one column per 128 elements of K.
+extern "C" int fmb_gemm8(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
+                         long long ldd, int d_f32, int kind, const float* sa, const float* sb, int sa_ld, int sb_ld,
+                         int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 16) || (ldb % 16) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (reinterpret_cast<uintptr_t>(D) & 15) || (ldd % (d_f32 ? 4 : 8)) || sa == nullptr || sb == nullptr)
+    return -2;
+  if (kind != 0 && kind != 1) return -1;
+  const bool blocked = sa_ld > 0;
+  if (blocked && kind != 1) return -1;
+  G8Params p;
+  p.M = M; p.N = N;
+  p.tiles_m = (M + G8_BM - 1) / G8_BM;
+  p.tiles_n = (N + G8_BN - 1) / G8_BN;
+  p.kblocks = (K + G8_BK - 1) / G8_BK;
+  if (blocked && (sa_ld < p.kblocks || sb_ld < p.kblocks)) return -2;
+  p.D = D; p.ldd = ldd; p.d_f32 = d_f32;
+  p.sa = sa; p.sb = sb; p.sa_ld = sa_ld; p.sb_ld = sb_ld;
+  p.status = status;
+  CUtensorMap ta, tb;
+  if (!make_tmap_2d(&ta, A, M, K, lda, G8_BM, G8_BK, 1, TmapSwizzle::B128) ||
+      !make_tmap_2d(&tb, B, N, K, ldb, G8_BN, G8_BK, 1, TmapSwizzle::B128))
+    return -5;
+  const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const int sms = sm_count();
+  const int grid = static_cast<int>(total < sms ? total : sms);
+  if (kind == 0) return launch_gemm8<0, false>(ta, tb, p, grid, stream);
+  if (!blocked) return launch_gemm8<1, false>(ta, tb, p, grid, stream);
+  return launch_gemm8<1, true>(ta, tb, p, grid, stream);
+}
+
+// Row quantiser. x: bf16 (dtype 0) or fp32 (1), [rows, cols] with pitch ldx. block > 0: fp8 scales per row and
+// `block` columns, scale shape [rows, ceil(cols / block)]; block == 0: one scale per row.
+extern "C" int fmb_quant_rows(const void* x, void* q, float* scale, long long rows, int cols, long long ldx, int dtype,
+                              int kind, int block, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (block > 0 && kind != 1) return -1;
+  const int n_blocks = block > 0 ? (cols + block - 1) / block : 1;
+  const unsigned grid = static_cast<unsigned>((rows * 32 + 255) / 256);
+  cudaError_t e;
+#define FMB_QR(T, KIND)                                                                                     \
+  e = launch_pdl(quant_rows_kernel<T, KIND>, dim3(grid), dim3(256), 0, stream, static_cast<const T*>(x),     \
+                 static_cast<uint8_t*>(q), scale, rows, cols, ldx, block, n_blocks)
+  if (dtype == FMB_BF16 && kind == 0) FMB_QR(__nv_bfloat16, 0);
+  else if (dtype == FMB_BF16 && kind == 1) FMB_QR(__nv_bfloat16, 1);
+  else if (dtype == FMB_F32 && kind == 0) FMB_QR(float, 0);
+  else if (dtype == FMB_F32 && kind == 1) FMB_QR(float, 1);
+  else return -1;
+#undef FMB_QR
+  return e == cudaSuccess ? 0 : -3;
+}
+
+// fp8 quantiser with one scale per 128 x 128 block; scale shape [ceil(rows/128), ceil(cols/128)].
+extern "C" int fmb_quant_tiles_fp8(const void* x, void* q, float* scale, int rows, int cols, long long ldx, int dtype,
+                                   cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const dim3 grid((cols + 127) / 128, (rows + 127) / 128);
+  cudaError_t e;
+  if (dtype == FMB_BF16)
+    e = launch_pdl(quant_tiles_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x),
+                   static_cast<uint8_t*>(q), scale, rows, cols, ldx, static_cast<int>(grid.x));
+  else if (dtype == FMB_F32)
+    e = launch_pdl(quant_tiles_kernel<float>, grid, dim3(256), 0, stream, static_cast<const float*>(x),
+                   static_cast<uint8_t*>(q), scale, rows, cols, ldx, static_cast<int>(grid.x));
+  else return -1;
+  return e == cudaSuccess ? 0 : -3;
+}

@@ -1,0 +1,91 @@
+"""int8 / fp8 tensor-core products and their quantisers against plain PyTorch statements."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _C():
+    from forgeminds_b200 import ops
+    return ops.require()
+
+
+def _rand(shape, seed, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, device="cuda", generator=g) * scale).to(torch.bfloat16)
+
+
+def test_int8_row_quantiser_matches_statement():
+    from forgeminds_b200.quant import quantize_rows_int8
+    x = _rand((300, 512), 0, 3.0)
+    q, s = _C().quant_rows(x, 0, 0)
+    want_q, want_s = quantize_rows_int8(x)
+    assert torch.allclose(s, want_s, rtol=1e-6, atol=0)
+    diff = (q.view(torch.int8).int() - want_q.int()).abs()
+    assert diff.max() <= 1 and (diff > 0).float().mean() < 1e-3        # 1/s vs division: rare off-by-one at .5
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (200, 136, 272), (1024, 1024, 2048)])
+def test_int8_gemm_is_exact(M, N, K, cuda_status):
+    C = _C()
+    a, b = _rand((M, K), 1), _rand((N, K), 2)
+    aq, sa = C.quant_rows(a, 0, 0)
+    bq, sb = C.quant_rows(b, 0, 0)
+    got = C.gemm8(aq, bq, sa, sb, 0, True, cuda_status)
+    acc = aq.view(torch.int8).double() @ bq.view(torch.int8).double().T
+    want = (acc * sa.double()[:, None] * sb.double()[None, :]).float()
+    assert torch.allclose(got, want, rtol=1e-5, atol=1e-5), (got - want).abs().max()
+    # and it approximates the bf16 product
+    ref = a.float() @ b.float().T
+    assert (got - ref).norm() / ref.norm() < 0.03
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (200, 136, 272)])
+def test_fp8_gemm_row_scales(M, N, K, cuda_status):
+    C = _C()
+    a, b = _rand((M, K), 3), _rand((N, K), 4)
+    aq, sa = C.quant_rows(a, 1, 0)
+    bq, sb = C.quant_rows(b, 1, 0)
+    got = C.gemm8(aq, bq, sa, sb, 1, True, cuda_status)
+    af = aq.view(torch.float8_e4m3fn).float() * sa[:, None]
+    bf = bq.view(torch.float8_e4m3fn).float() * sb[:, None]
+    want = af @ bf.T
+    assert torch.allclose(got, want, rtol=2e-3, atol=2e-3 * want.abs().max().item()), (got - want).abs().max()
+    ref = a.float() @ b.float().T
+    assert (got - ref).norm() / ref.norm() < 0.06
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (200, 136, 400), (512, 1024, 1024)])
+def test_fp8_gemm_block_scales(M, N, K, cuda_status):
+    from forgeminds_b200.quant import _dequant_fp8
+    C = _C()
+    a = _rand((M, K), 5) * torch.linspace(0.1, 4.0, K, device="cuda").to(torch.bfloat16)     # scales vary along K
+    b = _rand((N, K), 6)
+    aq, sa = C.quant_rows(a, 1, 128)
+    bq, sb = C.quant_tiles_fp8(b)
+    assert sa.shape == (M, (K + 127) // 128) and sb.shape == ((N + 127) // 128, (K + 127) // 128)
+    got = C.gemm8(aq, bq, sa, sb, 1, True, cuda_status)
+    want = _dequant_fp8(aq.view(torch.float8_e4m3fn), sa, 1, 128) @ _dequant_fp8(bq.view(torch.float8_e4m3fn), sb, 128, 128).T
+    assert torch.allclose(got, want, rtol=2e-3, atol=2e-3 * want.abs().max().item()), (got - want).abs().max()
+    ref = a.float() @ b.float().T
+    assert (got - ref).norm() / ref.norm() < 0.06
+
+
+@pytest.mark.parametrize("mode", ["int8", "fp8"])
+def test_quant_linear_forward_backward(mode, cuda_status):
+    from forgeminds_b200.quant import Fp8Linear, Int8Linear
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(512, 384, bias=False).cuda()
+    q = (Int8Linear if mode == "int8" else Fp8Linear).from_linear(lin)
+    x = _rand((4, 64, 512), 7).requires_grad_()
+    xr = x.detach().clone().requires_grad_()
+    y = q(x)
+    yr = torch.nn.functional.linear(xr.float(), lin.weight.float())
+    assert (y.float() - yr).norm() / yr.norm() < 0.06
+    g = _rand(y.shape, 8)
+    y.backward(g)
+    wq_grad = lin.weight.grad.clone()
+    lin.weight.grad = None
+    yr.backward(g.float())
+    assert (x.grad.float() - xr.grad.float()).norm() / xr.grad.float().norm() < 0.08
+    assert (wq_grad.float() - lin.weight.grad.float()).norm() / lin.weight.grad.float().norm() < 0.02
