@@ -313,6 +313,25 @@ void ns_axpby(const Tensor& x, const Tensor& y, Tensor& out, double a, double b)
                   dt(x), cur_stream()), "ns_axpby");
 }
 
+// ---- expert parallelism over peer memory
+const unsigned* uflags(const Tensor& flags) {
+  TORCH_CHECK(flags.scalar_type() == at::kInt && flags.is_cuda());
+  return reinterpret_cast<const unsigned*>(flags.data_ptr<int>());
+}
+
+void ep_collect_idx(const std::vector<int64_t>& idx_ptrs, Tensor& out, int64_t n, int64_t rank, int64_t e_local,
+                    const Tensor& flags, int64_t slot, int64_t epoch, double timeout_ms, Tensor& status);
+void ep_gather(const std::vector<int64_t>& x_ptrs, const Tensor& token_of_slot, const Tensor& limit, Tensor& out,
+               int64_t tokens_per_rank, const Tensor& flags, int64_t slot, int64_t epoch, double timeout_ms,
+               Tensor& status);
+void ep_combine(const std::vector<int64_t>& ys_ptrs, const std::vector<int64_t>& slot_ptrs, const Tensor& idx,
+                const c10::optional<Tensor>& w, Tensor& out, int64_t e_local, int64_t rank, const Tensor& flags,
+                int64_t slot, int64_t epoch, double timeout_ms, Tensor& status);
+void ep_combine_bwd(const std::vector<int64_t>& dout_ptrs, const std::vector<int64_t>& w_ptrs,
+                    const std::vector<int64_t>& drw_ptrs, const Tensor& ys, const Tensor& entry_of_slot,
+                    const Tensor& limit, Tensor& dys, int64_t n, int64_t k, const Tensor& flags, int64_t slot,
+                    int64_t epoch, double timeout_ms, Tensor& status);
+
 // ---- 8-bit products. kind: 0 = int8, 1 = fp8 e4m3. Quantised tensors travel as uint8.
 std::vector<Tensor> quant_rows(const Tensor& x, int64_t kind, int64_t block) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1, "quant_rows: 2-D CUDA tensor with contiguous rows");
@@ -481,6 +500,57 @@ void comm_barrier(const std::vector<int64_t>& flag_ptrs, int64_t slot, int64_t e
   c10::cuda::CUDAGuard guard(status.device());
   ok(fmb_comm_barrier(f.p, static_cast<int>(slot), static_cast<unsigned>(epoch), static_cast<int>(rank), f.world,
                       to_ns(timeout_ms), status.data_ptr<int>(), cur_stream()), "comm_barrier");
+}
+
+void ep_collect_idx(const std::vector<int64_t>& idx_ptrs, Tensor& out, int64_t n, int64_t rank, int64_t e_local,
+                    const Tensor& flags, int64_t slot, int64_t epoch, double timeout_ms, Tensor& status) {
+  PtrTable p(idx_ptrs);
+  TORCH_CHECK(out.scalar_type() == at::kInt && out.is_cuda() && out.numel() == n * p.world);
+  c10::cuda::CUDAGuard guard(out.device());
+  ok(fmb_ep_collect_idx(p.p, out.data_ptr<int>(), n, p.world, static_cast<int>(rank), static_cast<int>(e_local),
+                        uflags(flags), static_cast<int>(slot), static_cast<unsigned>(epoch), to_ns(timeout_ms),
+                        status.data_ptr<int>(), cur_stream()), "ep_collect_idx");
+}
+
+void ep_gather(const std::vector<int64_t>& x_ptrs, const Tensor& token_of_slot, const Tensor& limit, Tensor& out,
+               int64_t tokens_per_rank, const Tensor& flags, int64_t slot, int64_t epoch, double timeout_ms,
+               Tensor& status) {
+  PtrTable p(x_ptrs);
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.is_contiguous());
+  TORCH_CHECK(token_of_slot.scalar_type() == at::kInt && token_of_slot.numel() >= out.size(0) && limit.scalar_type() == at::kInt);
+  c10::cuda::CUDAGuard guard(out.device());
+  ok(fmb_ep_gather(p.p, token_of_slot.data_ptr<int>(), limit.data_ptr<int>(), out.data_ptr(), out.size(0),
+                   static_cast<int>(out.size(1)), tokens_per_rank, p.world, uflags(flags), static_cast<int>(slot),
+                   static_cast<unsigned>(epoch), to_ns(timeout_ms), status.data_ptr<int>(), cur_stream()), "ep_gather");
+}
+
+void ep_combine(const std::vector<int64_t>& ys_ptrs, const std::vector<int64_t>& slot_ptrs, const Tensor& idx,
+                const c10::optional<Tensor>& w, Tensor& out, int64_t e_local, int64_t rank, const Tensor& flags,
+                int64_t slot, int64_t epoch, double timeout_ms, Tensor& status) {
+  PtrTable y(ys_ptrs), s(slot_ptrs);
+  TORCH_CHECK(y.world == s.world && idx.scalar_type() == at::kInt && idx.dim() == 2 && idx.is_contiguous());
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.is_contiguous() && out.size(0) == idx.size(0));
+  if (w.has_value() && w->defined()) TORCH_CHECK(w->scalar_type() == at::kFloat && w->is_contiguous() && w->numel() == idx.numel());
+  c10::cuda::CUDAGuard guard(out.device());
+  ok(fmb_ep_combine(y.p, s.p, idx.data_ptr<int>(), static_cast<const float*>(cptr(w)), out.data_ptr(), idx.size(0),
+                    static_cast<int>(idx.size(1)), static_cast<int>(out.size(1)), static_cast<int>(e_local),
+                    static_cast<int>(rank), y.world, uflags(flags), static_cast<int>(slot),
+                    static_cast<unsigned>(epoch), to_ns(timeout_ms), status.data_ptr<int>(), cur_stream()), "ep_combine");
+}
+
+void ep_combine_bwd(const std::vector<int64_t>& dout_ptrs, const std::vector<int64_t>& w_ptrs,
+                    const std::vector<int64_t>& drw_ptrs, const Tensor& ys, const Tensor& entry_of_slot,
+                    const Tensor& limit, Tensor& dys, int64_t n, int64_t k, const Tensor& flags, int64_t slot,
+                    int64_t epoch, double timeout_ms, Tensor& status) {
+  PtrTable g(dout_ptrs), w(w_ptrs), dr(drw_ptrs);
+  TORCH_CHECK(g.world == w.world && g.world == dr.world);
+  TORCH_CHECK(ys.scalar_type() == at::kBFloat16 && ys.dim() == 2 && ys.is_contiguous() && dys.sizes() == ys.sizes() &&
+              dys.is_contiguous() && entry_of_slot.scalar_type() == at::kInt && entry_of_slot.numel() >= ys.size(0));
+  c10::cuda::CUDAGuard guard(ys.device());
+  ok(fmb_ep_combine_bwd(g.p, w.p, dr.p, ys.data_ptr(), entry_of_slot.data_ptr<int>(), limit.data_ptr<int>(),
+                        dys.data_ptr(), ys.size(0), n, static_cast<int>(k), static_cast<int>(ys.size(1)), g.world,
+                        uflags(flags), static_cast<int>(slot), static_cast<unsigned>(epoch), to_ns(timeout_ms),
+                        status.data_ptr<int>(), cur_stream()), "ep_combine_bwd");
 }
 
 // ---- router / MoE
@@ -674,6 +744,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("comm_step_reduce", &comm_step_reduce);
   m.def("comm_adamw_push", &comm_adamw_push);
   m.def("comm_barrier", &comm_barrier);
+  m.def("ep_collect_idx", &ep_collect_idx);
+  m.def("ep_gather", &ep_gather);
+  m.def("ep_combine", &ep_combine);
+  m.def("ep_combine_bwd", &ep_combine_bwd);
   m.def("quant_rows", &quant_rows);
   m.def("quant_tiles_fp8", &quant_tiles_fp8);
   m.def("gemm8", &gemm8);

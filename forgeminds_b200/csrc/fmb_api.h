@@ -98,6 +98,21 @@ int fmb_quant_rows(const void* x, void* q, float* scale, long long rows, int col
 int fmb_quant_tiles_fp8(const void* x, void* q, float* scale, int rows, int cols, long long ldx, int dtype,
                         cudaStream_t stream);
 
+// ---- expert parallelism over peer memory (moe_ep.cu); see the comment at the top of that file
+int fmb_ep_collect_idx(const void* const* idx_ptrs, int* out, long long n, int world, int rank, int e_local,
+                       const unsigned* flags, int slot, unsigned epoch, unsigned long long timeout_ns, int* status,
+                       cudaStream_t stream);
+int fmb_ep_gather(const void* const* x_ptrs, const int* token_of_slot, const int* limit_ptr, void* out,
+                  long long max_slots, int d, long long tokens_per_rank, int world, const unsigned* flags, int slot,
+                  unsigned epoch, unsigned long long timeout_ns, int* status, cudaStream_t stream);
+int fmb_ep_combine(const void* const* ys_ptrs, const void* const* slot_ptrs, const int* idx, const float* w, void* out,
+                   long long tokens, int k, int d, int e_local, int rank, int world, const unsigned* flags, int slot,
+                   unsigned epoch, unsigned long long timeout_ns, int* status, cudaStream_t stream);
+int fmb_ep_combine_bwd(const void* const* dout_ptrs, const void* const* w_ptrs, const void* const* drw_ptrs,
+                       const void* ys, const int* entry_of_slot, const int* limit_ptr, void* dys, long long max_slots,
+                       long long n, int k, int d, int world, const unsigned* flags, int slot, unsigned epoch,
+                       unsigned long long timeout_ns, int* status, cudaStream_t stream);
+
 // ---- collectives over peer memory, fused with what follows them (comm.cu)
 // `*_ptrs` are HOST arrays of `world` device pointers: the same symmetric buffer as mapped for each
 // rank. Flags are uint32 epochs, FMB_MAX_PEERS per slot, zero before first use; `epoch` must grow by

@@ -97,6 +97,9 @@ class Trainer:
                 if hasattr(blk, "native"):
                     blk.native = False
 
+        if pc.ep > 1 and self.native and pc.fused_comm and pc.ep <= 8 and not oc.experts:
+            from .parallel import ep as fused_ep      # dispatch / combine inside the permutation kernels
+            fused_ep.attach(model, ctx)
         self.quant: QuantState = quantize_model(model, cfg.quant, ctx.dp_group)
         if pc.tp > 1:
             native.apply_tp(model, ctx)

@@ -47,6 +47,11 @@ def test_fused_tensor_parallel_two_ranks():
     _run("tp_fused", 2, 29614)
 
 
+@needs2
+def test_expert_parallel_over_peer_memory_two_ranks():
+    _run("ep_fused", 2, 29616)
+
+
 def test_peer_step_single_rank(cuda_status):
     """World of one: the same kernels, peer tables of length one."""
     import forgeminds_b200 as fm
