@@ -468,6 +468,68 @@ __global__ void softmax_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, l
   }
 }
 
+// Rows of up to 1024 values: one warp per row, the row lives in registers (one read, one write).
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256)
+softmax_fwd_warp_kernel(const T* __restrict__ x, T* __restrict__ y, long long rows, int n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const T* xr = x + row * n;
+  float v[VPT];
+  float m = -CUDART_INF_F;
+  bool has_nan = false;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = j * 32 + lane;
+    v[j] = i < n ? static_cast<float>(xr[i]) : -CUDART_INF_F;
+    has_nan |= (v[j] != v[j]);
+    m = fmaxf(m, v[j]);
+  }
+  m = warp_max(m);
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    v[j] = (j * 32 + lane) < n ? __expf(v[j] - m) : 0.f;
+    s += v[j];
+  }
+  s = warp_sum(s);
+  const bool any_nan = __any_sync(0xffffffffu, has_nan);
+  const float inv = 1.f / s;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = j * 32 + lane;
+    if (i < n) y[row * n + i] = static_cast<T>(any_nan ? CUDART_NAN_F : v[j] * inv);
+  }
+}
+
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256)
+softmax_bwd_warp_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, long long rows, int n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float yv[VPT], gv[VPT];
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = j * 32 + lane;
+    yv[j] = i < n ? static_cast<float>(y[row * n + i]) : 0.f;
+    gv[j] = i < n ? static_cast<float>(dy[row * n + i]) : 0.f;
+    s += yv[j] * gv[j];
+  }
+  s = warp_sum(s);
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = j * 32 + lane;
+    if (i < n) dx[row * n + i] = static_cast<T>(yv[j] * (gv[j] - s));
+  }
+}
+
 template <typename T>
 __global__ void softmax_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx,
                                    long long rows, int n) {
@@ -534,6 +596,136 @@ __global__ void topk_kernel(const T* __restrict__ x, T* __restrict__ values, lon
       indices[row * k + round] = bi;
     }
     __syncthreads();
+  }
+}
+
+
+// Top-k by radix selection, one CTA per row. The row is staged in shared memory as order-preserving
+// integer keys (16 bits for bf16, 32 for fp32; NaN maps to the largest key); the k-th largest key is
+// found digit by digit with 256-bin histograms, the winners are gathered (ties at the boundary by
+// smallest index) and the k of them are sorted with a bitonic network. The row is read from global
+// memory once, whatever k is. Used when the keys of a row fit in shared memory and k <= 1024.
+template <typename T> struct TopkKey;
+template <> struct TopkKey<float> {
+  using Key = uint32_t;
+  static constexpr int BITS = 32;
+  static __device__ __forceinline__ Key of(float f) {
+    if (f != f) return 0xFFFFFFFFu;
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  }
+};
+template <> struct TopkKey<__nv_bfloat16> {
+  using Key = uint16_t;
+  static constexpr int BITS = 16;
+  static __device__ __forceinline__ Key of(__nv_bfloat16 b) {
+    const uint16_t u = __bfloat16_as_ushort(b);
+    if ((u & 0x7FFFu) > 0x7F80u) return 0xFFFFu;
+    return (u & 0x8000u) ? static_cast<uint16_t>(~u) : static_cast<uint16_t>(u | 0x8000u);
+  }
+};
+
+constexpr int TOPK_THREADS = 512;
+
+template <typename T>
+__global__ void __launch_bounds__(TOPK_THREADS)
+topk_select_kernel(const T* __restrict__ x, T* __restrict__ values, long long* __restrict__ indices, long long rows,
+                   int n, int k, int kpad) {
+  using KT = TopkKey<T>;
+  using Key = typename KT::Key;
+  extern __shared__ __align__(16) uint8_t topk_smem[];
+  uint32_t* sel_key = reinterpret_cast<uint32_t*>(topk_smem);          // [kpad]
+  int* sel_idx = reinterpret_cast<int*>(sel_key + kpad);               // [kpad]
+  int* hist = sel_idx + kpad;                                          // [256]
+  int* misc = hist + 256;                                              // [8]: prefix, remaining, counters
+  int* warp_cnt = misc + 8;                                            // [16]
+  Key* keys = reinterpret_cast<Key*>(warp_cnt + 16);                   // [n]
+  const long long row = blockIdx.x;
+  const T* xr = x + row * n;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < n; i += TOPK_THREADS) keys[i] = KT::of(xr[i]);
+  if (tid == 0) { misc[0] = 0; misc[1] = k; misc[2] = 0; misc[3] = 0; }
+  __syncthreads();
+  // ---- the k-th largest key, one byte at a time
+  for (int shift = KT::BITS - 8; shift >= 0; shift -= 8) {
+    for (int b = tid; b < 256; b += TOPK_THREADS) hist[b] = 0;
+    __syncthreads();
+    const uint32_t prefix = static_cast<uint32_t>(misc[0]);
+    const int hi = shift + 8;
+    for (int i = tid; i < n; i += TOPK_THREADS) {
+      const uint32_t key = keys[i];
+      if (hi >= KT::BITS || (key >> hi) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int remaining = misc[1], b = 255;
+      for (; b > 0; --b) {
+        if (hist[b] >= remaining) break;
+        remaining -= hist[b];
+      }
+      misc[0] = static_cast<int>((prefix << 8) | static_cast<uint32_t>(b));
+      misc[1] = remaining;
+    }
+    __syncthreads();
+  }
+  const uint32_t thr = static_cast<uint32_t>(misc[0]);
+  const int need_eq = misc[1];             // how many keys equal to the threshold belong to the result
+  const int n_gt = k - need_eq;
+  // ---- keys above the threshold: any order (sorted afterwards)
+  for (int i = tid; i < n; i += TOPK_THREADS) {
+    const uint32_t key = keys[i];
+    if (key > thr) {
+      const int pos = atomicAdd(&misc[2], 1);
+      sel_key[pos] = key;
+      sel_idx[pos] = i;
+    }
+  }
+  // ---- keys equal to the threshold: the first need_eq of them in index order
+  for (int base = 0; base < n; base += TOPK_THREADS) {
+    __syncthreads();
+    const int taken = misc[3];
+    if (taken >= need_eq) break;
+    const int i = base + tid;
+    const bool eq = i < n && static_cast<uint32_t>(keys[i]) == thr;
+    const unsigned ballot = __ballot_sync(0xffffffffu, eq);
+    if (lane == 0) warp_cnt[warp] = __popc(ballot);
+    __syncthreads();
+    int before = taken;
+    for (int w = 0; w < warp; ++w) before += warp_cnt[w];
+    const int rank = before + __popc(ballot & ((1u << lane) - 1u));
+    if (eq && rank < need_eq) {
+      sel_key[n_gt + rank] = thr;
+      sel_idx[n_gt + rank] = i;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int total = 0;
+      for (int w = 0; w < TOPK_THREADS / 32; ++w) total += warp_cnt[w];
+      misc[3] = taken + total;
+    }
+  }
+  __syncthreads();
+  for (int i = k + tid; i < kpad; i += TOPK_THREADS) { sel_key[i] = 0; sel_idx[i] = 0x7FFFFFFF; }   // padding sorts last
+  __syncthreads();
+  // ---- bitonic sort: key descending, then index ascending
+  for (int size = 2; size <= kpad; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int t = tid; t < (kpad >> 1); t += TOPK_THREADS) {
+        const int lo = 2 * t - (t & (stride - 1));
+        const int hi2 = lo + stride;
+        const bool up = (lo & size) == 0;
+        const uint32_t ka = sel_key[lo], kb = sel_key[hi2];
+        const int ia = sel_idx[lo], ib = sel_idx[hi2];
+        const bool a_first = ka > kb || (ka == kb && ia < ib);
+        if (a_first != up) { sel_key[lo] = kb; sel_key[hi2] = ka; sel_idx[lo] = ib; sel_idx[hi2] = ia; }
+      }
+      __syncthreads();
+    }
+  }
+  for (int i = tid; i < k; i += TOPK_THREADS) {
+    const int idx = sel_idx[i];
+    values[row * k + i] = xr[idx];
+    indices[row * k + i] = idx;
   }
 }
 
@@ -736,6 +928,17 @@ extern "C" int fmb_softmax_fwd(const void* x, void* y, long long rows, int n, in
   const int threads = n >= 1024 ? 256 : (n >= 128 ? 128 : 32);
   return by_dtype(dtype, [&](auto* tp) {
     using T = std::remove_pointer_t<decltype(tp)>;
+    if (n <= 1024) {
+      const dim3 grid(static_cast<unsigned>((rows * 32 + 255) / 256));
+      const T* xp = static_cast<const T*>(x);
+      T* yp = static_cast<T*>(y);
+      cudaError_t e;
+      if (n <= 128) e = launch_pdl(softmax_fwd_warp_kernel<T, 4>, grid, dim3(256), 0, stream, xp, yp, rows, n);
+      else if (n <= 256) e = launch_pdl(softmax_fwd_warp_kernel<T, 8>, grid, dim3(256), 0, stream, xp, yp, rows, n);
+      else if (n <= 512) e = launch_pdl(softmax_fwd_warp_kernel<T, 16>, grid, dim3(256), 0, stream, xp, yp, rows, n);
+      else e = launch_pdl(softmax_fwd_warp_kernel<T, 32>, grid, dim3(256), 0, stream, xp, yp, rows, n);
+      return e == cudaSuccess ? 0 : -3;
+    }
     softmax_fwd_kernel<T><<<static_cast<unsigned>(rows), threads, 0, stream>>>(static_cast<const T*>(x), static_cast<T*>(y), rows, n);
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
   });
@@ -747,6 +950,18 @@ extern "C" int fmb_softmax_bwd(const void* y, const void* dy, void* dx, long lon
   const int threads = n >= 1024 ? 256 : (n >= 128 ? 128 : 32);
   return by_dtype(dtype, [&](auto* tp) {
     using T = std::remove_pointer_t<decltype(tp)>;
+    if (n <= 1024) {
+      const dim3 grid(static_cast<unsigned>((rows * 32 + 255) / 256));
+      const T* yp = static_cast<const T*>(y);
+      const T* gp = static_cast<const T*>(dy);
+      T* dp = static_cast<T*>(dx);
+      cudaError_t e;
+      if (n <= 128) e = launch_pdl(softmax_bwd_warp_kernel<T, 4>, grid, dim3(256), 0, stream, yp, gp, dp, rows, n);
+      else if (n <= 256) e = launch_pdl(softmax_bwd_warp_kernel<T, 8>, grid, dim3(256), 0, stream, yp, gp, dp, rows, n);
+      else if (n <= 512) e = launch_pdl(softmax_bwd_warp_kernel<T, 16>, grid, dim3(256), 0, stream, yp, gp, dp, rows, n);
+      else e = launch_pdl(softmax_bwd_warp_kernel<T, 32>, grid, dim3(256), 0, stream, yp, gp, dp, rows, n);
+      return e == cudaSuccess ? 0 : -3;
+    }
     softmax_bwd_kernel<T><<<static_cast<unsigned>(rows), threads, 0, stream>>>(
         static_cast<const T*>(y), static_cast<const T*>(dy), static_cast<T*>(dx), rows, n);
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
@@ -760,6 +975,20 @@ extern "C" int fmb_topk(const void* x, void* values, long long* indices, long lo
   const int threads = n >= 4096 ? 512 : (n >= 512 ? 256 : 64);
   return by_dtype(dtype, [&](auto* tp) {
     using T = std::remove_pointer_t<decltype(tp)>;
+    int kpad = 2;
+    while (kpad < k) kpad <<= 1;
+    const size_t smem = static_cast<size_t>(kpad) * 8 + (256 + 8 + 16) * 4 + static_cast<size_t>(n) * sizeof(typename TopkKey<T>::Key) + 16;
+    if (k <= 1024 && n >= 1024 && smem <= 200 * 1024) {       // one pass over the row
+      auto kern = topk_select_kernel<T>;
+      static bool attr_set = false;
+      if (!attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return -6;
+        attr_set = true;
+      }
+      kern<<<static_cast<unsigned>(rows), TOPK_THREADS, smem, stream>>>(static_cast<const T*>(x), static_cast<T*>(values),
+                                                                       indices, rows, n, k, kpad);
+      return cudaGetLastError() == cudaSuccess ? 0 : -3;
+    }
     topk_kernel<T><<<static_cast<unsigned>(rows), threads, 0, stream>>>(static_cast<const T*>(x), static_cast<T*>(values), indices, rows, n, k);
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
   });

@@ -477,15 +477,16 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
   // Pick the N tile and the split count that fill the machine best.
   int best_bn = 256, best_split = 1;
   double best_score = -1.0;
-  for (int bn : {256, 128}) {
+  for (int bn : {256, 128, 64}) {
     if (force_bn && bn != force_bn) continue;
+    if (bn == 64 && (gs.mode != 0 || ps != nullptr)) continue;   // narrow tiles serve small plain products only
     const int tn = (N + bn - 1) / bn;
     const long long tiles = static_cast<long long>(tiles_m) * tn;
     const int max_split = can_split ? 8 : 1;
     for (int s = 1; s <= max_split; ++s) {
       if (s > 1 && (kblocks / s) < 8) break;            // keep each split's K loop long enough
       double score = wave_eff(tiles * s, sms);
-      score *= (bn == 256 ? 1.0 : 0.93);                // narrower tiles re-read A more often
+      score *= (bn == 256 ? 1.0 : bn == 128 ? 0.93 : 0.80);   // narrower tiles re-read A more often
       score *= 1.0 - 0.015 * (s - 1);                   // atomics and extra epilogues are not free
       const double pad = static_cast<double>(N) / (static_cast<double>(tn) * bn);
       score *= pad;
@@ -602,7 +603,7 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
   else if (a_mn)          e = launch_cfg<BN, ST, true, false, false>(sa, sb, p, grid, stream);        \
   else if (b_mn)          e = launch_cfg<BN, ST, false, true, false>(sa, sb, p, grid, stream);        \
   else                    e = launch_cfg<BN, ST, false, false, false>(sa, sb, p, grid, stream);
-    if (best_bn == 256) { FMB_DISPATCH(256, 4) } else { FMB_DISPATCH(128, 6) }
+    if (best_bn == 256) { FMB_DISPATCH(256, 4) } else if (best_bn == 128) { FMB_DISPATCH(128, 6) } else { FMB_DISPATCH(64, 8) }
 #undef FMB_DISPATCH
   }
   return e == cudaSuccess ? 0 : -10 - static_cast<int>(e);

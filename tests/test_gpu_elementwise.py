@@ -126,6 +126,27 @@ def test_softmax_and_topk():
     assert torch.equal(torch.gather(z, -1, i), v)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,k", [(32000, 64), (4096, 1), (5000, 1000), (1024, 7)])
+def test_topk_radix_select(dtype, n, k):
+    """The one-pass selection kernel: values as torch.topk, ties by smallest index, NaN first."""
+    from forgeminds_b200.ops import functional as Fn
+    g = torch.Generator(device="cuda").manual_seed(n + k)
+    x = torch.randn(37, n, device="cuda", generator=g).to(dtype)
+    x[1] = torch.randint(-3, 3, (n,), device="cuda", generator=g).to(dtype)      # heavy ties, negative values
+    x[2] = 0                                                                       # one value only
+    x[3, 17] = float("nan")
+    x[4] = -x[4].abs()
+    v, i = Fn.topk_lastdim(x, k)
+    vr, _ = torch.topk(x.float(), k, dim=-1)
+    assert torch.equal(torch.nan_to_num(v.float(), nan=1e30), torch.nan_to_num(vr, nan=1e30))
+    assert torch.equal(torch.nan_to_num(torch.gather(x, -1, i).float(), nan=1e30), torch.nan_to_num(v.float(), nan=1e30))
+    same = v[:, 1:] == v[:, :-1]
+    assert bool(((i[:, 1:] > i[:, :-1]) | ~same).all())
+    assert i[3, 0].item() == 17
+    assert torch.equal(i[2], torch.arange(k, device="cuda"))
+
+
 def test_cross_entropy_kernel():
     from forgeminds_b200 import ops
     C = ops.require()
