@@ -1,18 +1,19 @@
-"""``python -m forgeminds_b200.cli {bench,kbench,matrix} [options]``"""
+"""``python -m forgeminds_b200.cli {bench,kbench,matrix,audit} [options]``"""
 from __future__ import annotations
 
 import sys
 
-_COMMANDS = ("bench", "kbench", "matrix")
+TOOLS = ("bench", "kbench", "matrix", "audit")
 
 
 def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
-    if not argv or argv[0] in ("-h", "--help") or argv[0] not in _COMMANDS:
-        print("usage: python -m forgeminds_b200.cli {bench|kbench|matrix} [options]\n"
+    if not argv or argv[0] in ("-h", "--help") or argv[0] not in TOOLS:
+        print("usage: python -m forgeminds_b200.cli {bench|kbench|matrix|audit} [options]\n"
               "  bench   training throughput of a GPT preset under any mesh / quant / offload setting\n"
               "  kbench  per-kernel timings against eager PyTorch\n"
-              "  matrix  sweep of bench over quantisation modes")
+              "  matrix  sweep of bench over quantisation modes\n"
+              "  audit   host reads, kernel launches and top kernels of one training step")
         return 0 if argv and argv[0] in ("-h", "--help") else 2
     import importlib
     mod = importlib.import_module(f"forgeminds_b200.cli.{argv[0]}")

@@ -1,0 +1,58 @@
+"""The documentation names only things that exist, and documents every configuration field."""
+import dataclasses
+import os
+import re
+
+import forgeminds_b200 as fm
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DOCS = [os.path.join(ROOT, "docs", "documentation.md"), os.path.join(ROOT, "README.md")]
+
+
+def _text(path):
+    with open(path, encoding="utf-8") as f:
+        return f.read()
+
+
+def _resolve(dotted: str):
+    import importlib
+    obj, path = fm, fm.__name__
+    for part in dotted.split(".")[1:]:
+        path = f"{path}.{part}"
+        try:
+            obj = getattr(obj, part)
+        except AttributeError:
+            try:
+                obj = importlib.import_module(path)          # a submodule that nothing imported yet
+            except ImportError:
+                raise AttributeError(dotted) from None
+    return obj
+
+
+def test_every_fm_name_in_the_docs_resolves():
+    names = set()
+    for path in DOCS:
+        if os.path.exists(path):
+            names |= set(re.findall(r"\bfm(?:\.[A-Za-z_][A-Za-z0-9_]*)+", _text(path)))
+    assert len(names) > 30
+    missing = []
+    for name in sorted(names):
+        try:
+            _resolve(name)
+        except AttributeError:
+            missing.append(name)
+    assert not missing, missing
+
+
+def test_every_config_field_is_documented():
+    text = _text(DOCS[0])
+    for cls in (fm.ParallelConfig, fm.QuantConfig, fm.OffloadConfig, fm.TrainConfig, fm.GPTConfig):
+        for f in dataclasses.fields(cls):
+            assert f"| `{f.name}` |" in text, f"{cls.__name__}.{f.name} is not in docs/documentation.md"
+
+
+def test_documented_cli_tools_exist():
+    from forgeminds_b200.cli import __main__ as cli
+    text = _text(DOCS[0])
+    for tool in re.findall(r"python -m forgeminds_b200\.cli (\w+)", text):
+        assert tool in cli.TOOLS, tool
