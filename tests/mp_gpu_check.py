@@ -240,6 +240,53 @@ def ep_fused():
         print("OK ep_fused", flush=True)
 
 
+def peer_failure():
+    """Failures made on the host: a late rank is waited for; a rank that skips a launch makes the
+    other rank's kernel give up after its limit, report, and leave the GPU usable."""
+    import time
+    from forgeminds_b200 import ops
+    from forgeminds_b200.parallel.symm import SymmGroup
+    rank, world, dev = _init()
+    sg = SymmGroup(None, dev, timeout_ms=4000)
+    slot = sg.reserve_slots(2)
+    # 1. a delayed rank: the others wait (well inside the limit) and nobody reports anything
+    if rank == world - 1:
+        time.sleep(0.4)
+    sg.barrier(slot)
+    torch.cuda.synchronize()
+    sg.check()
+    dist.barrier()
+    # 2. the last rank skips one launch: everybody else times out after 0.3 s and says so
+    sg.timeout_ms = 300.0
+    t0 = time.perf_counter()
+    if rank != world - 1:
+        sg.barrier(slot + 1)
+        torch.cuda.synchronize()
+        waited = time.perf_counter() - t0
+        assert 0.25 < waited < 3.0, waited
+        try:
+            sg.check()
+        except ops.CommTimeout as e:
+            assert "code 5" in str(e)
+        else:
+            raise AssertionError("the missing rank went unnoticed")
+        assert int(ops.status_word(dev).item()) == 0                 # reading the status cleared it
+        y = torch.arange(8, device=dev).float().sum()                # the context still works
+        assert y.item() == 28.0
+    dist.barrier()                                                   # NCCL is unaffected
+    # 3. the skipped epoch is made up for and the protocol continues
+    if rank == world - 1:
+        sg._epochs[slot + 1] += 1
+        ops.require().comm_signal(sg.flags.ptrs, slot + 1, sg._epochs[slot + 1], rank, sg.status)
+    sg.timeout_ms = 4000.0
+    sg.barrier(slot + 1)
+    torch.cuda.synchronize()
+    sg.check()
+    dist.barrier()
+    if rank == 0:
+        print("OK peer_failure", flush=True)
+
+
 def tp_grads():
     """Loss and every gradient of the sharded, sequence-parallel model equal those of the whole model."""
     import copy

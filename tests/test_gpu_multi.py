@@ -52,6 +52,11 @@ def test_expert_parallel_over_peer_memory_two_ranks():
     _run("ep_fused", 2, 29616)
 
 
+@needs2
+def test_missing_rank_is_reported_not_waited_for_forever():
+    _run("peer_failure", 2, 29617)
+
+
 def test_peer_step_single_rank(cuda_status):
     """World of one: the same kernels, peer tables of length one."""
     import forgeminds_b200 as fm
