@@ -795,8 +795,8 @@ extern "C" int fmb_attn_fwd(const void* q, const void* k, const void* v, void* o
 extern "C" int fmb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
                             const float* lse, void* dq, void* dk, void* dv, float* delta, float* dq_acc, int B, int T,
                             int Hq, int Hkv, int hd, long long q_stride_t, long long kv_stride_t, long long o_stride_t,
-                            long long dq_stride_t, long long dkv_stride_t, float scale, int causal, int* status,
-                            cudaStream_t stream) {
+                            long long dq_stride_t, long long dkv_stride_t, float scale, int causal, int delta_ready,
+                            int* status, cudaStream_t stream) {
   if (B <= 0 || T <= 0) return 0;
   if (hd % 8 || hd > 128 || Hq % Hkv || (q_stride_t % 8) || (kv_stride_t % 8) || (o_stride_t % 8) ||
       (dq_stride_t % 8) || (dkv_stride_t % 8))
@@ -805,7 +805,7 @@ extern "C" int fmb_attn_bwd(const void* q, const void* k, const void* v, const v
   if (!make_head_tmap(&tq, q, B, T, Hq, hd, q_stride_t) || !make_head_tmap(&tk, k, B, T, Hkv, hd, kv_stride_t) ||
       !make_head_tmap(&tv, v, B, T, Hkv, hd, kv_stride_t) || !make_head_tmap(&tdo, d_o, B, T, Hq, hd, o_stride_t))
     return -5;
-  {
+  if (!delta_ready) {     // else the caller computed delta[b, h, t] already (fused into the producer of dO)
     const long long items = static_cast<long long>(B) * T * Hq;
     launch_pdl(attn_delta_kernel, dim3(static_cast<unsigned>((items * 32 + 255) / 256)), dim3(256), 0, stream,
                static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, B, T, Hq, hd,

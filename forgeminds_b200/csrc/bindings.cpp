@@ -92,6 +92,51 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& D, const c10::optional<Tenso
   ok(rc, "gemm_bf16");
 }
 
+// ---- products with fused epilogues (fmb_gemm_bf16_epi)
+void check_bf16_rows(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.dim() == 2 && t.scalar_type() == at::kBFloat16 && t.stride(1) == 1, name,
+              ": 2-D bf16 CUDA tensor with contiguous rows required");
+}
+
+// gu[M, 2h] = x[M, K] @ w13[2h, K].T (gate | up) and act[M, h] = silu(gate) * up in one kernel
+void gemm_swiglu_fwd(const Tensor& x, const Tensor& w13, Tensor& gu, Tensor& act, Tensor& status) {
+  check_bf16_rows(x, "x"); check_bf16_rows(w13, "w13"); check_bf16_rows(gu, "gu"); check_bf16_rows(act, "act");
+  const int64_t M = x.size(0), K = x.size(1), h = w13.size(0) / 2;
+  TORCH_CHECK(w13.size(1) == K && gu.size(0) == M && gu.size(1) == 2 * h && act.size(0) == M && act.size(1) == h);
+  c10::cuda::CUDAGuard guard(x.device());
+  ok(fmb_gemm_bf16_epi(x.data_ptr(), w13.data_ptr(), gu.data_ptr(), static_cast<int>(M), static_cast<int>(2 * h),
+                       static_cast<int>(K), 0, 0, x.stride(0), w13.stride(0), gu.stride(0), 0, 1.f, 1,
+                       static_cast<int>(h), 0, nullptr, 0, act.data_ptr(), act.stride(0), status.data_ptr<int>(),
+                       cur_stream()), "gemm_swiglu_fwd");
+}
+
+// dgu[M, 2h] = SwiGLU backward of (dy[M, d] @ w2[d, h]) through gu[M, 2h]; d(act) is never stored
+void gemm_swiglu_bwd(const Tensor& dy, const Tensor& w2, const Tensor& gu, Tensor& dgu, Tensor& status) {
+  check_bf16_rows(dy, "dy"); check_bf16_rows(w2, "w2"); check_bf16_rows(gu, "gu"); check_bf16_rows(dgu, "dgu");
+  const int64_t M = dy.size(0), K = dy.size(1), h = w2.size(1);
+  TORCH_CHECK(w2.size(0) == K && gu.size(0) == M && gu.size(1) == 2 * h && dgu.sizes() == gu.sizes());
+  c10::cuda::CUDAGuard guard(dy.device());
+  ok(fmb_gemm_bf16_epi(dy.data_ptr(), w2.data_ptr(), dgu.data_ptr(), static_cast<int>(M), static_cast<int>(h),
+                       static_cast<int>(K), 0, 1, dy.stride(0), w2.stride(0), dgu.stride(0), 0, 1.f, 2,
+                       static_cast<int>(h), 0, gu.data_ptr(), gu.stride(0), nullptr, 0, status.data_ptr<int>(),
+                       cur_stream()), "gemm_swiglu_bwd");
+}
+
+// out[M, N] = a @ op(b) and rowdot[M, N / seg] = sums of out * src over seg-wide column groups
+// `seq` > 0: rows are (batch, t) pairs with t < seq and rowdot is stored as [batch, N / seg, seq]
+void gemm_rowdot(const Tensor& a, const Tensor& b, bool b_mn, Tensor& out, const Tensor& src, Tensor& rowdot,
+                 int64_t seg, int64_t seq, Tensor& status) {
+  check_bf16_rows(a, "a"); check_bf16_rows(b, "b"); check_bf16_rows(out, "out"); check_bf16_rows(src, "src");
+  const int64_t M = a.size(0), K = a.size(1), N = b_mn ? b.size(1) : b.size(0);
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == K && out.size(0) == M && out.size(1) == N && src.sizes() == out.sizes());
+  TORCH_CHECK(rowdot.scalar_type() == at::kFloat && rowdot.is_contiguous() && rowdot.numel() == M * (N / seg));
+  c10::cuda::CUDAGuard guard(a.device());
+  ok(fmb_gemm_bf16_epi(a.data_ptr(), b.data_ptr(), out.data_ptr(), static_cast<int>(M), static_cast<int>(N),
+                       static_cast<int>(K), 0, b_mn, a.stride(0), b.stride(0), out.stride(0), 0, 1.f, 3,
+                       static_cast<int>(seq), static_cast<int>(seg), src.data_ptr(), src.stride(0), rowdot.data_ptr(), N / seg,
+                       status.data_ptr<int>(), cur_stream()), "gemm_rowdot");
+}
+
 std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
   cuda_contig(x, "x"); cuda_contig(w, "w");
   const int64_t d = x.size(-1);
@@ -702,19 +747,22 @@ std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, 
 
 // writes dq/dk/dv into the given (possibly strided) views
 void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o, const Tensor& lse,
-              Tensor& dq, Tensor& dk, Tensor& dv, double scale, bool causal, const c10::optional<Tensor>& status) {
+              Tensor& dq, Tensor& dk, Tensor& dv, double scale, bool causal, const c10::optional<Tensor>& status,
+              const c10::optional<Tensor>& delta_in) {
   const int64_t B = q.size(0), T = q.size(1), Hq = q.size(2), hd = q.size(3), Hkv = k.size(2);
   TORCH_CHECK(d_o.is_contiguous() && o.is_contiguous(), "attention backward: o and d_o must be contiguous");
   TORCH_CHECK(dk.stride(1) == dv.stride(1), "attention backward: dk and dv must share a token pitch");
   c10::cuda::CUDAGuard guard(q.device());
-  Tensor delta = torch::empty({B, Hq, T}, q.options().dtype(at::kFloat));
+  const bool have_delta = delta_in.has_value() && delta_in->defined();   // [B, Hq, T] fp32 computed elsewhere
+  if (have_delta) TORCH_CHECK(delta_in->scalar_type() == at::kFloat && delta_in->is_contiguous() && delta_in->numel() == B * Hq * T);
+  Tensor delta = have_delta ? *delta_in : torch::empty({B, Hq, T}, q.options().dtype(at::kFloat));
   Tensor dq_acc = torch::zeros({B, T, Hq, hd}, q.options().dtype(at::kFloat));
   int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
   ok(fmb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr<float>(),
                   dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr<float>(), dq_acc.data_ptr<float>(),
                   static_cast<int>(B), static_cast<int>(T), static_cast<int>(Hq), static_cast<int>(Hkv),
                   static_cast<int>(hd), q.stride(1), k.stride(1), o.stride(1), dq.stride(1), dk.stride(1),
-                  static_cast<float>(scale), causal, st, cur_stream()), "attn_bwd", 3);
+                  static_cast<float>(scale), causal, have_delta ? 1 : 0, st, cur_stream()), "attn_bwd", have_delta ? 2 : 3);
 }
 #endif
 
@@ -744,6 +792,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("comm_step_reduce", &comm_step_reduce);
   m.def("comm_adamw_push", &comm_adamw_push);
   m.def("comm_barrier", &comm_barrier);
+  m.def("gemm_swiglu_fwd", &gemm_swiglu_fwd);
+  m.def("gemm_swiglu_bwd", &gemm_swiglu_bwd);
+  m.def("gemm_rowdot", &gemm_rowdot);
   m.def("ep_collect_idx", &ep_collect_idx);
   m.def("ep_gather", &ep_gather);
   m.def("ep_combine", &ep_combine);

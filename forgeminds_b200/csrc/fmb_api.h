@@ -87,7 +87,15 @@ int fmb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
 int fmb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
                  void* dq, void* dk, void* dv, float* delta, float* dq_acc, int B, int T, int Hq, int Hkv, int hd,
                  long long q_stride_t, long long kv_stride_t, long long o_stride_t, long long dq_stride_t,
-                 long long dkv_stride_t, float scale, int causal, int* status, cudaStream_t stream);
+                 long long dkv_stride_t, float scale, int causal, int delta_ready, int* status, cudaStream_t stream);
+
+// bf16 product with a fused epilogue: epi 1 SwiGLU forward (B = stacked gate|up weight [2h, K], D = gate|up
+// [M, 2h], aux_out = activation [M, h]); 2 SwiGLU backward (accumulator = d(act) [M, h], aux_in = gate|up,
+// D = d(gate)|d(up) [M, 2h]); 3 also writes aux_out[row, col / seg] = sum over seg columns of D * aux_in.
+int fmb_gemm_bf16_epi(const void* A, const void* B, void* D, int M, int N, int K, int a_mn, int b_mn, long long lda,
+                      long long ldb, long long ldd, int d_f32, float alpha, int epi, int h, int seg,
+                      const void* aux_in, long long ld_aux_in, void* aux_out, long long ld_aux_out, int* status,
+                      cudaStream_t stream);
 
 // ---- 8-bit GEMMs and their quantisers (gemm8_sm100.cu)
 int fmb_gemm8(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb, long long ldd,

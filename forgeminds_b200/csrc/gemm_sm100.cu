@@ -59,6 +59,20 @@ struct GemmParams {
   void* d_peer[FMB_MAX_PEERS];
   int rot_m;                // row tiles are visited starting from this one (own shard first / remote first)
   int rot_k;                // reduction blocks are visited starting from this one (own shard first)
+  // fused epilogues (BN = 256, plain products only):
+  //   1  SwiGLU forward. B is the stacked gate|up weight [2h, K]; a tile multiplies by rows [n0, n0+128)
+  //      (gate) and [h+n0, h+n0+128) (up), D is the gate|up buffer [M, 2h] and aux_out[M, h] receives
+  //      silu(gate) * up.
+  //   2  SwiGLU backward. The accumulator is d(act) [M, h]; gate|up are read from aux_in [M, 2h] and
+  //      d(gate)|d(up) are written to D [M, 2h]; d(act) itself is never stored.
+  //   3  row dots. Besides D, rowdot[row, col / seg] = sum of D * aux_in over each seg-wide column group
+  //      (aux_in has the layout of D). With epi_h = T > 0 the rows are (batch, t) pairs and the result is
+  //      stored as [batch, group, t].
+  int epi, epi_h, seg;
+  const void* aux_in;
+  long long ld_aux_in;
+  void* aux_out;
+  long long ld_aux_out;
 };
 
 // One tensor map per source rank (PEER) or a single one.
@@ -224,7 +238,12 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
               tma_load_2d(sA + j * (BK * 128), ma, full_bar(stage), m_blk * BM + j * 64, a_y);
           }
           if constexpr (!B_MN) {
-            tma_load_3d(sB, mb, full_bar(stage), kb * BK, b_y, ti.zb);
+            if (BN == 256 && p.epi == 1) {       // gate rows and up rows of the stacked weight
+              tma_load_3d(sB, mb, full_bar(stage), kb * BK, n_blk * 128, ti.zb);
+              tma_load_3d(sB + 128u * 128u, mb, full_bar(stage), kb * BK, p.epi_h + n_blk * 128, ti.zb);
+            } else {
+              tma_load_3d(sB, mb, full_bar(stage), kb * BK, b_y, ti.zb);
+            }
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
@@ -293,6 +312,69 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
       const int row = m_blk * BM + quarter * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if (BN == 256 && p.epi == 1) {
+        // SwiGLU forward: accumulator columns [0,128) are gate, [128,256) up, of hidden units n_blk*128 ...
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(t_row + c * 32, rg);
+          tmem_ld_32x32(t_row + 128 + c * 32, ru);
+          tmem_wait_ld();
+          if (!row_ok) continue;
+          const int hc = n_blk * 128 + c * 32;                // hidden-unit column, < epi_h by construction
+          __nv_bfloat16* gp = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + hc;
+          __nv_bfloat16* up = gp + p.epi_h;
+          __nv_bfloat16* ap = reinterpret_cast<__nv_bfloat16*>(p.aux_out) + static_cast<long long>(row) * p.ld_aux_out + hc;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t og[4], ou[4], oa[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              // round gate and up to bf16 first: the activation is what a separate kernel would compute from them
+              og[q] = pack_bf16(__uint_as_float(rg[8 * i + 2 * q]), __uint_as_float(rg[8 * i + 2 * q + 1]));
+              ou[q] = pack_bf16(__uint_as_float(ru[8 * i + 2 * q]), __uint_as_float(ru[8 * i + 2 * q + 1]));
+              const float2 g = unpack_bf16(og[q]), u = unpack_bf16(ou[q]);
+              oa[q] = pack_bf16(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
+            }
+            reinterpret_cast<uint4*>(gp)[i] = make_uint4(og[0], og[1], og[2], og[3]);
+            reinterpret_cast<uint4*>(up)[i] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+            reinterpret_cast<uint4*>(ap)[i] = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+          }
+        }
+      } else if (p.epi == 2) {
+        // SwiGLU backward: v = d(act); d(gate) = v*u*s*(1+g*(1-s)), d(up) = v*g*s with s = sigmoid(g)
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n_blk * BN + c * 32;
+          if (col0 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_wait_ld();
+          if (!row_ok) continue;
+          const __nv_bfloat16* gin = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + static_cast<long long>(row) * p.ld_aux_in + col0;
+          const __nv_bfloat16* uin = gin + p.epi_h;
+          __nv_bfloat16* dg = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
+          __nv_bfloat16* du = dg + p.epi_h;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4 gv = reinterpret_cast<const uint4*>(gin)[i], uv = reinterpret_cast<const uint4*>(uin)[i];
+            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+            uint32_t og[4], ou[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 g = unpack_bf16(gw[q]), u = unpack_bf16(uw[q]);
+              const float2 d = unpack_bf16(pack_bf16(__uint_as_float(r[8 * i + 2 * q]) * alpha,
+                                                     __uint_as_float(r[8 * i + 2 * q + 1]) * alpha));
+              const float s0 = 1.f / (1.f + __expf(-g.x)), s1 = 1.f / (1.f + __expf(-g.y));
+              og[q] = pack_bf16(d.x * u.x * s0 * (1.f + g.x * (1.f - s0)), d.y * u.y * s1 * (1.f + g.y * (1.f - s1)));
+              ou[q] = pack_bf16(d.x * g.x * s0, d.y * g.y * s1);
+            }
+            reinterpret_cast<uint4*>(dg)[i] = make_uint4(og[0], og[1], og[2], og[3]);
+            reinterpret_cast<uint4*>(du)[i] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+          }
+        }
+      } else {
+      float seg_dot = 0.f;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col0 = n_blk * BN + c * 32;
@@ -305,6 +387,31 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
         const bool full = col0 + 32 <= p.N;
+        if (p.epi == 3) {
+          // dot of this chunk (as it will be stored, rounded to bf16) with the same chunk of aux_in
+          const __nv_bfloat16* sp = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + static_cast<long long>(row) * p.ld_aux_in + col0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4 sv = reinterpret_cast<const uint4*>(sp)[i];
+            const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 a = unpack_bf16(sw[q]);
+              const float2 d = unpack_bf16(pack_bf16(v[8 * i + 2 * q], v[8 * i + 2 * q + 1]));
+              seg_dot += a.x * d.x + a.y * d.y;
+            }
+          }
+          if (((col0 + 32) % p.seg) == 0) {
+            const int g = (col0 + 32) / p.seg - 1;          // column group; ld_aux_out = number of groups
+            long long at = static_cast<long long>(row) * p.ld_aux_out + g;
+            if (p.epi_h > 0) {                             // rows are (batch, t) with t < epi_h: store as [batch, group, t]
+              const int bb = row / p.epi_h, tt = row - bb * p.epi_h;
+              at = (static_cast<long long>(bb) * p.ld_aux_out + g) * p.epi_h + tt;
+            }
+            reinterpret_cast<float*>(p.aux_out)[at] = seg_dot;
+            seg_dot = 0.f;
+          }
+        }
         if (p.C != nullptr && beta != 0.f) {
           if (p.c_f32) {
             const float* cp = reinterpret_cast<const float*>(p.C) + ti.d_off + static_cast<long long>(row) * p.ldc + col0;
@@ -376,6 +483,7 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
           }
         }
       }
+      }   // generic epilogue
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -424,6 +532,15 @@ struct GroupSpec {
   long long group_stride_d = 0;  // elements between the D (and C) matrices of consecutive groups (mode 2)
 };
 
+// Fused epilogues (see GemmParams::epi).
+struct EpiSpec {
+  int epi = 0, h = 0, seg = 0;
+  const void* aux_in = nullptr;
+  long long ld_aux_in = 0;
+  void* aux_out = nullptr;
+  long long ld_aux_out = 0;
+};
+
 // Operands / output spread over the ranks of one NVSwitch domain (see GemmParams).
 struct PeerSpec {
   int rank = 0, world = 1;
@@ -444,10 +561,25 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
                     int b_mn, long long lda, long long ldb, long long ldd, long long ldc, int d_f32,
                     int c_f32, float alpha, float beta, const float* alpha_ptr, int allow_split, int* status,
                     int force_bn, const fmb::GroupSpec& gs, cudaStream_t stream,
-                    const fmb::PeerSpec* ps = nullptr) {
+                    const fmb::PeerSpec* ps = nullptr, const fmb::EpiSpec* es = nullptr) {
   using namespace fmb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (gs.mode != 0 || ps != nullptr) allow_split = 0;
+  if (es != nullptr && es->epi != 0) {
+    if (gs.mode != 0 || ps != nullptr || C != nullptr) return -2;
+    allow_split = 0;
+    force_bn = 256;
+    if (es->epi == 1 && (b_mn || d_f32 || es->h <= 0 || es->h % 128 || N != 2 * es->h || es->aux_out == nullptr ||
+                         (es->ld_aux_out % 8) || (reinterpret_cast<uintptr_t>(es->aux_out) & 15)))
+      return -2;
+    if (es->epi == 2 && (d_f32 || es->h <= 0 || es->h % 32 || N != es->h || es->aux_in == nullptr ||
+                         (es->ld_aux_in % 8) || (reinterpret_cast<uintptr_t>(es->aux_in) & 15)))
+      return -2;
+    if (es->epi == 3 && (es->seg <= 0 || es->seg % 32 || 256 % es->seg || N % es->seg || es->aux_in == nullptr ||
+                         es->aux_out == nullptr || (es->ld_aux_in % 8) || (reinterpret_cast<uintptr_t>(es->aux_in) & 15)))
+      return -2;
+    if (es->epi < 1 || es->epi > 3) return -2;
+  }
   if (ps != nullptr) {
     if (gs.mode != 0 || ps->world < 1 || ps->world > FMB_MAX_PEERS || ps->rank < 0 || ps->rank >= ps->world) return -2;
     if (ps->a_ptrs != nullptr) {
@@ -523,6 +655,14 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
   p.timeout_ns = 0;
   p.rot_m = p.rot_k = 0;
   for (int r = 0; r < FMB_MAX_PEERS; ++r) p.d_peer[r] = nullptr;
+  p.epi = 0; p.epi_h = 0; p.seg = 0;
+  p.aux_in = nullptr; p.ld_aux_in = 0; p.aux_out = nullptr; p.ld_aux_out = 0;
+  if (es != nullptr && es->epi != 0) {
+    p.epi = es->epi; p.epi_h = es->h; p.seg = es->seg;
+    p.aux_in = es->aux_in; p.ld_aux_in = es->ld_aux_in;
+    p.aux_out = es->aux_out; p.ld_aux_out = es->ld_aux_out;
+    if (es->epi == 1) p.tiles_n = es->h / 128;          // a tile = 128 hidden units = 128 gate + 128 up columns
+  }
   if (ps != nullptr) {
     p.rank = ps->rank; p.world = ps->world;
     p.flags = ps->flags;
@@ -574,7 +714,7 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
                                           : brows * static_cast<uint64_t>(ldb);
     uint64_t dims[3], strides[3];
     uint32_t box[3];
-    if (!b_mn) { dims[0] = K; dims[1] = N; box[0] = GEMM_BK; box[1] = best_bn; }
+    if (!b_mn) { dims[0] = K; dims[1] = N; box[0] = GEMM_BK; box[1] = (p.epi == 1) ? 128 : best_bn; }
     else       { dims[0] = N; dims[1] = brows; box[0] = 64; box[1] = GEMM_BK; }
     dims[2] = nb; box[2] = 1;
     strides[0] = 2; strides[1] = static_cast<uint64_t>(ldb) * 2; strides[2] = gstride * 2;
@@ -667,4 +807,19 @@ extern "C" int fmb_gemm_bf16_peer(const void* A, const void* B, void* D, int M, 
   const bool acc = accumulate && d_ptrs == nullptr;      // D += product (local output only)
   return run_gemm(a0, b0, d0, acc ? d0 : nullptr, M, N, K, a_mn, b_mn, lda, ldb, ldd, acc ? ldd : 0, d_f32,
                   acc ? d_f32 : 0, alpha, acc ? 1.f : 0.f, nullptr, 0, status, 0, gs, stream, &ps);
+}
+
+// Plain product with a fused epilogue (GemmParams::epi): 1 SwiGLU forward (N = 2h), 2 SwiGLU backward
+// (N = h, D is [M, 2h]), 3 row dots against aux_in over seg-wide column groups.
+extern "C" int fmb_gemm_bf16_epi(const void* A, const void* B, void* D, int M, int N, int K, int a_mn, int b_mn,
+                                 long long lda, long long ldb, long long ldd, int d_f32, float alpha, int epi, int h,
+                                 int seg, const void* aux_in, long long ld_aux_in, void* aux_out, long long ld_aux_out,
+                                 int* status, cudaStream_t stream) {
+  fmb::GroupSpec gs;
+  fmb::EpiSpec es;
+  es.epi = epi; es.h = h; es.seg = seg;
+  es.aux_in = aux_in; es.ld_aux_in = ld_aux_in;
+  es.aux_out = aux_out; es.ld_aux_out = ld_aux_out;
+  return run_gemm(A, B, D, nullptr, M, N, K, a_mn, b_mn, lda, ldb, ldd, 0, d_f32, 0, alpha, 0.f, nullptr, 0, status, 256,
+                  gs, stream, nullptr, &es);
 }

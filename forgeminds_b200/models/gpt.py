@@ -168,8 +168,7 @@ class Attention(nn.Module):
                                       passthrough=True)
         cos, sin = rope_tables(T, hd, self.theta, x.device, torch.float32)
         qkv = Fn.rope_qkv_(qkv, cos.reshape(T, hd // 2), sin.reshape(T, hd // 2), n_q, n_kv, hd)
-        o = Fn.attention_qkv(qkv, n_q, n_kv, hd, True)
-        return Fn.linear(o, self.wo.weight, x)
+        return Fn.attention_proj(qkv, self.wo.weight, x, n_q, n_kv, hd, True)
 
 
 class SwiGLU(nn.Module):
@@ -185,6 +184,8 @@ class SwiGLU(nn.Module):
     def forward_native(self, x, norm):
         """``x + mlp(norm(x))``; the norm output and the activation are recomputed in the backward."""
         from ..ops import functional as Fn
+        if self.w1.weight.shape[0] % 128 == 0:
+            return Fn.mlp_block(x, norm.weight, norm.eps, self.w1.weight, self.w3.weight, self.w2.weight)
         gu, x = Fn.norm_linear_multi(x, norm.weight, norm.eps, (self.w1.weight, self.w3.weight), passthrough=True)
         return Fn.swiglu_linear(gu, self.w2.weight, x)
 

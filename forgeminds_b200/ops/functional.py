@@ -174,7 +174,7 @@ def fused_bf16(weights) -> torch.Tensor:
     if _adjacent(shadows):
         return _stack_view(shadows)
     head = weights[0]
-    key = tuple((id(w), w._version) for w in weights)
+    key = (_weights_epoch,) + tuple((id(w), w._version) for w in weights)
     cached = getattr(head, "_fm_fused", None)
     if cached is not None and cached[0] == key:
         return cached[1]
@@ -571,8 +571,162 @@ class _Attention(torch.autograd.Function):
         dk = dqkv[..., n_q * hd: (n_q + n_kv) * hd].unflatten(-1, (n_kv, hd))
         dv = dqkv[..., (n_q + n_kv) * hd:].unflatten(-1, (n_kv, hd))
         C.attn_bwd(q, k, v, o, d_o.contiguous().view(B, T, n_q, hd), lse, dq, dk, dv, 1.0 / math.sqrt(hd), causal,
-                   status_word(qkv.device))
+                   status_word(qkv.device), None)
         return dqkv, None, None, None, None
+
+
+class _AttentionProj(torch.autograd.Function):
+    """``attention(qkv) @ Wo.T + residual`` as one autograd node. In the backward, the product that
+    yields ``dO = dY @ Wo`` also emits ``delta = rowsum(dO * O)`` per head from its epilogue, so the
+    attention backward needs no separate pass over ``O`` and ``dO``."""
+
+    @staticmethod
+    def forward(ctx, qkv, weight, residual, n_q, n_kv, hd, causal):
+        C = require()
+        B, T, _ = qkv.shape
+        q = qkv[..., : n_q * hd].unflatten(-1, (n_q, hd))
+        k = qkv[..., n_q * hd: (n_q + n_kv) * hd].unflatten(-1, (n_kv, hd))
+        v = qkv[..., (n_q + n_kv) * hd:].unflatten(-1, (n_kv, hd))
+        o, lse = C.attn_fwd(q, k, v, 1.0 / math.sqrt(hd), causal, status_word(qkv.device))
+        w = bf16_of(weight)
+        o2 = o.view(B * T, n_q * hd)
+        res2 = None
+        if residual is not None:
+            res2 = _rows(residual)
+            if not res2.is_contiguous():
+                res2 = res2.contiguous()
+        y = torch.empty((B, T, w.shape[0]), dtype=BF16, device=qkv.device)
+        gemm(o2, w, out=y.view(B * T, w.shape[0]), c=res2, beta=1.0 if res2 is not None else 0.0)
+        ctx.save_for_backward(qkv, o, lse, w)
+        ctx.weight = weight
+        ctx.dims = (n_q, n_kv, hd, causal, residual is not None)
+        return y
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dy):
+        C = require()
+        qkv, o, lse, w = ctx.saved_tensors
+        weight = ctx.weight
+        n_q, n_kv, hd, causal, has_res = ctx.dims
+        B, T, _ = qkv.shape
+        st = status_word(qkv.device)
+        dy2 = _rows(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        o2 = o.view(B * T, n_q * hd)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            main = getattr(weight, "_fm_main_grad", None)
+            if main is not None:
+                gemm(dy2, o2, a_mn=True, b_mn=True, out=main, c=main, beta=1.0, allow_split=True)
+            else:
+                dw = gemm(dy2, o2, a_mn=True, b_mn=True, out_dtype=torch.float32, allow_split=True)
+                if dw.dtype != weight.dtype:
+                    dw = dw.to(weight.dtype)
+        dqkv = None
+        if ctx.needs_input_grad[0]:
+            d_o = torch.empty_like(o2)
+            delta = None
+            if hd % 32 == 0 and 256 % hd == 0:
+                delta = torch.empty((B, n_q, T), dtype=torch.float32, device=qkv.device)
+                C.gemm_rowdot(dy2, w, True, d_o, o2, delta, hd, T, st)
+            else:
+                gemm(dy2, w, b_mn=True, out=d_o)
+            dqkv = torch.empty_like(qkv)
+            q = qkv[..., : n_q * hd].unflatten(-1, (n_q, hd))
+            k = qkv[..., n_q * hd: (n_q + n_kv) * hd].unflatten(-1, (n_kv, hd))
+            v = qkv[..., (n_q + n_kv) * hd:].unflatten(-1, (n_kv, hd))
+            dq = dqkv[..., : n_q * hd].unflatten(-1, (n_q, hd))
+            dk = dqkv[..., n_q * hd: (n_q + n_kv) * hd].unflatten(-1, (n_kv, hd))
+            dv = dqkv[..., (n_q + n_kv) * hd:].unflatten(-1, (n_kv, hd))
+            C.attn_bwd(q, k, v, o, d_o.view(B, T, n_q, hd), lse, dq, dk, dv, 1.0 / math.sqrt(hd), causal, st, delta)
+        return dqkv, dw, (dy if has_res else None), None, None, None, None
+
+
+def attention_proj(qkv, weight, residual, n_q, n_kv, hd, causal=True):
+    """Causal GQA attention on a fused q|k|v buffer followed by the output projection (+ residual)."""
+    return _AttentionProj.apply(qkv, weight, residual, n_q, n_kv, hd, causal)
+
+
+# Whether the SwiGLU runs in the epilogue of the neighbouring product (forward: gate|up product; backward:
+# activation-gradient product) or as its own kernel. Measured on a B200 at M = 8192, d = 1024, h = 2816
+# the fused forms are slower (forward 0.187 ms against 0.172 ms, forward + backward 0.633 against 0.580):
+# four epilogue warps per SM do the exponentials and three row-strided stores of a 128 x 256 tile more
+# slowly than a full-occupancy element-wise kernel streams the same bytes, and the main loop of a
+# K = 1024 product is too short to hide it. They stay available (and tested) for wider K.
+MLP_FUSE_FWD = False
+MLP_FUSE_BWD = False
+
+
+class _MLPBlock(torch.autograd.Function):
+    """``x + W2 (silu(W1 n) * (W3 n))`` with ``n = rms_norm(x)``, the SwiGLU fused into GEMM epilogues.
+
+    Forward: the gate|up product writes gate, up and the activation from its epilogue. Backward: the
+    product ``dY @ W2`` turns its accumulator (the activation gradient) straight into the gate and up
+    gradients in its epilogue. Kept for the backward: ``x``, ``rstd``, gate|up (the normalised input
+    and the activation are recomputed)."""
+
+    @staticmethod
+    def forward(ctx, x, norm_w, eps, w1, w3, w2):
+        C = require()
+        st = status_word(x.device)
+        w13 = fused_bf16((w1, w3))
+        b2 = bf16_of(w2)
+        x2 = _rows(x)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        nw = norm_w.detach()
+        if nw.dtype not in (torch.float32, x2.dtype):
+            nw = nw.to(x2.dtype)
+        nw = nw.contiguous()
+        xn, rstd = C.rmsnorm_fwd(x2, nw, eps)
+        m, h = x2.shape[0], w13.shape[0] // 2
+        gu = torch.empty((m, 2 * h), dtype=BF16, device=x.device)
+        if MLP_FUSE_FWD:
+            act = torch.empty((m, h), dtype=BF16, device=x.device)
+            C.gemm_swiglu_fwd(xn, w13, gu, act, st)
+        else:
+            gemm(xn, w13, out=gu)
+            act = C.swiglu_fwd(gu[:, :h], gu[:, h:])
+        y = torch.empty_like(x)
+        gemm(act, b2, out=y.view(m, -1), c=x2, beta=1.0)
+        ctx.save_for_backward(x2, nw, rstd, gu, w13, b2)
+        ctx.params = (w1, w3, w2)
+        ctx.meta = (eps, x.shape, norm_w.dtype)
+        return y
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dy):
+        C = require()
+        x2, nw, rstd, gu, w13, b2 = ctx.saved_tensors
+        w1, w3, w2 = ctx.params
+        eps, x_shape, nw_dtype = ctx.meta
+        st = status_word(dy.device)
+        dy2 = _rows(dy)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        h = gu.shape[1] // 2
+        act = C.swiglu_fwd(gu[:, :h], gu[:, h:])                        # recomputed
+        g2 = _weight_grads(ctx.needs_input_grad[5:6], (w2,), dy2, act)
+        dgu = torch.empty_like(gu)
+        if MLP_FUSE_BWD:
+            C.gemm_swiglu_bwd(dy2, b2, gu, dgu, st)
+        else:
+            dact = gemm(dy2, b2, b_mn=True)
+            C.swiglu_bwd(gu[:, :h], gu[:, h:], dact, dgu[:, :h], dgu[:, h:])
+        xn, _ = C.rmsnorm_fwd(x2, nw, eps)                              # recomputed
+        g13 = _weight_grads(ctx.needs_input_grad[3:5], (w1, w3), dgu, xn)
+        dxn = gemm(dgu, w13, b_mn=True)
+        dx, dnw = C.rmsnorm_bwd(dxn, x2, nw, rstd, dy2, ctx.needs_input_grad[1])
+        if dnw is not None and dnw.dtype != nw_dtype:
+            dnw = dnw.to(nw_dtype)
+        return dx.view(x_shape), dnw, None, g13[0], g13[1], g2[0]
+
+
+def mlp_block(x, norm_w, eps, w1, w3, w2):
+    return _MLPBlock.apply(x, norm_w, eps, w1, w3, w2)
 
 
 def attention_qkv(qkv, n_q, n_kv, hd, causal=True):

@@ -109,3 +109,53 @@ def test_main_grad_accumulation(cuda_status):
     assert w.grad is None
     ref = 2 * torch.ones(1024, 128, device="cuda").t() @ x.float()
     assert (w._fm_main_grad - ref).norm() / ref.norm() < 2e-3
+
+
+def test_swiglu_fused_into_gemm_epilogues(cuda_status):
+    """gate|up product with the activation from its epilogue; d(act) product with the SwiGLU backward in its epilogue."""
+    from forgeminds_b200 import ops
+    C = ops.require()
+    torch.manual_seed(0)
+    M, K, h, d = 384, 256, 640, 256
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w13 = (torch.randn(2 * h, K, device="cuda") * 0.1).to(torch.bfloat16)
+    gu = torch.empty(M, 2 * h, dtype=torch.bfloat16, device="cuda")
+    act = torch.empty(M, h, dtype=torch.bfloat16, device="cuda")
+    C.gemm_swiglu_fwd(x, w13, gu, act, cuda_status)
+    want_gu = (x.float() @ w13.float().T)
+    assert (gu.float() - want_gu).abs().max() < 0.02 * want_gu.abs().max()
+    g, u = gu[:, :h].float(), gu[:, h:].float()
+    want_act = torch.nn.functional.silu(g) * u
+    assert (act.float() - want_act).abs().max() < 0.02 * want_act.abs().max() + 1e-3
+    # backward
+    dy = (torch.randn(M, d, device="cuda") * 0.5).to(torch.bfloat16)
+    w2 = (torch.randn(d, h, device="cuda") * 0.1).to(torch.bfloat16)
+    dgu = torch.empty_like(gu)
+    C.gemm_swiglu_bwd(dy, w2, gu, dgu, cuda_status)
+    dact = (dy.float() @ w2.float()).to(torch.bfloat16).float()
+    s = torch.sigmoid(g)
+    want_dg = dact * u * s * (1 + g * (1 - s))
+    want_du = dact * g * s
+    assert (dgu[:, :h].float() - want_dg).abs().max() < 0.03 * want_dg.abs().max() + 1e-3
+    assert (dgu[:, h:].float() - want_du).abs().max() < 0.03 * want_du.abs().max() + 1e-3
+
+
+@pytest.mark.parametrize("seg,seq", [(64, 0), (64, 96), (128, 0), (32, 48)])
+def test_row_dots_from_the_gemm_epilogue(seg, seq, cuda_status):
+    from forgeminds_b200 import ops
+    C = ops.require()
+    torch.manual_seed(1)
+    M, K, N = 192, 320, 512
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    b = (torch.randn(K, N, device="cuda") * 0.1).to(torch.bfloat16)          # MN-major operand: out = a @ b
+    src = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    groups = N // seg
+    rd = torch.empty((M // seq, groups, seq) if seq else (M, groups), dtype=torch.float32, device="cuda")
+    C.gemm_rowdot(a, b, True, out, src, rd, seg, seq, cuda_status)
+    want = a.float() @ b.float()
+    assert (out.float() - want).abs().max() < 0.02 * want.abs().max()
+    dots = (out.float() * src.float()).view(M, groups, seg).sum(-1)
+    if seq:
+        dots = dots.view(M // seq, seq, groups).transpose(1, 2)
+    assert torch.allclose(rd, dots, rtol=2e-3, atol=2e-2)
