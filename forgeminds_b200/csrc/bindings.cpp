@@ -488,47 +488,58 @@ void comm_adamw_push(Tensor& master, const Tensor& grad, Tensor& m, Tensor& v, c
      "comm_adamw_push");
 }
 
-// Product with operands / output spread over the ranks (see fmb_gemm_bf16_peer). `a`, `b`, `d` are
-// this rank's tensors: a shard when the matching pointer list is non-empty, the whole matrix otherwise.
-void gemm_peer(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, double alpha, bool accumulate, int64_t rank,
-               int64_t world, const std::vector<int64_t>& a_ptrs, const std::vector<int64_t>& b_ptrs,
-               const std::vector<int64_t>& d_ptrs, const Tensor& flags, int64_t a_slot, int64_t a_epoch,
-               int64_t b_slot, int64_t b_epoch, double timeout_ms, Tensor& status) {
+// Product with operands / output spread over the ranks (see fmb_gemm_bf16_peer). `gather` = 1 / 2: `a` / `b` is this
+// rank's full-size symmetric buffer of the gathered operand and `gather_ptrs` every rank's; `ready` holds one int
+// per 128 rows of it. With `d_ptrs`, `d` is this rank's bf16 staging buffer [world * rows_per_rank, N].
+void gemm_peer(const Tensor& a, const Tensor& b, Tensor& d, bool a_mn, bool b_mn, double alpha, bool accumulate,
+               int64_t rank, int64_t world, int64_t gather, const std::vector<int64_t>& gather_ptrs,
+               const c10::optional<Tensor>& ready, const std::vector<int64_t>& d_ptrs, const Tensor& flags,
+               int64_t slot, int64_t epoch, double timeout_ms, Tensor& status) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && d.is_cuda() && a.dim() == 2 && b.dim() == 2 && d.dim() == 2);
   TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm_peer: bf16 operands required");
   TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && d.stride(1) == 1, "gemm_peer: innermost dimension must be contiguous");
-  TORCH_CHECK(world >= 1 && world <= FMB_MAX_PEERS);
-  const bool a_sh = !a_ptrs.empty(), b_sh = !b_ptrs.empty(), d_sh = !d_ptrs.empty();
-  TORCH_CHECK((!a_sh || static_cast<int64_t>(a_ptrs.size()) == world) && (!b_sh || static_cast<int64_t>(b_ptrs.size()) == world) &&
+  TORCH_CHECK(world >= 1 && world <= FMB_MAX_PEERS && gather >= 0 && gather <= 2);
+  const bool d_sh = !d_ptrs.empty();
+  TORCH_CHECK((gather == 0 || static_cast<int64_t>(gather_ptrs.size()) == world) &&
               (!d_sh || static_cast<int64_t>(d_ptrs.size()) == world), "gemm_peer: one pointer per rank");
-  int64_t M = a_mn ? a.size(1) : a.size(0) * (a_sh ? world : 1);
-  int64_t K = a_mn ? a.size(0) * (a_sh ? world : 1) : a.size(1);
+  const int64_t M = a_mn ? a.size(1) : a.size(0);
+  const int64_t K = a_mn ? a.size(0) : a.size(1);
   const int64_t N = b_mn ? b.size(1) : b.size(0);
-  const int64_t Kb = b_mn ? b.size(0) * (b_sh ? world : 1) : b.size(1);
-  TORCH_CHECK(K == Kb, "gemm_peer: inner dimensions differ: ", K, " vs ", Kb);
-  TORCH_CHECK(d.size(1) == N && d.size(0) * (d_sh ? world : 1) == M, "gemm_peer: output shape mismatch");
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == K, "gemm_peer: inner dimensions differ");
+  TORCH_CHECK(d.size(1) == N && d.size(0) == M, "gemm_peer: output shape mismatch");
   const bool d_f32 = d.scalar_type() == at::kFloat;
   TORCH_CHECK(d_f32 || d.scalar_type() == at::kBFloat16);
-  TORCH_CHECK(flags.scalar_type() == at::kInt && flags.is_cuda());
-  const void* ap[FMB_MAX_PEERS];
-  const void* bp[FMB_MAX_PEERS];
+  int* ready_ptr = nullptr;
+  if (gather) {
+    TORCH_CHECK(ready.has_value() && ready->scalar_type() == at::kInt && ready->is_cuda() &&
+                ready->numel() >= ((gather == 1 ? (a_mn ? K : M) : K) + 127) / 128, "gemm_peer: ready counters");
+    ready_ptr = ready->data_ptr<int>();
+  }
+  const void* gp[FMB_MAX_PEERS];
   void* dp[FMB_MAX_PEERS];
   for (int r = 0; r < FMB_MAX_PEERS; ++r) {
-    ap[r] = a_sh && r < world ? reinterpret_cast<const void*>(a_ptrs[r]) : nullptr;
-    bp[r] = b_sh && r < world ? reinterpret_cast<const void*>(b_ptrs[r]) : nullptr;
+    gp[r] = gather && r < world ? reinterpret_cast<const void*>(gather_ptrs[r]) : nullptr;
     dp[r] = d_sh && r < world ? reinterpret_cast<void*>(d_ptrs[r]) : nullptr;
   }
   c10::cuda::CUDAGuard guard(a.device());
   ok(fmb_gemm_bf16_peer(a.data_ptr(), b.data_ptr(), d.data_ptr(), static_cast<int>(M), static_cast<int>(N),
                         static_cast<int>(K), a_mn, b_mn, a.stride(0), b.stride(0), d.stride(0), d_f32,
                         static_cast<float>(alpha), accumulate ? 1 : 0, static_cast<int>(rank), static_cast<int>(world),
-                        a_sh ? ap : nullptr, a_sh ? static_cast<int>(a.size(0)) : 0, b_sh ? bp : nullptr,
-                        b_sh ? static_cast<int>(b.size(0)) : 0, d_sh ? dp : nullptr,
-                        d_sh ? static_cast<int>(d.size(0)) : 0,
-                        reinterpret_cast<const unsigned*>(flags.data_ptr<int>()), static_cast<int>(a_slot),
-                        static_cast<unsigned>(a_epoch), static_cast<int>(b_slot), static_cast<unsigned>(b_epoch),
-                        to_ns(timeout_ms), status.data_ptr<int>(), cur_stream()),
-     "gemm_bf16_peer");
+                        static_cast<int>(gather), gather ? gp : nullptr, ready_ptr, d_sh ? dp : nullptr,
+                        uflags(flags), static_cast<int>(slot), static_cast<unsigned>(epoch), to_ns(timeout_ms),
+                        status.data_ptr<int>(), cur_stream()), "gemm_bf16_peer", gather ? 2 : 1);
+}
+
+// out[rows, cols] = sum of the slices of staging[world, rows, cols] (+ residual), all bf16
+void comm_sum_partials(const Tensor& staging, const c10::optional<Tensor>& residual, Tensor& out, int64_t world) {
+  TORCH_CHECK(staging.is_cuda() && staging.is_contiguous() && staging.scalar_type() == at::kBFloat16 &&
+              out.is_contiguous() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 &&
+              staging.numel() == out.numel() * world);
+  if (residual.has_value() && residual->defined())
+    TORCH_CHECK(residual->is_contiguous() && residual->scalar_type() == at::kBFloat16 && residual->numel() == out.numel());
+  c10::cuda::CUDAGuard guard(out.device());
+  ok(fmb_comm_sum_partials(staging.data_ptr(), cptr(residual), out.data_ptr(), out.size(0), static_cast<int>(out.size(1)),
+                           static_cast<int>(world), cur_stream()), "comm_sum_partials");
 }
 
 // Post this rank's epoch on a flag slot of every rank (no wait): "my shard is ready".
@@ -804,6 +815,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm8", &gemm8);
   m.def("comm_signal", &comm_signal);
   m.def("gemm_peer", &gemm_peer);
+  m.def("comm_sum_partials", &comm_sum_partials);
   m.def("comm_adam_chunk", []() { return fmb_comm_adam_chunk(); });
   m.attr("MAX_PEERS") = FMB_MAX_PEERS;
   m.def("scale_cast", &scale_cast);

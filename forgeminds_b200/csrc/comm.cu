@@ -172,6 +172,30 @@ __global__ void barrier_kernel(Peers flags, int slot, uint32_t epoch, int rank, 
   wait_all(flags, slot, rank, world, epoch, timeout_ns, status);
 }
 
+// out = sum of the `world` bf16 slices of a staging buffer (+ residual), fp32 accumulation in slice order
+__global__ void __launch_bounds__(256)
+sum_partials_kernel(const uint4* __restrict__ staging, const uint4* __restrict__ residual, uint4* __restrict__ out,
+                    long long nvec, int world) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < world; ++r) {
+      const uint4 u = staging[static_cast<long long>(r) * nvec + i];
+      const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    if (residual != nullptr) {
+      const uint4 u = residual[i];
+      const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+    out[i] = o;
+  }
+}
+
 __global__ void signal_kernel(Peers flags, int slot, uint32_t epoch, int rank, int world) {
   signal_all(flags, slot, rank, world, epoch);
 }
@@ -243,5 +267,18 @@ extern "C" int fmb_comm_signal(const void* const* flag_ptrs, int slot, unsigned 
   Peers f;
   if (!fill(f, flag_ptrs, world) || rank < 0 || rank >= world) return -2;
   signal_kernel<<<1, 32, 0, stream>>>(f, slot, epoch, rank, world);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int fmb_comm_sum_partials(const void* staging, const void* residual, void* out, long long rows, int cols,
+                                     int world, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (cols % 8 || world < 1 || world > MAX_PEERS) return -2;
+  const long long nvec = rows * (cols / 8);
+  long long blocks = (nvec + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  sum_partials_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const uint4*>(staging),
+                                                                         static_cast<const uint4*>(residual),
+                                                                         static_cast<uint4*>(out), nvec, world);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

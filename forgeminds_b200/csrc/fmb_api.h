@@ -141,9 +141,12 @@ int fmb_comm_signal(const void* const* flag_ptrs, int slot, unsigned epoch, int 
 // Product whose operands / output are spread over the ranks (gemm_sm100.cu): see the comment at the definition.
 int fmb_gemm_bf16_peer(const void* A, const void* B, void* D, int M, int N, int K, int a_mn, int b_mn, long long lda,
                        long long ldb, long long ldd, int d_f32, float alpha, int accumulate, int rank, int world,
-                       const void* const* a_ptrs, int a_rows_per_src, const void* const* b_ptrs, int b_rows_per_src,
-                       void* const* d_ptrs, int d_rows_per_rank, const unsigned* flags, int a_slot, unsigned a_epoch,
-                       int b_slot, unsigned b_epoch, unsigned long long timeout_ns, int* status, cudaStream_t stream);
+                       int gather, const void* const* gather_ptrs, int* ready, void* const* d_ptrs,
+                       const unsigned* flags, int slot, unsigned epoch, unsigned long long timeout_ns, int* status,
+                       cudaStream_t stream);
+// out[rows, cols] (bf16) = sum over the `world` slices of staging[world, rows, cols] (bf16) (+ residual)
+int fmb_comm_sum_partials(const void* staging, const void* residual, void* out, long long rows, int cols, int world,
+                          cudaStream_t stream);
 int fmb_comm_barrier(const void* const* flag_ptrs, int slot, unsigned epoch, int rank, int world,
                      unsigned long long timeout_ns, int* status, cudaStream_t stream);
 

@@ -42,19 +42,31 @@ struct GemmParams {
   const int* tile_group;
   const int* region;
   long long group_stride_d;
-  // peer modes (PEER instantiations only). An operand whose rows (the y coordinate of its TMA map:
-  // the M rows of a K-major A, the reduction rows of an MN-major A or B) are spread over the ranks
-  // is read shard by shard through one tensor map per rank ("all-gather fused into the product");
-  // `*_rows_per_src` is the shard height (0 = operand is local). Before the first load from rank r
-  // the producer waits for flags[slot * MAX_PEERS + r] to reach `epoch` (slot < 0: no wait).
-  // With `d_rows_per_rank` > 0 the output rows belong to the rank that owns them and every rank
-  // adds its partial product into the owner's fp32 buffer ("reduce-scatter fused into the epilogue").
+  // peer modes (PEER instantiations only).
+  // Gathered operand ("all-gather fused into the product"): the operand's rows (the y coordinate of its
+  // TMA map: the M rows of a K-major A, the reduction rows of an MN-major A or B) are spread over the
+  // ranks, `g_rows_per_src` (a multiple of 128) each, at the same offsets of one symmetric buffer per
+  // rank. Two extra warps of every CTA pull the other ranks' rows into THIS rank's buffer -- each row
+  // crosses NVLink exactly once -- and count finished rows per 128-row block in `g_ready`; the TMA
+  // producer reads only local memory and waits for a block's count before its first load from it. The
+  // copy of rank r's rows starts after flags[g_slot * MAX_PEERS + r] reached g_epoch (g_slot < 0: at once).
+  // Row tiles of this rank's own rows are scheduled first, so the copy hides behind them.
+  // Scattered output ("reduce-scatter fused into the epilogue"): with d_rows_per_rank > 0 the rows of the
+  // output belong to the rank that owns them and every rank stores its bf16 partial product into the
+  // owner's staging buffer [world, d_rows_per_rank, N] at slice `rank`; the owner sums the slices.
   int rank, world;
-  int a_rows_per_src, b_rows_per_src;
+  int gather;               // 0 none, 1 operand A, 2 operand B
+  int g_rows_per_src;
+  long long g_ld;           // elements per row
+  int g_row_bytes;          // bytes to copy per row (multiple of 16)
+  void* g_local;
+  const void* g_src[FMB_MAX_PEERS];
+  int* g_ready;
   const uint32_t* flags;
-  int a_slot, b_slot;
-  uint32_t a_epoch, b_epoch;
+  int g_slot;
+  uint32_t g_epoch;
   unsigned long long timeout_ns;
+  int own_m_tiles;          // > 0: row tiles [rot_m, rot_m + own_m_tiles) (all column tiles) come first
   int d_rows_per_rank;
   void* d_peer[FMB_MAX_PEERS];
   int rot_m;                // row tiles are visited starting from this one (own shard first / remote first)
@@ -75,10 +87,9 @@ struct GemmParams {
   long long ld_aux_out;
 };
 
-// One tensor map per source rank (PEER) or a single one.
 template <bool PEER>
 struct MapSet {
-  CUtensorMap m[PEER ? FMB_MAX_PEERS : 1];
+  CUtensorMap m[1];
 };
 
 struct TileInfo {
@@ -105,9 +116,21 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
   }
   const int ks = tile % p.splits;
   const int mn = tile / p.splits;
-  t.m_blk = mn % p.tiles_m;
-  if (p.rot_m) t.m_blk = (t.m_blk + p.rot_m) % p.tiles_m;
-  t.n_blk = mn / p.tiles_m;
+  if (p.own_m_tiles > 0) {            // this rank's own rows first (all column tiles), then the gathered ones
+    const int own = p.own_m_tiles, first = own * p.tiles_n;
+    if (mn < first) {
+      t.m_blk = p.rot_m + mn % own;
+      t.n_blk = mn / own;
+    } else {
+      const int rest = p.tiles_m - own, r = mn - first;
+      t.m_blk = (p.rot_m + own + r % rest) % p.tiles_m;
+      t.n_blk = r / rest;
+    }
+  } else {
+    t.m_blk = mn % p.tiles_m;
+    if (p.rot_m) t.m_blk = (t.m_blk + p.rot_m) % p.tiles_m;
+    t.n_blk = mn / p.tiles_m;
+  }
   t.k0 = ks * p.kblocks_per_split;
   t.k1 = min(p.kblocks_total, t.k0 + p.kblocks_per_split);
   if (p.mode == 1) {
@@ -135,8 +158,64 @@ __device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, flo
                : "memory");
 }
 
+// Bounded wait for a counter in local memory (rows of a gathered block that have arrived).
+__device__ __forceinline__ bool wait_count(const int* ctr, int want, unsigned long long timeout_ns, int* status) {
+  const uint64_t t0 = globaltimer_ns();
+  int spins = 0;
+  for (;;) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+    if (v >= want) return true;
+    if (++spins > 32) {
+      __nanosleep(64);
+      if (globaltimer_ns() - t0 > timeout_ns) {
+        if (status != nullptr) atomicCAS(status, 0, ERR_WAIT_PEER);
+        return false;
+      }
+    }
+  }
+}
+
+constexpr int GATHER_THREADS = 64;
+
+// Executed by the two gather warps of every CTA: pull the other ranks' rows of the gathered operand into
+// this rank's buffer, 128-row block by block, nearest rank first. Row r of a block is copied by the CTA
+// with blockIdx.x == r (mod gridDim.x); each CTA adds the number of rows it finished to the block's counter.
+__device__ __forceinline__ void gather_rows(const GemmParams& p, int tid) {
+  const int vec_per_row = p.g_row_bytes >> 4;
+  const int blocks_per_src = p.g_rows_per_src >> 7;
+  for (int step = 1; step < p.world; ++step) {
+    const int src = (p.rank + step) % p.world;
+    if (p.g_slot >= 0 && !wait_epoch(p.flags + p.g_slot * MAX_PEERS + src, p.g_epoch, p.timeout_ns, p.status)) return;
+    for (int b = 0; b < blocks_per_src; ++b) {
+      const int blk = src * blocks_per_src + b;
+      int done = 0;
+      for (int r = blockIdx.x; r < 128; r += gridDim.x) {
+        const long long off = (static_cast<long long>(blk) * 128 + r) * p.g_ld * 2;
+        const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const char*>(p.g_src[src]) + off);
+        uint4* dp = reinterpret_cast<uint4*>(static_cast<char*>(p.g_local) + off);
+        for (int v0 = tid; v0 < vec_per_row; v0 += GATHER_THREADS * 8) {
+          uint4 buf[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (v0 + u * GATHER_THREADS < vec_per_row) buf[u] = ld_peer_u4(sp + v0 + u * GATHER_THREADS);
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (v0 + u * GATHER_THREADS < vec_per_row) dp[v0 + u * GATHER_THREADS] = buf[u];
+        }
+        ++done;
+      }
+      if (done) {
+        __threadfence();
+        asm volatile("bar.sync 1, 64;" ::: "memory");
+        if (tid == 0) atomicAdd(p.g_ready + blk, done);
+      }
+    }
+  }
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN, bool PEER>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS + (PEER ? GATHER_THREADS : 0), 1)
 gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant__ MapSet<PEER> tmB, GemmParams p) {
   using L = GemmSmem<BN, STAGES>;
   constexpr int BM = GEMM_BM, BK = GEMM_BK;
@@ -186,7 +265,7 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
     if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       uint32_t armed = 0, armed_parity = 0;
-      uint32_t a_ready = 0, b_ready = 0;        // peers whose shard is known to be complete
+      int ready_blk = -1;                       // last gathered 128-row block known to be complete
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
         const TileInfo ti = decode_tile(p, tile);
@@ -195,31 +274,21 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
         for (int kq = k0; kq < k1; ++kq) {
           int kb = kq;
           if (PEER && p.rot_k) { kb = kq + p.rot_k; if (kb >= k1) kb -= (k1 - k0); }
-          // source rank and shard-local row of each operand
-          int a_src = 0, a_y = A_MN ? kb * BK : m_blk * BM;
-          int b_src = 0, b_y = B_MN ? kb * BK : n_blk * BN;
+          const int a_y = A_MN ? kb * BK : m_blk * BM;
+          const int b_y = B_MN ? kb * BK : n_blk * BN;
           if constexpr (PEER) {
-            if (p.a_rows_per_src > 0) { a_src = a_y / p.a_rows_per_src; a_y -= a_src * p.a_rows_per_src; }
-            if (p.b_rows_per_src > 0) { b_src = b_y / p.b_rows_per_src; b_y -= b_src * p.b_rows_per_src; }
-            if (p.a_rows_per_src > 0 && p.a_slot >= 0 && !(a_ready & (1u << a_src))) {
-              if (a_src != p.rank &&
-                  !wait_epoch(p.flags + p.a_slot * MAX_PEERS + a_src, p.a_epoch, p.timeout_ns, p.status)) {
-                raise_abort(ab, p.status, ERR_WAIT_PEER);
-                ok = false;
-                break;
+            if (p.gather) {
+              const int blk = (p.gather == 1 ? a_y : b_y) >> 7;
+              if (blk != ready_blk) {
+                const int owner = blk / (p.g_rows_per_src >> 7);
+                if (owner != p.rank && !wait_count(p.g_ready + blk, 128, p.timeout_ns, p.status)) {
+                  raise_abort(ab, p.status, ERR_WAIT_PEER);
+                  ok = false;
+                  break;
+                }
+                ready_blk = blk;
+                fence_proxy_async_all();        // the rows were written by ordinary stores; TMA reads them next
               }
-              a_ready |= 1u << a_src;
-              fence_proxy_async_all();
-            }
-            if (p.b_rows_per_src > 0 && p.b_slot >= 0 && !(b_ready & (1u << b_src))) {
-              if (b_src != p.rank &&
-                  !wait_epoch(p.flags + p.b_slot * MAX_PEERS + b_src, p.b_epoch, p.timeout_ns, p.status)) {
-                raise_abort(ab, p.status, ERR_WAIT_PEER);
-                ok = false;
-                break;
-              }
-              b_ready |= 1u << b_src;
-              fence_proxy_async_all();
             }
           }
           if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, ab, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
@@ -228,8 +297,8 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
           mbar_expect_tx(full_bar(stage), L::STAGE_BYTES);
           armed |= 1u << stage;
           armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
-          const CUtensorMap* ma = &tmA.m[PEER ? a_src : 0];
-          const CUtensorMap* mb = &tmB.m[PEER ? b_src : 0];
+          const CUtensorMap* ma = &tmA.m[0];
+          const CUtensorMap* mb = &tmB.m[0];
           if constexpr (!A_MN) {
             tma_load_2d(sA, ma, full_bar(stage), kb * BK, a_y);
           } else {
@@ -296,6 +365,11 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
         acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
       }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------- gather warps (PEER launches only)
+    if constexpr (PEER) {
+      if (p.gather) gather_rows(p, static_cast<int>(threadIdx.x) - GEMM_THREADS);
     }
   } else {
     // ------------------------------------------------------------- epilogue warps
@@ -445,13 +519,6 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
         }
         if (p.d_f32) {
           float* dp = reinterpret_cast<float*>(p.D) + ti.d_off + static_cast<long long>(row) * p.ldd + col0;
-          if constexpr (PEER) {
-            if (p.d_rows_per_rank > 0) {          // the row's owner accumulates every rank's partial product
-              const int owner = row / p.d_rows_per_rank;
-              dp = reinterpret_cast<float*>(p.d_peer[owner]) +
-                   static_cast<long long>(row - owner * p.d_rows_per_rank) * p.ldd + col0;
-            }
-          }
           if (p.atomic) {
             if (full) {
 #pragma unroll
@@ -468,6 +535,13 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
           }
         } else {
           __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + ti.d_off + static_cast<long long>(row) * p.ldd + col0;
+          if constexpr (PEER) {
+            if (p.d_rows_per_rank > 0) {          // slice `rank` of the staging buffer of the rank that owns this row
+              const int owner = row / p.d_rows_per_rank;
+              dp = reinterpret_cast<__nv_bfloat16*>(p.d_peer[owner]) +
+                   (static_cast<long long>(p.rank) * p.d_rows_per_rank + (row - owner * p.d_rows_per_rank)) * p.ldd + col0;
+            }
+          }
           if (full) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -512,7 +586,7 @@ static cudaError_t launch_cfg(const MapSet<PEER>& ta, const MapSet<PEER>& tb, co
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  return launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), smem, stream, ta, tb, p);
+  return launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS + (PEER ? GATHER_THREADS : 0)), smem, stream, ta, tb, p);
 }
 
 static double wave_eff(long long work, int sms) {
@@ -544,15 +618,13 @@ struct EpiSpec {
 // Operands / output spread over the ranks of one NVSwitch domain (see GemmParams).
 struct PeerSpec {
   int rank = 0, world = 1;
-  const void* const* a_ptrs = nullptr;   // rank r's shard of A as mapped here (null: A is local)
-  int a_rows_per_src = 0;
-  const void* const* b_ptrs = nullptr;   // likewise for an MN-major B
-  int b_rows_per_src = 0;
-  void* const* d_ptrs = nullptr;         // fp32 reduce-scatter destinations (null: D is local)
-  int d_rows_per_rank = 0;
+  int gather = 0;                        // 0 none, 1 operand A, 2 operand B (MN-major only)
+  const void* const* gather_ptrs = nullptr;   // rank r's full-size buffer of the gathered operand, as mapped here
+  int* ready = nullptr;                  // one counter per 128-row block of the gathered operand
+  void* const* d_ptrs = nullptr;         // bf16 staging buffers [world, rows / world, N] (null: D is local)
   const uint32_t* flags = nullptr;       // this rank's flag words
-  int a_slot = -1, b_slot = -1;
-  uint32_t a_epoch = 0, b_epoch = 0;
+  int slot = -1;
+  uint32_t epoch = 0;
   unsigned long long timeout_ns = 2000000000ull;
 };
 }  // namespace fmb
@@ -580,22 +652,18 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
       return -2;
     if (es->epi < 1 || es->epi > 3) return -2;
   }
+  int g_rows = 0, g_rps = 0;
   if (ps != nullptr) {
     if (gs.mode != 0 || ps->world < 1 || ps->world > FMB_MAX_PEERS || ps->rank < 0 || ps->rank >= ps->world) return -2;
-    if (ps->a_ptrs != nullptr) {
-      const int unit = a_mn ? GEMM_BK_C : 128;
-      if (ps->a_rows_per_src <= 0 || ps->a_rows_per_src % unit) return -2;
-      if (static_cast<long long>(ps->a_rows_per_src) * ps->world != (a_mn ? K : M)) return -2;
+    if (ps->gather == 1) g_rows = a_mn ? K : M;
+    else if (ps->gather == 2) { if (!b_mn) return -2; g_rows = K; }
+    else if (ps->gather != 0) return -2;
+    if (ps->gather) {
+      if (ps->gather_ptrs == nullptr || ps->ready == nullptr || g_rows % (128 * ps->world)) return -2;
+      g_rps = g_rows / ps->world;
+      if (ps->slot >= 0 && ps->flags == nullptr) return -2;
     }
-    if (ps->b_ptrs != nullptr) {
-      if (!b_mn || ps->b_rows_per_src <= 0 || ps->b_rows_per_src % GEMM_BK_C) return -2;
-      if (static_cast<long long>(ps->b_rows_per_src) * ps->world != K) return -2;
-    }
-    if (ps->d_ptrs != nullptr) {
-      if (!d_f32 || C != nullptr || ps->d_rows_per_rank <= 0 || ps->d_rows_per_rank % 128) return -2;
-      if (static_cast<long long>(ps->d_rows_per_rank) * ps->world != M) return -2;
-    }
-    if ((ps->a_slot >= 0 || ps->b_slot >= 0) && ps->flags == nullptr) return -2;
+    if (ps->d_ptrs != nullptr && (d_f32 || C != nullptr || M % (128 * ps->world))) return -2;
   }
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(D) & 15) || (ldd % (d_f32 ? 4 : 8)))
@@ -648,13 +716,42 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
   p.region = gs.region;
   p.group_stride_d = gs.group_stride_d;
   p.rank = 0; p.world = 1;
-  p.a_rows_per_src = p.b_rows_per_src = p.d_rows_per_rank = 0;
-  p.flags = nullptr;
-  p.a_slot = p.b_slot = -1;
-  p.a_epoch = p.b_epoch = 0;
-  p.timeout_ns = 0;
+  p.gather = 0; p.g_rows_per_src = 0; p.g_ld = 0; p.g_row_bytes = 0; p.g_local = nullptr; p.g_ready = nullptr;
+  p.flags = nullptr; p.g_slot = -1; p.g_epoch = 0; p.timeout_ns = 0;
+  p.own_m_tiles = 0; p.d_rows_per_rank = 0;
   p.rot_m = p.rot_k = 0;
-  for (int r = 0; r < FMB_MAX_PEERS; ++r) p.d_peer[r] = nullptr;
+  for (int r = 0; r < FMB_MAX_PEERS; ++r) { p.d_peer[r] = nullptr; p.g_src[r] = nullptr; }
+  if (ps != nullptr) {
+    p.rank = ps->rank; p.world = ps->world;
+    p.flags = ps->flags; p.g_slot = ps->slot; p.g_epoch = ps->epoch; p.timeout_ns = ps->timeout_ns;
+    if (ps->gather) {
+      const bool on_a = ps->gather == 1;
+      p.gather = ps->gather;
+      p.g_rows_per_src = g_rps;
+      p.g_ld = on_a ? lda : ldb;
+      p.g_row_bytes = 2 * (on_a ? (a_mn ? M : K) : N);
+      if (p.g_row_bytes % 16) return -2;
+      p.g_local = const_cast<void*>(on_a ? A : B);
+      p.g_ready = ps->ready;
+      for (int r = 0; r < ps->world; ++r) {
+        if (ps->gather_ptrs[r] == nullptr || (reinterpret_cast<uintptr_t>(ps->gather_ptrs[r]) & 15)) return -2;
+        p.g_src[r] = ps->gather_ptrs[r];
+      }
+      if (cudaMemsetAsync(ps->ready, 0, sizeof(int) * static_cast<size_t>(g_rows / 128), stream) != cudaSuccess) return -3;
+      if (on_a && !a_mn) {              // row tiles: own rows first
+        p.own_m_tiles = g_rps / GEMM_BM;
+        p.rot_m = ps->rank * p.own_m_tiles;
+      } else {                          // reduction blocks: start with the own ones
+        p.rot_k = ps->rank * (g_rps / GEMM_BK);
+      }
+    }
+    if (ps->d_ptrs != nullptr) {
+      p.d_rows_per_rank = M / ps->world;
+      for (int r = 0; r < ps->world; ++r) p.d_peer[r] = ps->d_ptrs[r];
+      if (p.rot_m == 0 && p.own_m_tiles == 0)
+        p.rot_m = ((ps->rank + 1) % ps->world) * (p.d_rows_per_rank / GEMM_BM);   // remote rows first
+    }
+  }
   p.epi = 0; p.epi_h = 0; p.seg = 0;
   p.aux_in = nullptr; p.ld_aux_in = 0; p.aux_out = nullptr; p.ld_aux_out = 0;
   if (es != nullptr && es->epi != 0) {
@@ -663,28 +760,6 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
     p.aux_out = es->aux_out; p.ld_aux_out = es->ld_aux_out;
     if (es->epi == 1) p.tiles_n = es->h / 128;          // a tile = 128 hidden units = 128 gate + 128 up columns
   }
-  if (ps != nullptr) {
-    p.rank = ps->rank; p.world = ps->world;
-    p.flags = ps->flags;
-    p.a_slot = ps->a_slot; p.b_slot = ps->b_slot;
-    p.a_epoch = ps->a_epoch; p.b_epoch = ps->b_epoch;
-    p.timeout_ns = ps->timeout_ns;
-    if (ps->a_ptrs != nullptr) {
-      p.a_rows_per_src = ps->a_rows_per_src;
-      if (a_mn) p.rot_k = ps->rank * (ps->a_rows_per_src / GEMM_BK);
-      else      p.rot_m = ps->rank * (ps->a_rows_per_src / GEMM_BM);
-    }
-    if (ps->b_ptrs != nullptr) {
-      p.b_rows_per_src = ps->b_rows_per_src;
-      p.rot_k = ps->rank * (ps->b_rows_per_src / GEMM_BK);
-    }
-    if (ps->d_ptrs != nullptr) {
-      p.d_rows_per_rank = ps->d_rows_per_rank;
-      p.atomic = 1;                       // partial products of all ranks meet in the owner's buffer
-      for (int r = 0; r < ps->world; ++r) p.d_peer[r] = ps->d_ptrs[r];
-      if (p.rot_m == 0) p.rot_m = ((ps->rank + 1) % ps->world) * (ps->d_rows_per_rank / GEMM_BM);   // remote rows first
-    }
-  }
   if (splits > 1) {
     // Every split adds alpha*partial into D, which already holds the C term (C == D) or zeros.
     if (C == D && beta == 1.f) { p.C = nullptr; }
@@ -692,36 +767,24 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
     else return -4;
   }
 
-  const int n_src = ps != nullptr ? ps->world : 1;
   MapSet<true> ta, tb;
   bool ok = true;
-  for (int r = 0; r < n_src && ok; ++r) {
-    const bool a_sharded = ps != nullptr && ps->a_ptrs != nullptr;
-    const void* abase = a_sharded ? ps->a_ptrs[r] : A;
-    if (a_sharded && (abase == nullptr || (reinterpret_cast<uintptr_t>(abase) & 15))) return -2;
-    if (!a_mn) ok = make_tmap_2d(&ta.m[r], abase, a_sharded ? ps->a_rows_per_src : M, K, lda, GEMM_BM, GEMM_BK, 2,
-                                 TmapSwizzle::B128);
-    else       ok = make_tmap_2d(&ta.m[r], abase, a_sharded ? ps->a_rows_per_src : K, M, lda, GEMM_BK, 64, 2,
-                                 TmapSwizzle::B128);
-    if (!ok) break;
+  if (!a_mn) ok = make_tmap_2d(&ta.m[0], A, M, K, lda, GEMM_BM, GEMM_BK, 2, TmapSwizzle::B128);
+  else       ok = make_tmap_2d(&ta.m[0], A, K, M, lda, GEMM_BK, 64, 2, TmapSwizzle::B128);
+  if (ok) {
     // B is always described by a 3-D map (inner, rows, group); plain products have one group.
-    const bool b_sharded = ps != nullptr && ps->b_ptrs != nullptr;
-    const void* bbase = b_sharded ? ps->b_ptrs[r] : B;
-    if (b_sharded && (bbase == nullptr || (reinterpret_cast<uintptr_t>(bbase) & 15))) return -2;
     const int nb = gs.mode == 1 ? gs.n_groups : 1;
-    const uint64_t brows = b_mn ? (b_sharded ? ps->b_rows_per_src : K) : N;
     const uint64_t gstride = gs.mode == 1 ? static_cast<uint64_t>(gs.group_stride_b)
-                                          : brows * static_cast<uint64_t>(ldb);
+                                          : static_cast<uint64_t>(b_mn ? K : N) * static_cast<uint64_t>(ldb);
     uint64_t dims[3], strides[3];
     uint32_t box[3];
     if (!b_mn) { dims[0] = K; dims[1] = N; box[0] = GEMM_BK; box[1] = (p.epi == 1) ? 128 : best_bn; }
-    else       { dims[0] = N; dims[1] = brows; box[0] = 64; box[1] = GEMM_BK; }
+    else       { dims[0] = N; dims[1] = K; box[0] = 64; box[1] = GEMM_BK; }
     dims[2] = nb; box[2] = 1;
     strides[0] = 2; strides[1] = static_cast<uint64_t>(ldb) * 2; strides[2] = gstride * 2;
-    ok = make_tmap_nd(&tb.m[r], bbase, 3, dims, strides, box, 2, TmapSwizzle::B128);
+    ok = make_tmap_nd(&tb.m[0], B, 3, dims, strides, box, 2, TmapSwizzle::B128);
   }
   if (!ok) return -5;
-  for (int r = n_src; r < FMB_MAX_PEERS; ++r) { ta.m[r] = ta.m[0]; tb.m[r] = tb.m[0]; }
 
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * (gs.mode == 2 ? gs.n_groups : p.splits);
   const int grid = static_cast<int>(total < sms ? total : sms);
@@ -781,31 +844,26 @@ extern "C" int fmb_gemm_bf16_grouped(const void* A, const void* B, void* D, cons
 }
 
 // Products whose operands or output are spread over the ranks of one NVSwitch domain.
-//   a_ptrs / b_ptrs   `world` device pointers: rank r's shard as mapped into this process (null: local)
-//   d_ptrs            fp32 reduce-scatter destinations, [d_rows_per_rank, N] on each rank (null: local D)
-//   flags             this rank's flag words; slot < 0 means "do not wait"
+//   gather        1: A, 2: B (MN-major) is the operand whose rows are spread over the ranks; A / B then points to
+//                 THIS rank's full-size symmetric buffer, of which only the own rows need to be filled in
+//   gather_ptrs   `world` device pointers: rank r's buffer as mapped into this process
+//   ready         int counters, one per 128 rows of the gathered operand (cleared here)
+//   d_ptrs        bf16 staging buffers [world, M / world, N] of every rank (null: D is an ordinary local output)
+//   flags         this rank's flag words; rank r's rows are copied once flags[slot * 8 + r] reached epoch
 extern "C" int fmb_gemm_bf16_peer(const void* A, const void* B, void* D, int M, int N, int K, int a_mn, int b_mn,
                                   long long lda, long long ldb, long long ldd, int d_f32, float alpha, int accumulate,
-                                  int rank, int world, const void* const* a_ptrs, int a_rows_per_src,
-                                  const void* const* b_ptrs, int b_rows_per_src, void* const* d_ptrs,
-                                  int d_rows_per_rank, const unsigned* flags, int a_slot, unsigned a_epoch,
-                                  int b_slot, unsigned b_epoch, unsigned long long timeout_ns, int* status,
-                                  cudaStream_t stream) {
+                                  int rank, int world, int gather, const void* const* gather_ptrs, int* ready,
+                                  void* const* d_ptrs, const unsigned* flags, int slot, unsigned epoch,
+                                  unsigned long long timeout_ns, int* status, cudaStream_t stream) {
   fmb::GroupSpec gs;
   fmb::PeerSpec ps;
   ps.rank = rank; ps.world = world;
-  ps.a_ptrs = a_ptrs; ps.a_rows_per_src = a_rows_per_src;
-  ps.b_ptrs = b_ptrs; ps.b_rows_per_src = b_rows_per_src;
-  ps.d_ptrs = d_ptrs; ps.d_rows_per_rank = d_rows_per_rank;
-  ps.flags = flags;
-  ps.a_slot = a_slot; ps.a_epoch = a_epoch;
-  ps.b_slot = b_slot; ps.b_epoch = b_epoch;
+  ps.gather = gather; ps.gather_ptrs = gather_ptrs; ps.ready = ready;
+  ps.d_ptrs = d_ptrs;
+  ps.flags = flags; ps.slot = slot; ps.epoch = epoch;
   ps.timeout_ns = timeout_ns;
-  const void* a0 = a_ptrs != nullptr ? a_ptrs[rank] : A;
-  const void* b0 = b_ptrs != nullptr ? b_ptrs[rank] : B;
-  void* d0 = d_ptrs != nullptr ? d_ptrs[rank] : D;
   const bool acc = accumulate && d_ptrs == nullptr;      // D += product (local output only)
-  return run_gemm(a0, b0, d0, acc ? d0 : nullptr, M, N, K, a_mn, b_mn, lda, ldb, ldd, acc ? ldd : 0, d_f32,
+  return run_gemm(A, B, D, acc ? D : nullptr, M, N, K, a_mn, b_mn, lda, ldb, ldd, acc ? ldd : 0, d_f32,
                   acc ? d_f32 : 0, alpha, acc ? 1.f : 0.f, nullptr, 0, status, 0, gs, stream, &ps);
 }
 

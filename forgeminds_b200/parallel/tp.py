@@ -6,22 +6,25 @@ block is then one kernel that does its collective while it computes (``csrc/gemm
 instantiations):
 
 * column-parallel ``wq|wk|wv`` and ``w1|w3``: **all-gather -> GEMM**. Each rank publishes its
-  normalised rows in a symmetric buffer; the GEMM's TMA producer reads every row tile from the rank
-  that owns it (one tensor map per rank, no multicast), after a bounded wait on that rank's flag,
-  starting with its own rows so that the remote tiles arrive while the local ones are multiplied.
-* row-parallel ``wo`` and ``w2``: **GEMM -> reduce-scatter**. The epilogue adds each 128-row tile of
-  the partial product into the fp32 buffer of the rank that owns those rows (``red.global.add.v4.f32``
-  on the peer pointer), remote rows first.
+  normalised rows in its slice of a symmetric ``[M, d]`` buffer. Two extra warps of every CTA of the
+  GEMM pull the other ranks' slices into the local buffer -- every row crosses NVLink once -- and count
+  arrived rows per 128-row block; the TMA producer reads local memory only, multiplies this rank's own
+  rows first and waits (bounded) for a block's count before it touches it.
+* row-parallel ``wo`` and ``w2``: **GEMM -> reduce-scatter**. The epilogue stores each 128-row tile of
+  the bf16 partial product into the staging buffer of the rank that owns those rows (slice = source
+  rank), remote rows first; after a flag barrier the owner sums the slices (fp32, fixed order) together
+  with the residual.
 
 The backward uses the same two kernels: the input gradient of a column-parallel layer is a
 GEMM -> reduce-scatter, its weight gradient an all-gather -> GEMM with the gathered operand on the
-reduction side; for a row-parallel layer the roles swap.
+reduction side; for a row-parallel layer the roles swap (and its second product reuses the rows the
+first one gathered).
 
-Buffer protocol (one :class:`TPState` per group). Two publish buffers (activations, gradients) and
-one fp32 accumulator, each ``[Ms, d]``. A publish is always separated from the previous product
-that read the same buffer by a full flag barrier (every reduce-scatter ends with one), and an
-accumulator is zeroed by its owner right after it has been read, before the owner's next publish,
-which every peer waits for before it can reach its next reduce-scatter into that accumulator.
+Buffer protocol (one :class:`TPState` per group). Two gather buffers ``[M, d]`` (activations,
+gradients) and one staging buffer ``[W, Ms, d]``. A publish is always separated from the previous
+product that read the same slice by a full flag barrier (every reduce-scatter ends with one), and a
+peer can only reach its next reduce-scatter into a rank's staging buffer after waiting for that rank's
+next publish, which comes after the rank has summed the buffer.
 
 The reference expresses the same layout with DTensor ``ColwiseParallel`` / ``RowwiseParallel`` and
 NCCL all-reduces (``forgemind/parallel/native.py:21-49``); that path remains the fallback
@@ -56,32 +59,41 @@ class TPState:
         self._bufs: dict = {}
 
     def buffers(self, rows: int, width: int):
-        """(publish-activations, publish-gradients, accumulator) for shards of ``[rows, width]``."""
+        """(gather buffer for activations, gather buffer for gradients, staging) for row shards ``[rows, width]``:
+        the gather buffers hold ``[world * rows, width]``, the staging buffer ``[world, rows, width]``."""
         key = (rows, width)
         if key not in self._bufs:
-            sg = self.sg
-            self._bufs[key] = (sg.alloc(rows * width, BF16), sg.alloc(rows * width, BF16),
-                               sg.alloc(rows * width, torch.float32))
+            sg, w = self.sg, self.world
+            self._bufs[key] = (sg.alloc(w * rows * width, BF16), sg.alloc(w * rows * width, BF16),
+                               sg.alloc(w * rows * width, BF16),
+                               torch.zeros(max(1, w * rows // 128), dtype=torch.int32, device=sg.device))
         return self._bufs[key]
 
     def publish(self, buf, slot: int, shard: torch.Tensor) -> int:
-        """Copy ``shard`` into the symmetric buffer and tell the peers; returns the epoch to wait for."""
-        buf.local.view(shard.shape).copy_(shard)
+        """Copy ``shard`` into this rank's slice of the gather buffer and tell the peers; returns the epoch."""
+        rows = shard.shape[0]
+        buf.local.view(self.world * rows, -1)[self.rank * rows:(self.rank + 1) * rows].copy_(shard)
         epoch = self.sg.next_epoch(slot)
         ops.require().comm_signal(self.sg.flags.ptrs, slot, epoch, self.rank, self.sg.status)
         return epoch
 
-    def gemm(self, a, b, out, a_mn=False, b_mn=False, accumulate=False, a_buf=None, b_buf=None, d_buf=None,
-             a_wait=(-1, 0), b_wait=(-1, 0)):
+    def gemm(self, a, b, out, a_mn=False, b_mn=False, accumulate=False, gather=0, gather_buf=None, ready=None,
+             d_buf=None, wait=(-1, 0)):
         sg = self.sg
-        ops.require().gemm_peer(a, b, out, a_mn, b_mn, 1.0, accumulate, self.rank, self.world,
-                                a_buf.ptrs if a_buf is not None else [], b_buf.ptrs if b_buf is not None else [],
-                                d_buf.ptrs if d_buf is not None else [], sg.flags.local, a_wait[0], a_wait[1],
-                                b_wait[0], b_wait[1], sg.timeout_ms, sg.status)
+        ops.require().gemm_peer(a, b, out, a_mn, b_mn, 1.0, accumulate, self.rank, self.world, gather,
+                                gather_buf.ptrs if gather else [], ready if gather else None,
+                                d_buf.ptrs if d_buf is not None else [], sg.flags.local, wait[0], wait[1],
+                                sg.timeout_ms, sg.status)
         return out
 
     def barrier(self):
         self.sg.barrier(self.slot_bar)
+
+    def reduce(self, staging, rows: int, width: int, residual=None) -> torch.Tensor:
+        """Sum of the slices that the ranks stored into this rank's staging buffer (+ residual)."""
+        out = torch.empty((rows, width), dtype=BF16, device=self.sg.device)
+        ops.require().comm_sum_partials(staging.local, residual, out, self.world)
+        return out
 
 
 def _main_grad_or_new(param, shape, device):
@@ -99,10 +111,11 @@ class _GatherLinear(torch.autograd.Function):
         from ..ops.functional import bf16_of
         w = bf16_of(weight)
         ms, k = x_shard.shape
-        act, _, _ = tp.buffers(ms, k)
+        act, _, _, ready = tp.buffers(ms, k)
         epoch = tp.publish(act, tp.slot_act, x_shard)
-        y = torch.empty((ms * tp.world, w.shape[0]), dtype=BF16, device=x_shard.device)
-        tp.gemm(act.local.view(ms, k), w, y, a_buf=act, a_wait=(tp.slot_act, epoch))
+        m = ms * tp.world
+        y = torch.empty((m, w.shape[0]), dtype=BF16, device=x_shard.device)
+        tp.gemm(act.local.view(m, k), w, y, gather=1, gather_buf=act, ready=ready, wait=(tp.slot_act, epoch))
         ctx.save_for_backward(x_shard, w)
         ctx.tp, ctx.weight = tp, weight
         return y
@@ -113,23 +126,23 @@ class _GatherLinear(torch.autograd.Function):
         x_shard, w = ctx.saved_tensors
         tp, weight = ctx.tp, ctx.weight
         ms, k = x_shard.shape
-        act, _, acc = tp.buffers(ms, k)
+        m = ms * tp.world
+        act, _, staging, ready = tp.buffers(ms, k)
         dy = dy.contiguous()
         dw = None
         if ctx.needs_input_grad[1]:
             # dW[N_l, K] = dy[M, N_l].T @ gather(x)[M, K]: the gathered operand is on the reduction side
             epoch = tp.publish(act, tp.slot_act, x_shard)
             out, is_main = _main_grad_or_new(weight, w.shape, dy.device)
-            tp.gemm(dy, act.local.view(ms, k), out, a_mn=True, b_mn=True, accumulate=is_main, b_buf=act,
-                    b_wait=(tp.slot_act, epoch))
+            tp.gemm(dy, act.local.view(m, k), out, a_mn=True, b_mn=True, accumulate=is_main, gather=2, gather_buf=act,
+                    ready=ready, wait=(tp.slot_act, epoch))
             dw = None if is_main else out.to(weight.dtype)
         dx = None
         if ctx.needs_input_grad[0]:
             # dx_shard = reduce_scatter_rows(dy @ W_local)
-            tp.gemm(dy, w, acc.local.view(ms, k), b_mn=True, d_buf=acc)
+            tp.gemm(dy, w, staging.local.view(m, k), b_mn=True, d_buf=staging)
             tp.barrier()
-            dx = acc.local.view(ms, k).to(BF16)
-            acc.local.zero_()
+            dx = tp.reduce(staging, ms, k)
         return dx, dw, None
 
 
@@ -142,14 +155,11 @@ class _LinearScatter(torch.autograd.Function):
         w = bf16_of(weight)
         m, n = h.shape[0], w.shape[0]
         ms = m // tp.world
-        _, _, acc = tp.buffers(ms, n)
+        _, _, staging, _ = tp.buffers(ms, n)
         h = h.contiguous()
-        tp.gemm(h, w, acc.local.view(ms, n), d_buf=acc)
+        tp.gemm(h, w, staging.local.view(m, n), d_buf=staging)
         tp.barrier()
-        out = acc.local.view(ms, n).to(BF16)
-        acc.local.zero_()
-        if residual is not None:
-            out += residual
+        out = tp.reduce(staging, ms, n, residual.contiguous() if residual is not None else None)
         ctx.save_for_backward(h, w)
         ctx.tp, ctx.weight, ctx.has_res = tp, weight, residual is not None
         return out
@@ -160,19 +170,26 @@ class _LinearScatter(torch.autograd.Function):
         h, w = ctx.saved_tensors
         tp, weight = ctx.tp, ctx.weight
         ms, n = dout.shape
-        _, grad, _ = tp.buffers(ms, n)
+        m = ms * tp.world
+        _, grad, _, ready = tp.buffers(ms, n)
         dout = dout.contiguous()
         epoch = tp.publish(grad, tp.slot_grad, dout)
+        full = grad.local.view(m, n)
         dh = dw = None
+        gathered = False
         if ctx.needs_input_grad[0]:
             # dh[M, K_l] = gather(dout)[M, N] @ W_local[N, K_l]
             dh = torch.empty_like(h)
-            tp.gemm(grad.local.view(ms, n), w, dh, b_mn=True, a_buf=grad, a_wait=(tp.slot_grad, epoch))
+            tp.gemm(full, w, dh, b_mn=True, gather=1, gather_buf=grad, ready=ready, wait=(tp.slot_grad, epoch))
+            gathered = True
         if ctx.needs_input_grad[1]:
-            # dW[N, K_l] = gather(dout)[M, N].T @ h[M, K_l]
+            # dW[N, K_l] = gather(dout)[M, N].T @ h[M, K_l]; the rows are already here after the product above
             out, is_main = _main_grad_or_new(weight, w.shape, dout.device)
-            tp.gemm(grad.local.view(ms, n), h, out, a_mn=True, b_mn=True, accumulate=is_main, a_buf=grad,
-                    a_wait=(tp.slot_grad, epoch))
+            if gathered:
+                tp.gemm(full, h, out, a_mn=True, b_mn=True, accumulate=is_main)
+            else:
+                tp.gemm(full, h, out, a_mn=True, b_mn=True, accumulate=is_main, gather=1, gather_buf=grad, ready=ready,
+                        wait=(tp.slot_grad, epoch))
             dw = None if is_main else out.to(weight.dtype)
         return dh, dw, (dout if ctx.has_res else None), None
 
