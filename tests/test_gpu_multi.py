@@ -20,41 +20,43 @@ def _run(scenario: str, nproc: int, port: int, timeout: int = 420):
 
 
 needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+# number of ranks of the multi-process scenarios: 2, or 4 when FMB_TEST_RANKS=4 and the box has them
+RANKS = 4 if (os.environ.get("FMB_TEST_RANKS") == "4" and torch.cuda.device_count() >= 4) else 2
 
 
 @needs2
 def test_peer_kernels_two_ranks():
-    _run("peer_kernels", 2, 29611)
+    _run("peer_kernels", RANKS, 29611)
 
 
 @needs2
 def test_peer_trainer_two_ranks():
-    _run("peer_trainer", 2, 29612)
+    _run("peer_trainer", RANKS, 29612)
 
 
 @needs2
 def test_gemm_with_gathered_operands_and_scattered_output_two_ranks():
-    _run("gemm_peer", 2, 29613)
+    _run("gemm_peer", RANKS, 29613)
 
 
 @needs2
 def test_fused_tensor_parallel_gradients_two_ranks():
-    _run("tp_grads", 2, 29615)
+    _run("tp_grads", RANKS, 29615)
 
 
 @needs2
 def test_fused_tensor_parallel_two_ranks():
-    _run("tp_fused", 2, 29614)
+    _run("tp_fused", RANKS, 29614)
 
 
 @needs2
 def test_expert_parallel_over_peer_memory_two_ranks():
-    _run("ep_fused", 2, 29616)
+    _run("ep_fused", RANKS, 29616)
 
 
 @needs2
 def test_missing_rank_is_reported_not_waited_for_forever():
-    _run("peer_failure", 2, 29617)
+    _run("peer_failure", RANKS, 29617)
 
 
 def test_peer_step_single_rank(cuda_status):
