@@ -255,7 +255,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       *put_slot = mx;
-      if (!named_bar_and(1, 32 * ATT_ROW_WARPS, ok)) { alive = false; break; }
+      // only the two warps that share these 32 rows meet here (barrier 1 + quarter, 64 threads)
+      if (!named_bar_and(1 + quarter, 64, ok)) { alive = false; break; }
       const float m_new = fmaxf(m_run, fmaxf(mx, *get_slot) * p.scale_log2);
       const float alpha = exp2f(m_run - m_new);          // 0 on the first tile (m_run = -inf)
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -318,7 +319,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       bool ok = mbar_wait_bounded(o_full, 0, ab, p.status, ERR_WAIT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       *put_slot = l_run;                                  // P is no longer read: the last MMA has completed
-      if (named_bar_and(1, 32 * ATT_ROW_WARPS, ok)) {
+      if (named_bar_and(1 + quarter, 64, ok)) {
         tc_fence_after();
         const float l_tot = l_run + *get_slot;
         const float inv_l = 1.f / l_tot;

@@ -8,24 +8,6 @@
 
 #include "fmb_api.h"
 
-extern "C" {
-int fmb_sqnorm_f32_scratch(const float* x, float* partial, float* out, long long n, int accumulate, cudaStream_t stream);
-int fmb_router_blocks(long long rows);
-int fmb_router_fwd(const void* logits, long long ld, int dtype, float* probs, float* weights, int* idx, float* lse,
-                   float* psum_partial, int* counts, long long rows, int E, int k, int nblocks, cudaStream_t stream);
-int fmb_router_bwd(const float* probs, const int* idx, const float* weights, const float* lse, const float* dweights,
-                   const float* aux_grad, const float* zc, void* dlogits, long long ld, int dtype, long long rows, int E,
-                   int k, cudaStream_t stream);
-int fmb_moe_plan(const int* idx, int* chunk_counts, int* region, int* meta, int* slot_of_entry, int* token_of_slot,
-                 long long entries, int E, int k, int align, int cap, int mode, cudaStream_t stream);
-int fmb_moe_tile_groups(const int* region, int* tile_group, int n_tiles, int E, cudaStream_t stream);
-int fmb_gemm_bf16_grouped(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int a_mn, int b_mn,
-                          long long lda, long long ldb, long long ldd, long long ldc, int d_f32, int c_f32, float alpha,
-                          float beta, int mode, int n_groups, const int* tile_group, const int* region,
-                          long long group_stride_b, long long group_stride_d, int* status, cudaStream_t stream);
-int fmb_moe_combine_bwd(const void* dout, const void* ys, const int* slot_of_entry, const float* w, void* dys, float* dw,
-                        long long entries, int k, int d, cudaStream_t stream);
-}
 
 namespace {
 
@@ -183,23 +165,31 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
   return {dx, dw};
 }
 
-Tensor swiglu_fwd(const Tensor& gate, const Tensor& up) {
+const int* limit_ptr(const c10::optional<Tensor>& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->numel() >= 1, "row limit: CUDA int32 tensor required");
+  return t->data_ptr<int>();
+}
+
+Tensor swiglu_fwd(const Tensor& gate, const Tensor& up, const c10::optional<Tensor>& row_limit) {
   TORCH_CHECK(gate.is_cuda() && gate.stride(-1) == 1 && up.stride(-1) == 1 && gate.dim() == 2 && up.dim() == 2);
   TORCH_CHECK(gate.stride(0) == up.stride(0), "swiglu: gate and up must share a row pitch");
   c10::cuda::CUDAGuard guard(gate.device());
   Tensor out = torch::empty({gate.size(0), gate.size(1)}, gate.options());
   ok(fmb_swiglu_fwd(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.size(0), static_cast<int>(gate.size(1)),
-                    gate.stride(0), dt(gate), cur_stream()), "swiglu_fwd");
+                    gate.stride(0), dt(gate), limit_ptr(row_limit), cur_stream()), "swiglu_fwd");
   return out;
 }
 
-void swiglu_bwd(const Tensor& gate, const Tensor& up, const Tensor& dy, Tensor& dgate, Tensor& dup) {
+void swiglu_bwd(const Tensor& gate, const Tensor& up, const Tensor& dy, Tensor& dgate, Tensor& dup,
+                const c10::optional<Tensor>& row_limit) {
   TORCH_CHECK(gate.dim() == 2 && gate.stride(0) == up.stride(0) && dgate.stride(0) == gate.stride(0) &&
               dup.stride(0) == gate.stride(0), "swiglu_bwd: all gate/up views must share one row pitch");
   cuda_contig(dy, "dy");
   c10::cuda::CUDAGuard guard(gate.device());
   ok(fmb_swiglu_bwd(gate.data_ptr(), up.data_ptr(), dy.data_ptr(), dgate.data_ptr(), dup.data_ptr(), gate.size(0),
-                    static_cast<int>(gate.size(1)), gate.stride(0), dt(gate), cur_stream()), "swiglu_bwd");
+                    static_cast<int>(gate.size(1)), gate.stride(0), dt(gate), limit_ptr(row_limit), cur_stream()),
+     "swiglu_bwd");
 }
 
 void rope(const Tensor& x, Tensor& out, const Tensor& cos, const Tensor& sin, int64_t T, int64_t n_rot,
@@ -786,8 +776,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
-  m.def("swiglu_fwd", &swiglu_fwd);
-  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd, pybind11::arg("gate"), pybind11::arg("up"), pybind11::arg("row_limit") = pybind11::none());
+  m.def("swiglu_bwd", &swiglu_bwd, pybind11::arg("gate"), pybind11::arg("up"), pybind11::arg("dy"), pybind11::arg("dgate"),
+        pybind11::arg("dup"), pybind11::arg("row_limit") = pybind11::none());
   m.def("rope", &rope);
   m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);

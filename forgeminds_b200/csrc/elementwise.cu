@@ -235,9 +235,10 @@ colsum_kernel(const float* __restrict__ part, float* __restrict__ out, int nrows
 // ------------------------------------------------------------------ SwiGLU
 template <typename T>
 __global__ void swiglu_fwd_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out,
-                                  long long rows, int h, long long ld_in) {
+                                  long long rows, int h, long long ld_in, const int* __restrict__ row_limit) {
   pdl_wait();
   pdl_launch_dependents();
+  if (row_limit != nullptr) rows = min(rows, static_cast<long long>(*row_limit));   // rows known only on the device
   const int hv = h >> 3;
   const long long total = rows * hv;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -255,9 +256,11 @@ __global__ void swiglu_fwd_kernel(const T* __restrict__ gate, const T* __restric
 
 template <typename T>
 __global__ void swiglu_bwd_kernel(const T* __restrict__ gate, const T* __restrict__ up, const T* __restrict__ dy,
-                                  T* __restrict__ dgate, T* __restrict__ dup, long long rows, int h, long long ld_in) {
+                                  T* __restrict__ dgate, T* __restrict__ dup, long long rows, int h, long long ld_in,
+                                  const int* __restrict__ row_limit) {
   pdl_wait();
   pdl_launch_dependents();
+  if (row_limit != nullptr) rows = min(rows, static_cast<long long>(*row_limit));
   const int hv = h >> 3;
   const long long total = rows * hv;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -843,26 +846,26 @@ extern "C" int fmb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
 }
 
 extern "C" int fmb_swiglu_fwd(const void* gate, const void* up, void* out, long long rows, int h, long long ld_in,
-                              int dtype, cudaStream_t stream) {
+                              int dtype, const int* row_limit, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (h % 8 || ld_in % 8) return -2;
   return by_dtype(dtype, [&](auto* tp) {
     using T = std::remove_pointer_t<decltype(tp)>;
     return launch_pdl(swiglu_fwd_kernel<T>, dim3(grid_for(rows * (h / 8), 256)), dim3(256), 0, stream,
                       static_cast<const T*>(gate), static_cast<const T*>(up), static_cast<T*>(out), rows, h,
-                      ld_in) == cudaSuccess ? 0 : -3;
+                      ld_in, row_limit) == cudaSuccess ? 0 : -3;
   });
 }
 
 extern "C" int fmb_swiglu_bwd(const void* gate, const void* up, const void* dy, void* dgate, void* dup, long long rows,
-                              int h, long long ld_in, int dtype, cudaStream_t stream) {
+                              int h, long long ld_in, int dtype, const int* row_limit, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (h % 8 || ld_in % 8) return -2;
   return by_dtype(dtype, [&](auto* tp) {
     using T = std::remove_pointer_t<decltype(tp)>;
     return launch_pdl(swiglu_bwd_kernel<T>, dim3(grid_for(rows * (h / 8), 256)), dim3(256), 0, stream,
                       static_cast<const T*>(gate), static_cast<const T*>(up), static_cast<const T*>(dy),
-                      static_cast<T*>(dgate), static_cast<T*>(dup), rows, h, ld_in) == cudaSuccess ? 0 : -3;
+                      static_cast<T*>(dgate), static_cast<T*>(dup), rows, h, ld_in, row_limit) == cudaSuccess ? 0 : -3;
   });
 }
 

@@ -33,10 +33,11 @@ int fmb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
                     float* dw_partial, float* dw, int dw_accumulate, long long rows, int d, int dtype, int w_dtype,
                     int nblocks, cudaStream_t stream);
 int fmb_rmsnorm_bwd_blocks(long long rows, int d);
+// `row_limit` (device int, may be null): process only the first min(rows, *row_limit) rows
 int fmb_swiglu_fwd(const void* gate, const void* up, void* out, long long rows, int h, long long ld_in, int dtype,
-                   cudaStream_t stream);
+                   const int* row_limit, cudaStream_t stream);
 int fmb_swiglu_bwd(const void* gate, const void* up, const void* dy, void* dgate, void* dup, long long rows, int h,
-                   long long ld_in, int dtype, cudaStream_t stream);
+                   long long ld_in, int dtype, const int* row_limit, cudaStream_t stream);
 // Half-split rotary embedding of the first n_rot_heads heads of each row of
 // src[rows, n_heads_total * hd] into dst (dst may be src; otherwise the other heads are copied);
 // position = row % T; sign = +1 forward, -1 backward.
@@ -63,10 +64,19 @@ int fmb_kl_fwd_bwd(const void* student, const void* teacher, float* row_loss, vo
 int fmb_sum_f32(const float* x, float* out, long long n, float scale, int accumulate, cudaStream_t stream);
 
 // ---- router (moe.cu)
-int fmb_router_topk(const float* logits, float* weights, int* idx, float* probs_sum, int* counts, float* z_sum,
-                    long long rows, int E, int k, cudaStream_t stream);
+int fmb_router_blocks(long long rows);
+int fmb_router_fwd(const void* logits, long long ld, int dtype, float* probs, float* weights, int* idx, float* lse,
+                   float* psum_partial, int* counts, long long rows, int E, int k, int nblocks, cudaStream_t stream);
+int fmb_router_bwd(const float* probs, const int* idx, const float* weights, const float* lse, const float* dweights,
+                   const float* aux_grad, const float* zc, void* dlogits, long long ld, int dtype, long long rows, int E,
+                   int k, cudaStream_t stream);
+int fmb_moe_plan(const int* idx, int* chunk_counts, int* region, int* meta, int* slot_of_entry, int* token_of_slot,
+                 long long entries, int E, int k, int align, int cap, int mode, cudaStream_t stream);
+int fmb_moe_tile_groups(const int* region, int* tile_group, int n_tiles, int E, cudaStream_t stream);
+int fmb_moe_combine_bwd(const void* dout, const void* ys, const int* slot_of_entry, const float* w, void* dys, float* dw,
+                        long long entries, int k, int d, cudaStream_t stream);
 int fmb_moe_gather(const void* x, const int* token_of_slot, void* out, long long slots, int d, cudaStream_t stream);
-int fmb_moe_combine(const void* ys, const int* slot_of_token, const float* w, void* out, long long tokens, int k,
+int fmb_moe_combine(const void* ys, const int* slot_of_entry, const float* w, void* out, long long tokens, int k,
                     int d, cudaStream_t stream);
 
 // ---- optimizer (optim.cu)
@@ -74,7 +84,8 @@ int fmb_moe_combine(const void* ys, const int* slot_of_token, const float* w, vo
 // kernel leaves everything untouched. shadow (bf16, may be null) receives the updated weights.
 int fmb_adamw_flat(float* p, const float* g, float* m, float* v, void* shadow, long long n, float lr, float beta1,
                    float beta2, float eps, float wd, float bc1, float bc2, const float* ctl, cudaStream_t stream);
-int fmb_sqnorm_f32(const float* x, float* out, long long n, int accumulate, cudaStream_t stream);
+// sum of squares of n floats; `partial` must hold at least 1024 floats
+int fmb_sqnorm_f32_scratch(const float* x, float* partial, float* out, long long n, int accumulate, cudaStream_t stream);
 int fmb_scale_cast(const void* src, void* dst, long long n, float scale, int src_dtype, int dst_dtype,
                    cudaStream_t stream);
 int fmb_ns_axpby(const void* x, const void* y, void* out, long long n, float a, float b, int dtype,
@@ -88,6 +99,12 @@ int fmb_attn_bwd(const void* q, const void* k, const void* v, const void* o, con
                  void* dq, void* dk, void* dv, float* delta, float* dq_acc, int B, int T, int Hq, int Hkv, int hd,
                  long long q_stride_t, long long kv_stride_t, long long o_stride_t, long long dq_stride_t,
                  long long dkv_stride_t, float scale, int causal, int delta_ready, int* status, cudaStream_t stream);
+
+// grouped products (rows partitioned into expert regions): see the comment at the definition
+int fmb_gemm_bf16_grouped(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int a_mn, int b_mn,
+                          long long lda, long long ldb, long long ldd, long long ldc, int d_f32, int c_f32, float alpha,
+                          float beta, int mode, int n_groups, const int* tile_group, const int* region,
+                          long long group_stride_b, long long group_stride_d, int* status, cudaStream_t stream);
 
 // bf16 product with a fused epilogue: epi 1 SwiGLU forward (B = stacked gate|up weight [2h, K], D = gate|up
 // [M, 2h], aux_out = activation [M, h]); 2 SwiGLU backward (accumulator = d(act) [M, h], aux_in = gate|up,

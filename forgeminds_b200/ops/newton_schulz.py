@@ -44,7 +44,7 @@ def newton_schulz_bf16(g: torch.Tensor, steps: int = 5):
             gemm(gram, gram, out=poly, c=gram, alpha=NS_C, beta=NS_B)
             gemm(poly, cur, b_mn=True, out=nxt, c=cur, alpha=1.0, beta=NS_A)
             cur, nxt = nxt, cur
-        if cur is not out[i]:
+        if cur.data_ptr() != out[i].data_ptr():
             out[i].copy_(cur)
     if flip:
         out = out.mT

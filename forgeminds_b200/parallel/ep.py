@@ -116,15 +116,20 @@ class _EPExperts(torch.autograd.Function):
         entry_of[slots] = -1
         eng.slot_sym.local.copy_(slot_of)
         # 3. dispatch + experts
-        xs = torch.zeros((slots, d), dtype=BF16, device=x.device)
+        # Dropless plans have no dead row tile inside an expert's region and nothing below touches rows past
+        # `limit`, so the buffers need no clearing. With a capacity an unused tile inside a region would feed
+        # stale values into the expert weight gradients: those (bounded) buffers are cleared.
+        alloc = torch.zeros if cap else torch.empty
+        xs = alloc((slots, d), dtype=BF16, device=x.device)
         C.ep_gather(eng.x_sym.ptrs, token_of, limit, xs, n, sg.flags.local, eng.s_pub, e_pub, sg.timeout_ms, st)
         b1, b3, b2 = bf16_of(w1), bf16_of(w3), bf16_of(w2)
-        gu = torch.zeros((slots, 2 * h), dtype=BF16, device=x.device)
+        gu = alloc((slots, 2 * h), dtype=BF16, device=x.device)
         C.gemm_grouped_rows(xs, b1, gu[:, :h], tile_group, True, False, st)
         C.gemm_grouped_rows(xs, b3, gu[:, h:], tile_group, True, False, st)
-        act = C.swiglu_fwd(gu[:, :h], gu[:, h:])
+        act = C.swiglu_fwd(gu[:, :h], gu[:, h:], limit)
         ys = eng.rows_sym.local.view(slots, d)
-        ys.zero_()
+        if cap:
+            ys.zero_()
         C.gemm_grouped_rows(act, b2, ys, tile_group, True, False, st)
         e_ys = eng.signal(eng.s_ys)
         # 4. combine: every token pulls from the owners
@@ -137,7 +142,7 @@ class _EPExperts(torch.autograd.Function):
         ctx.save_for_backward(xs, gu, ys_keep, rw, idx, slot_of, entry_of, region, tile_group, b1, b3, b2)
         ctx.params = (w1, w3, w2)
         ctx.eng = eng
-        ctx.dims = (n, d, h, k, e_local, slots, route_w.dtype)
+        ctx.dims = (n, d, h, k, e_local, slots, route_w.dtype, bool(cap))
         return out
 
     @staticmethod
@@ -149,7 +154,8 @@ class _EPExperts(torch.autograd.Function):
         eng = ctx.eng
         sg, W, rank = eng.sg, eng.world, eng.rank
         st = sg.status
-        n, d, h, k, e_local, slots, rw_dtype = ctx.dims
+        n, d, h, k, e_local, slots, rw_dtype, clear = ctx.dims
+        alloc = torch.zeros if clear else torch.empty
         limit, own = region[e_local], region[:e_local]
         # publish what the owners need: output gradient rows, routing weights, this layer's slot table
         eng.x_sym.local.view(n, d).copy_(dout)
@@ -157,10 +163,10 @@ class _EPExperts(torch.autograd.Function):
         eng.slot_sym.local.copy_(slot_of)
         eng.drw_sym.local.zero_()            # entries dropped by a capacity limit get no push: their gradient is zero
         e_g = eng.signal(eng.s_gpub)
-        dys = torch.zeros((slots, d), dtype=BF16, device=dout.device)
+        dys = alloc((slots, d), dtype=BF16, device=dout.device)
         C.ep_combine_bwd(eng.x_sym.ptrs, eng.w_sym.ptrs, eng.drw_sym.ptrs, ys, entry_of, limit, dys, n * k, k,
                          sg.flags.local, eng.s_gpub, e_g, sg.timeout_ms, st)
-        act = C.swiglu_fwd(gu[:, :h], gu[:, h:])                              # recomputed
+        act = C.swiglu_fwd(gu[:, :h], gu[:, h:], limit)                       # recomputed
         grads = {}
 
         def wgrad(name, param, a, b):
@@ -174,14 +180,15 @@ class _EPExperts(torch.autograd.Function):
                 grads[name] = g if g.dtype == param.dtype else g.to(param.dtype)
 
         wgrad("w2", w2, act, dys)
-        dact = torch.zeros((slots, h), dtype=BF16, device=dout.device)
+        dact = alloc((slots, h), dtype=BF16, device=dout.device)
         C.gemm_grouped_rows(dys, b2, dact, tile_group, False, False, st)
-        dgu = torch.zeros_like(gu)
-        C.swiglu_bwd(gu[:, :h], gu[:, h:], dact, dgu[:, :h], dgu[:, h:])
+        dgu = alloc(gu.shape, dtype=BF16, device=dout.device)
+        C.swiglu_bwd(gu[:, :h], gu[:, h:], dact, dgu[:, :h], dgu[:, h:], limit)
         wgrad("w1", w1, xs, dgu[:, :h])
         wgrad("w3", w3, xs, dgu[:, h:])
         dxs = eng.rows_sym.local.view(slots, d)
-        dxs.zero_()
+        if clear:
+            dxs.zero_()
         C.gemm_grouped_rows(dgu[:, :h], b1, dxs, tile_group, False, False, st)
         C.gemm_grouped_rows(dgu[:, h:], b3, dxs, tile_group, False, True, st)
         e_dx = eng.signal(eng.s_dxs)

@@ -130,7 +130,7 @@ class Trainer:
             groups = self._param_groups(trainable, tc)
             from .parallel.deepspeed_backend import init_deepspeed
             self.engine, self.opt = init_deepspeed(self.model, groups, cfg, ctx.world, micro_batch)
-        elif self.native and self._flat_ok(oc, cfg):
+        elif self.native and self._flat_ok(oc, cfg) and self._fits_resident(trainable, pc):
             self._setup_native(model, tc, pc, dp)
         else:
             if dp and pc.dp_shard > 1:
@@ -199,6 +199,13 @@ class Trainer:
         tc, pc = cfg.train, cfg.parallel
         return not (oc.optimizer or cfg.quant.optimizer_8bit or pc.fsdp_cpu_offload or tc.compile) \
             and cfg.quant.mode in ("none", "fp8", "int8") and pc.tp == 1 and pc.ep == 1
+
+    def _fits_resident(self, params, pc) -> bool:
+        """The native engine keeps the bf16 working weights of the whole model on every GPU. A model
+        whose weights exceed ``fsdp_resident_bytes`` and that asks for sharding goes to FSDP2 instead."""
+        if pc.dp_shard in (0, 1):
+            return True
+        return 2 * sum(p.numel() for p in params) <= int(pc.fsdp_resident_bytes)
 
     def _setup_native(self, model, tc, pc, dp: bool) -> None:
         from .parallel.flat import BucketReducer, FlatAdamW, FlatParamStore
