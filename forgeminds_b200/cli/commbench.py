@@ -5,8 +5,8 @@
 
 Every figure is the median of ``--iters`` runs timed with CUDA events on the launching stream after
 warm-up, with a NCCL barrier before each run, and the MAX over ranks. For each fused kernel the table
-gives the roofline target ``max(FLOPs / measured bf16 GEMM rate, bytes over NVLink / 770 GB/s)`` and the
-achieved fraction, next to the unfused NCCL formulation of the same step.
+gives the roofline target ``max(FLOPs / measured bf16 GEMM rate, bytes over NVLink / 770 GB/s, bytes of
+local HBM traffic / measured copy bandwidth)`` and the achieved fraction, next to the unfused NCCL formulation of the same step.
 
   rs_reduce     pull reduce-scatter of a gradient bucket (+ sum of squares)    vs  reduce_scatter_tensor
   adamw_push    sharded AdamW + bf16 store into every rank's weights           vs  fused AdamW on the shard + all_gather
@@ -74,11 +74,11 @@ def main(argv=None) -> int:
         dist.init_process_group("nccl", device_id=dev)
     C = ops.require()
     sg = SymmGroup(None, dev, timeout_ms=10000)
-    tflops, _hbm, src = _peaks()
+    tflops, hbm_gbs, src = _peaks()
     rows = []
 
-    def add(name, fused_ms, nccl_ms, flops, link_bytes, note=""):
-        target = max(flops / (tflops * 1e12), link_bytes / (NVLINK_GBS * 1e9)) * 1e3
+    def add(name, fused_ms, nccl_ms, flops, link_bytes, note="", hbm_bytes=0.0):
+        target = max(flops / (tflops * 1e12), link_bytes / (NVLINK_GBS * 1e9), hbm_bytes / (hbm_gbs * 1e9)) * 1e3
         rows.append(dict(op=name, fused_ms=round(fused_ms, 4), nccl_ms=round(nccl_ms, 4), target_ms=round(target, 4),
                          achieved=round(target / fused_ms, 3) if fused_ms > 0 else None, note=note))
 
@@ -103,7 +103,7 @@ def main(argv=None) -> int:
         out_shard.square().sum()
 
     add("rs_reduce", _time(rs_fused, a.iters, a.warmup, dev), _time(rs_nccl, a.iters, a.warmup, dev), 0.0,
-        shard * 4 * (world - 1), f"{a.bucket_mb} MB fp32 bucket, {world} ranks")
+        shard * 4 * (world - 1), f"{a.bucket_mb} MB fp32 bucket, {world} ranks", hbm_bytes=shard * 8.0)
 
     # ---------------------------------------------------------------- sharded AdamW + push
     master = torch.randn(n, device=dev)
@@ -131,7 +131,7 @@ def main(argv=None) -> int:
         dist.all_gather_into_tensor(full_bf16, p_shard.detach().to(torch.bfloat16))
 
     add("adamw_push", _time(push_fused, a.iters, a.warmup, dev), _time(push_nccl, a.iters, a.warmup, dev), 0.0,
-        shard * 2 * (world - 1), "fp32 master + moments on the shard, bf16 to every rank")
+        shard * 2 * (world - 1), "fp32 master + moments on the shard, bf16 to every rank", hbm_bytes=shard * 30.0)
 
     # ---------------------------------------------------------------- all-gather -> GEMM
     M, K = a.tokens, a.dim

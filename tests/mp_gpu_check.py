@@ -351,7 +351,7 @@ def tp_fused():
         cfg = fm.ForgeConfig()
         cfg.parallel.tp = world
         cfg.parallel.fused_comm = fused
-        cfg.train.__dict__.update(max_steps=10, grad_accum=2, lr=3e-3, warmup_steps=3, bf16=True, resume=False,
+        cfg.train.__dict__.update(max_steps=10, grad_accum=2, lr=1e-3, warmup_steps=3, bf16=True, resume=False,
                                   log_every=1000, prefetch=False, ckpt_every=0, native=None if fused else False)
         mc = fm.GPTConfig(vocab_size=512, dim=256, n_layers=2, n_heads=8, n_kv_heads=4, max_seq=128, ffn_hidden=512)
         tr = fm.Trainer(lambda ctx: fm.GPT(mc), cfg, fm.SyntheticLM(512, 128, n=512), micro_batch=4)
