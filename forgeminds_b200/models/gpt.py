@@ -89,6 +89,11 @@ def apply_rope(x, cos, sin):
     return torch.cat((a * cos - b * sin, a * sin + b * cos), dim=-1)
 
 
+def _is_quantised(linear) -> bool:
+    """True for the int8 / fp8 linear layers that ``quantize_model`` swaps in."""
+    return hasattr(linear, "mode") and hasattr(linear, "block") and isinstance(linear, nn.Linear)
+
+
 def _native_ok(x: torch.Tensor, flag: Optional[bool]) -> bool:
     """Whether this call should run on the sm_100a kernels."""
     if flag is False or not x.is_cuda:
@@ -164,6 +169,13 @@ class Attention(nn.Module):
         B, T, _ = x.shape
         hd = self.hd
         n_q, n_kv = self.wq.weight.shape[0] // hd, self.wk.weight.shape[0] // hd
+        if _is_quantised(self.wq):
+            # int8 / fp8 training: every projection is its own quantised product (8-bit tcgen05 GEMMs)
+            xn = Fn.rms_norm(x, norm.weight, norm.eps)
+            qkv = torch.cat([self.wq(xn), self.wk(xn), self.wv(xn)], dim=-1)
+            cos, sin = rope_tables(T, hd, self.theta, x.device, torch.float32)
+            qkv = Fn.rope_qkv_(qkv, cos.reshape(T, hd // 2), sin.reshape(T, hd // 2), n_q, n_kv, hd)
+            return x + self.wo(Fn.attention_qkv(qkv, n_q, n_kv, hd, True))
         qkv, x = Fn.norm_linear_multi(x, norm.weight, norm.eps, (self.wq.weight, self.wk.weight, self.wv.weight),
                                       passthrough=True)
         cos, sin = rope_tables(T, hd, self.theta, x.device, torch.float32)
@@ -184,6 +196,9 @@ class SwiGLU(nn.Module):
     def forward_native(self, x, norm):
         """``x + mlp(norm(x))``; the norm output and the activation are recomputed in the backward."""
         from ..ops import functional as Fn
+        if _is_quantised(self.w1):
+            xn = Fn.rms_norm(x, norm.weight, norm.eps)
+            return x + self.w2(Fn.swiglu(self.w1(xn), self.w3(xn)))
         if self.w1.weight.shape[0] % 128 == 0:
             return Fn.mlp_block(x, norm.weight, norm.eps, self.w1.weight, self.w3.weight, self.w2.weight)
         gu, x = Fn.norm_linear_multi(x, norm.weight, norm.eps, (self.w1.weight, self.w3.weight), passthrough=True)
@@ -214,7 +229,8 @@ class Block(nn.Module):
             self.ffn = SwiGLU(c.dim, hidden)
 
     def forward(self, x):
-        if _native_ok(x, self.native) and hasattr(self.attn, "forward_native"):
+        if _native_ok(x, self.native) and hasattr(self.attn, "forward_native") and \
+                isinstance(getattr(self.attn, "wq", None), nn.Linear):      # weight-only int8 modules keep their own path
             return self._forward_native(x)
         x = x + self.attn(self.attn_norm(x))
         return x + self.ffn(self.ffn_norm(x))

@@ -37,7 +37,12 @@ def _cached_weight(weight, mode: str, block: int, transposed: bool):
             weight._fm_qcache = cache
         except Exception:                        # noqa: BLE001 - not every tensor takes attributes
             pass
-    w = weight.detach()
+    shadow = getattr(weight, "_fm_shadow", None)
+    if shadow is not None and len(shadow) == 2:
+        # a flat store owns this parameter: its bf16 copy is complete on every rank, the fp32 master may be sharded
+        w = Fn.bf16_of(weight)
+    else:
+        w = weight.detach()
     if transposed:
         w = w.t()
     w = w.contiguous()
