@@ -59,6 +59,10 @@ def apply_tp(model, ctx: DistContext, plan=None):
     if not hits:
         raise RuntimeError("apply_tp: no module matched the tensor-parallel plan")
     model._fm_tp = "dtensor"
+    # DTensor parameters go through PyTorch operators: the kernel path of the blocks takes plain tensors only
+    for blk in model.layers.values():
+        if hasattr(blk, "native"):
+            blk.native = False
     return model
 
 

@@ -368,6 +368,40 @@ def tp_fused():
         print("OK tp_fused", flush=True)
 
 
+def _mesh_run(world, rank, label, steps=8, quant="none", optimizer="adamw", **par):
+    cfg = fm.ForgeConfig()
+    cfg.parallel.__dict__.update(par)
+    cfg.quant.mode = quant
+    cfg.train.__dict__.update(max_steps=steps, grad_accum=2, lr=2e-3, warmup_steps=2, bf16=True, resume=False,
+                              log_every=1000, prefetch=False, ckpt_every=0, optimizer=optimizer)
+    mc = fm.GPTConfig(vocab_size=512, dim=256, n_layers=4, n_heads=8, n_kv_heads=4, max_seq=128, ffn_hidden=512)
+    tr = fm.Trainer(lambda ctx: fm.GPT(mc), cfg, fm.SyntheticLM(512, 128, n=1024), micro_batch=4)
+    hist = tr.fit()
+    tr.close()
+    losses = [h["loss"] for h in hist]
+    assert all(l == l for l in losses), (label, losses)
+    assert losses[-1] < 0.9 * losses[0], (label, losses)
+    if rank == 0:
+        print(f"  {label}: engine={'native' if tr.store is not None else 'library'} "
+              f"loss {losses[0]:.3f} -> {losses[-1]:.3f}", flush=True)
+
+
+def mesh_smoke():
+    """Every mesh / feature combination that the box has GPUs for trains a small model for a few steps."""
+    rank, world, dev = _init()
+    _mesh_run(world, rank, f"dp_shard={world}", dp_shard=world)
+    _mesh_run(world, rank, f"dp_replicate={world}", dp_replicate=world)
+    _mesh_run(world, rank, f"dp_shard={world} + fp8", quant="fp8", dp_shard=world)
+    _mesh_run(world, rank, f"dp_shard={world} + int8 + muon", quant="int8", optimizer="muon", dp_shard=world)
+    _mesh_run(world, rank, f"pp=2 x dp_shard={world // 2}", pp=2, dp_shard=world // 2, pp_microbatches=2)
+    _mesh_run(world, rank, f"tp=2 x dp_shard={world // 2}", tp=2, dp_shard=world // 2)
+    if world >= 4:
+        _mesh_run(world, rank, "dp_replicate=2 x dp_shard=2 (HSDP)", dp_replicate=2, dp_shard=world // 2)
+        _mesh_run(world, rank, f"tp=2 x pp=2 x dp_shard={world // 4}", tp=2, pp=2, dp_shard=world // 4, pp_microbatches=2)
+    if rank == 0:
+        print("OK mesh_smoke", flush=True)
+
+
 if __name__ == "__main__":
     name = sys.argv[1]
     globals()[name]()

@@ -59,6 +59,11 @@ def test_missing_rank_is_reported_not_waited_for_forever():
     _run("peer_failure", RANKS, 29617)
 
 
+@needs2
+def test_mesh_and_feature_combinations_train():
+    _run("mesh_smoke", RANKS, 29618, timeout=900)
+
+
 def test_peer_step_single_rank(cuda_status):
     """World of one: the same kernels, peer tables of length one."""
     import forgeminds_b200 as fm
