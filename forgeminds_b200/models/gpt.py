@@ -229,6 +229,10 @@ class Block(nn.Module):
             self.ffn = SwiGLU(c.dim, hidden)
 
     def forward(self, x):
+        tp_state = getattr(self, "_fm_tp", None)
+        if tp_state is not None:                 # sequence-parallel block on a row shard [Ms, d] (parallel/tp.py)
+            from ..parallel import tp as fused_tp
+            return fused_tp.block_forward(self, x, tp_state)
         if _native_ok(x, self.native) and hasattr(self.attn, "forward_native") and \
                 isinstance(getattr(self.attn, "wq", None), nn.Linear):      # weight-only int8 modules keep their own path
             return self._forward_native(x)

@@ -96,6 +96,14 @@ class TPState:
         return out
 
 
+def _plain(t, what: str):
+    """The kernels take raw device pointers: a DTensor / sharded parameter must never reach them."""
+    if hasattr(t, "to_local"):
+        raise TypeError(f"fused tensor parallelism got a DTensor for {what}; it needs the full local tensor "
+                        "(was the block called directly instead of through its data-parallel wrapper?)")
+    return t
+
+
 def _main_grad_or_new(param, shape, device):
     main = getattr(param, "_fm_main_grad", None)
     if main is not None:
@@ -109,7 +117,7 @@ class _GatherLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_shard, weight, tp: TPState):
         from ..ops.functional import bf16_of
-        w = bf16_of(weight)
+        w = bf16_of(_plain(weight, "a column-parallel weight"))
         ms, k = x_shard.shape
         act, _, _, ready = tp.buffers(ms, k)
         epoch = tp.publish(act, tp.slot_act, x_shard)
@@ -152,7 +160,7 @@ class _LinearScatter(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h, weight, residual, tp: TPState):
         from ..ops.functional import bf16_of
-        w = bf16_of(weight)
+        w = bf16_of(_plain(weight, "a row-parallel weight"))
         m, n = h.shape[0], w.shape[0]
         ms = m // tp.world
         _, _, staging, _ = tp.buffers(ms, n)
@@ -326,6 +334,6 @@ def stack_forward(model, x):
     xs = _TakeShard.apply(x.reshape(B * T, d).to(BF16), state.rank, state.world)
     for blk in model.layers.values():
         blk._fm_bt = (B, T)
-        xs = block_forward(blk, xs, state)
+        xs = blk(xs)          # through __call__: data-parallel wrappers (FSDP2 / DDP hooks) must see the call
     full = _GatherRows.apply(xs, state.group, state.rank, state.world)
     return full.view(B, T, d)
