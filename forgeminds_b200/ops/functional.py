@@ -44,6 +44,9 @@ def bf16_of(p: torch.Tensor) -> torch.Tensor:
     A cache entry is ``(shadow, version)`` when a flat store owns the shadow and keeps it current
     itself, or ``(shadow, version, epoch)`` when it was made here; the latter is refreshed when the
     parameter's version changed or any optimizer has stepped since."""
+    if hasattr(p, "to_local"):
+        raise TypeError("the sm_100a kernels take plain tensors; got a DTensor parameter (sharded by FSDP2 / DTensor "
+                        "tensor parallelism). Call the module through its wrapper or switch the block to native=False")
     if p.dtype == BF16:
         return p.detach()
     cached = getattr(p, "_fm_shadow", None)
