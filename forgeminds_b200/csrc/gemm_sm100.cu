@@ -10,6 +10,8 @@
 // the forward (K,K), input-gradient (K,MN) and weight-gradient (MN,MN) products of a linear layer
 // without a transpose pass. Split-K (fp32 atomic accumulation) fills the machine when the output
 // has fewer tiles than SMs, which is the usual case for weight gradients.
+#include <cstdlib>
+
 #include "ptx_sm100.cuh"
 #include "peer.cuh"
 #include "launch.cuh"
@@ -144,10 +146,10 @@ constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_THREADS = 192;
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int CTAS = 1>
 struct GemmSmem {
   static constexpr uint32_t A_BYTES = GEMM_BM * GEMM_BK * 2;
-  static constexpr uint32_t B_BYTES = BN * GEMM_BK * 2;
+  static constexpr uint32_t B_BYTES = (BN / CTAS) * GEMM_BK * 2;   // a CTA pair splits the B tile
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr uint32_t BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr uint32_t TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;  // + alignment slack
@@ -214,11 +216,24 @@ __device__ __forceinline__ void gather_rows(const GemmParams& p, int tid) {
   }
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool PEER>
+// CTAS = 2: the CTAs 2i and 2i+1 of the grid form a cluster and work on one 256 x BN tile together. Each
+// loads its own 128 rows of A and its own half (BN / 2 columns) of B; one thread of the even CTA issues
+// cta_group::2 MMAs that read both CTAs' shared memory and write 128 accumulator rows into each CTA's
+// TMEM; each CTA's epilogue warps store their own 128 rows. Per SM the B traffic from L2 is halved. All
+// pipeline barriers that the MMA thread waits on live in the even CTA: loads of both CTAs count their
+// bytes there and the epilogue warps of both arrive there; the MMA thread's commits arrive in both CTAs.
+// p.tiles_m then counts 256-row tiles.
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool PEER, int CTAS = 1>
 __global__ void __launch_bounds__(GEMM_THREADS + (PEER ? GATHER_THREADS : 0), 1)
 gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant__ MapSet<PEER> tmB, GemmParams p) {
-  using L = GemmSmem<BN, STAGES>;
+  static_assert(CTAS == 1 || (CTAS == 2 && !PEER && BN >= 128), "CTA pairs: plain products with BN >= 128");
+  using L = GemmSmem<BN, STAGES, CTAS>;
   constexpr int BM = GEMM_BM, BK = GEMM_BK;
+  constexpr int BN_CTA = BN / CTAS;                  // columns of B that this CTA loads
+  const uint32_t cta_rank = CTAS == 2 ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0u;
+  const int unit = CTAS == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int n_units = CTAS == 2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
@@ -240,7 +255,7 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(tfull_bar(s), 1);
-      mbar_init(tempty_bar(s), 4);
+      mbar_init(tempty_bar(s), 4 * CTAS);
     }
     ab->flag = 0;
     mbar_fence_init();
@@ -248,11 +263,21 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
     tma_prefetch_desc(&tmB.m[0]);
   }
   if (warp == 1) {
-    tmem_alloc<2 * BN>(smem_u32(tmem_slot));
-    tmem_relinquish();
+    if constexpr (CTAS == 2) {
+      tmem_alloc_pair<2 * BN>(smem_u32(tmem_slot));
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc<2 * BN>(smem_u32(tmem_slot));
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (CTAS == 2) {
+    __syncwarp();
+    cluster_sync_all();              // the other CTA's barriers are initialised before anything signals them
+  } else {
+    __syncthreads();
+  }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();                      // everything above touched only this CTA's shared memory and TMEM
@@ -267,15 +292,16 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
       uint32_t armed = 0, armed_parity = 0;
       int ready_blk = -1;                       // last gathered 128-row block known to be complete
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int tile = unit; ok && tile < total_tiles; tile += n_units) {
         const TileInfo ti = decode_tile(p, tile);
         if (!ti.valid) continue;
-        const int m_blk = ti.m_blk, n_blk = ti.n_blk, k0 = ti.k0, k1 = ti.k1;
+        const int m_blk = ti.m_blk * CTAS + static_cast<int>(cta_rank), n_blk = ti.n_blk, k0 = ti.k0, k1 = ti.k1;
+        const int n_off = n_blk * BN + static_cast<int>(cta_rank) * BN_CTA;     // first B column of this CTA
         for (int kq = k0; kq < k1; ++kq) {
           int kb = kq;
           if (PEER && p.rot_k) { kb = kq + p.rot_k; if (kb >= k1) kb -= (k1 - k0); }
           const int a_y = A_MN ? kb * BK : m_blk * BM;
-          const int b_y = B_MN ? kb * BK : n_blk * BN;
+          const int b_y = B_MN ? kb * BK : n_off;
           if constexpr (PEER) {
             if (p.gather) {
               const int blk = (p.gather == 1 ? a_y : b_y) >> 7;
@@ -294,11 +320,32 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
           if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, ab, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t sA = smem_base + stage * L::STAGE_BYTES;
           const uint32_t sB = sA + L::A_BYTES;
-          mbar_expect_tx(full_bar(stage), L::STAGE_BYTES);
-          armed |= 1u << stage;
-          armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+          if (leader) {                          // the even CTA's barrier counts the bytes of both CTAs
+            mbar_expect_tx(full_bar(stage), CTAS * L::STAGE_BYTES);
+            armed |= 1u << stage;
+            armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+          }
           const CUtensorMap* ma = &tmA.m[0];
           const CUtensorMap* mb = &tmB.m[0];
+          if constexpr (CTAS == 2) {
+            const uint32_t bar = mapa_shared(full_bar(stage), 0u);
+            if constexpr (!A_MN) {
+              tma_load_2d_pair(sA, ma, bar, kb * BK, a_y);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j)
+                tma_load_2d_pair(sA + j * (BK * 128), ma, bar, m_blk * BM + j * 64, a_y);
+            }
+            if constexpr (!B_MN) {
+              tma_load_3d_pair(sB, mb, bar, kb * BK, b_y, ti.zb);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN_CTA / 64; ++j)
+                tma_load_3d_pair(sB + j * (BK * 128), mb, bar, n_off + j * 64, b_y, ti.zb);
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           if constexpr (!A_MN) {
             tma_load_2d(sA, ma, full_bar(stage), kb * BK, a_y);
           } else {
@@ -332,14 +379,14 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
-    if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc(BM, BN, 1, 1, 1, A_MN, B_MN);
+    if ((CTAS == 1 || leader) && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc(BM * CTAS, BN, 1, 1, 1, A_MN, B_MN);
       constexpr uint32_t A_KSTEP = A_MN ? 16u * 128u : 32u;   // bytes per 16-wide K slice
       constexpr uint32_t B_KSTEP = B_MN ? 16u * 128u : 32u;
       constexpr uint32_t MN_LBO = BK * 128u;                  // next 64-wide block of an MN-major tile
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int tile = unit; ok && tile < total_tiles; tile += n_units) {
         const TileInfo ti = decode_tile(p, tile);
         if (!ti.valid) continue;
         const int k0 = ti.k0, k1 = ti.k1;
@@ -355,13 +402,16 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t da = umma_smem_desc_sw128(sA + k * A_KSTEP, A_MN ? MN_LBO : 16u, 1024u);
             const uint64_t db = umma_smem_desc_sw128(sB + k * B_KSTEP, B_MN ? MN_LBO : 16u, 1024u);
-            umma_f16_ss(d_tmem, da, db, idesc, (kb > k0 || k > 0) ? 1u : 0u);
+            if constexpr (CTAS == 2) umma_f16_ss_pair(d_tmem, da, db, idesc, (kb > k0 || k > 0) ? 1u : 0u);
+            else                     umma_f16_ss(d_tmem, da, db, idesc, (kb > k0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(empty_bar(stage));
+          if constexpr (CTAS == 2) umma_commit_pair(empty_bar(stage), 3);   // frees the stage in both CTAs
+          else                     umma_commit(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit(tfull_bar(acc));
+        if constexpr (CTAS == 2) umma_commit_pair(tfull_bar(acc), 3);
+        else                     umma_commit(tfull_bar(acc));
         acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -377,10 +427,13 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
     uint32_t acc = 0, acc_phase = 0;
     const float alpha = p.alpha_ptr != nullptr ? p.alpha * __ldg(p.alpha_ptr) : p.alpha;
     const float beta = p.beta;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    const long long d_es = p.d_f32 ? 4 : 2;
+    const bool wide_d = (reinterpret_cast<uintptr_t>(p.D) & 31) == 0 && (p.ldd * d_es) % 32 == 0 &&
+                        (p.group_stride_d * d_es) % 32 == 0;          // 32-byte stores stay aligned
+    for (int tile = unit; tile < total_tiles; tile += n_units) {
       const TileInfo ti = decode_tile(p, tile);
       if (!ti.valid) continue;
-      const int m_blk = ti.m_blk, n_blk = ti.n_blk;
+      const int m_blk = ti.m_blk * CTAS + static_cast<int>(cta_rank), n_blk = ti.n_blk;
       if (!mbar_wait_bounded(tfull_bar(acc), acc_phase, ab, p.status, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const int row = m_blk * BM + quarter * 32 + lane;
@@ -449,14 +502,12 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
         }
       } else {
       float seg_dot = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      const int cols_left = p.N - n_blk * BN;
+      const int n_chunks = cols_left >= BN ? BN / 32 : (cols_left + 31) / 32;     // uniform across the warp
+      // One 32-column chunk of this thread's row: scale, add C, store (and the row dots of epi 3).
+      auto finish_chunk = [&](int c, const uint32_t (&r)[32]) {
+        if (!row_ok) return;
         const int col0 = n_blk * BN + c * 32;
-        if (col0 >= p.N) break;                   // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c * 32, r);
-        tmem_wait_ld();
-        if (!row_ok) continue;
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
@@ -526,6 +577,12 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
             } else {
               _Pragma("unroll") for (int i = 0; i < 32; ++i) if (col0 + i < p.N) atomicAdd(dp + i, v[i]);
             }
+          } else if (full && wide_d) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              st_global_v8(dp + 8 * i, __float_as_uint(v[8 * i]), __float_as_uint(v[8 * i + 1]), __float_as_uint(v[8 * i + 2]),
+                           __float_as_uint(v[8 * i + 3]), __float_as_uint(v[8 * i + 4]), __float_as_uint(v[8 * i + 5]),
+                           __float_as_uint(v[8 * i + 6]), __float_as_uint(v[8 * i + 7]));
           } else if (full) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
@@ -535,14 +592,23 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
           }
         } else {
           __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + ti.d_off + static_cast<long long>(row) * p.ldd + col0;
+          bool wide = wide_d;
           if constexpr (PEER) {
             if (p.d_rows_per_rank > 0) {          // slice `rank` of the staging buffer of the rank that owns this row
               const int owner = row / p.d_rows_per_rank;
               dp = reinterpret_cast<__nv_bfloat16*>(p.d_peer[owner]) +
                    (static_cast<long long>(p.rank) * p.d_rows_per_rank + (row - owner * p.d_rows_per_rank)) * p.ldd + col0;
+              wide = false;
             }
           }
-          if (full) {
+          if (full && wide) {                     // one 32-byte sector per store
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+              st_global_v8(dp + 16 * i, pack_bf16(v[16 * i + 0], v[16 * i + 1]), pack_bf16(v[16 * i + 2], v[16 * i + 3]),
+                           pack_bf16(v[16 * i + 4], v[16 * i + 5]), pack_bf16(v[16 * i + 6], v[16 * i + 7]),
+                           pack_bf16(v[16 * i + 8], v[16 * i + 9]), pack_bf16(v[16 * i + 10], v[16 * i + 11]),
+                           pack_bf16(v[16 * i + 12], v[16 * i + 13]), pack_bf16(v[16 * i + 14], v[16 * i + 15]));
+          } else if (full) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 o;
@@ -556,36 +622,81 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
             _Pragma("unroll") for (int i = 0; i < 32; ++i) if (col0 + i < p.N) dp[i] = __float2bfloat16(v[i]);
           }
         }
+      };
+      // The accumulator is read two chunks ahead of the stores; the MMA warp gets it back as soon as the
+      // last chunk is in registers.
+      auto release_acc = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CTAS == 2) mbar_arrive_relaxed_cluster(mapa_shared(tempty_bar(acc), 0u));
+          else                     mbar_arrive_relaxed(tempty_bar(acc));
+        }
+      };
+      uint32_t ra[32], rb[32];
+      if (n_chunks > 0) tmem_ld_32x32(t_row, ra);
+#pragma unroll 1
+      for (int c = 0; c < n_chunks; c += 2) {
+        tmem_wait_ld();
+        if (c + 1 < n_chunks) tmem_ld_32x32(t_row + (c + 1) * 32, rb);
+        else release_acc();
+        finish_chunk(c, ra);
+        if (c + 1 < n_chunks) {
+          tmem_wait_ld();
+          if (c + 2 < n_chunks) tmem_ld_32x32(t_row + (c + 2) * 32, ra);
+          else release_acc();
+          finish_chunk(c + 1, rb);
+        }
       }
+      if (n_chunks <= 0) release_acc();
+      acc ^= 1u;
+      if (acc == 0) acc_phase ^= 1u;
+      continue;
       }   // generic epilogue
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if constexpr (CTAS == 2) mbar_arrive_cluster(mapa_shared(tempty_bar(acc), 0u));
+        else                     mbar_arrive(tempty_bar(acc));
+      }
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
   }
 
   tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc<2 * BN>(tmem_base);
+  if constexpr (CTAS == 2) {
+    // Neither CTA leaves (or frees TMEM) while the other may still read its shared memory, write its
+    // TMEM or signal its barriers: every role of both CTAs has left its loop when this barrier opens.
+    __syncwarp();
+    cluster_sync_all();
+    if (warp == 1) {
+      tc_fence_after();
+      tmem_dealloc_pair<2 * BN>(tmem_base);
+    }
+  } else {
+    __syncthreads();
+    if (warp == 1) {
+      tc_fence_after();
+      tmem_dealloc<2 * BN>(tmem_base);
+    }
   }
 }
 
 // ------------------------------------------------------------------------------------ host side
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool PEER>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool PEER, int CTAS = 1>
 static cudaError_t launch_cfg(const MapSet<PEER>& ta, const MapSet<PEER>& tb, const GemmParams& p, int grid,
                               cudaStream_t stream) {
-  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, PEER>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, PEER, CTAS>;
   static bool attr_set = false;
-  constexpr int smem = GemmSmem<BN, STAGES>::TOTAL;
+  constexpr int smem = GemmSmem<BN, STAGES, CTAS>::TOTAL;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
+  if constexpr (CTAS == 2)
+    return launch_pdl_cluster(kern, dim3(grid), dim3(GEMM_THREADS), smem, 2, stream, ta, tb, p);
   return launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS + (PEER ? GATHER_THREADS : 0)), smem, stream, ta, tb, p);
 }
 
@@ -670,29 +781,37 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
     return -2;   // TMA needs 16-byte aligned bases and pitches; the vector epilogue needs an aligned D
   if (C != nullptr && ((reinterpret_cast<uintptr_t>(C) & 15) || (ldc % (c_f32 ? 4 : 8)))) return -2;
   const int sms = sm_count();
-  const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
   const int kblocks = (K + GEMM_BK - 1) / GEMM_BK;
   const bool can_split = allow_split && d_f32 && (C == nullptr || C == D);
+  // CTA pairs (256-row tiles over two SMs) serve plain products; FMB_GEMM_PAIR=0 turns them off.
+  static const bool pair_env = [] { const char* v = getenv("FMB_GEMM_PAIR"); return v == nullptr || v[0] != '0'; }();
+  const bool pair_ok = pair_env && ps == nullptr && gs.mode == 0 && (es == nullptr || es->epi != 1) && sms % 2 == 0;
 
-  // Pick the N tile and the split count that fill the machine best.
-  int best_bn = 256, best_split = 1;
+  // Pick the N tile, the split count and the CTAs per tile that fill the machine best.
+  int best_bn = 256, best_split = 1, best_ctas = 1;
   double best_score = -1.0;
-  for (int bn : {256, 128, 64}) {
-    if (force_bn && bn != force_bn) continue;
-    if (bn == 64 && (gs.mode != 0 || ps != nullptr)) continue;   // narrow tiles serve small plain products only
-    const int tn = (N + bn - 1) / bn;
-    const long long tiles = static_cast<long long>(tiles_m) * tn;
-    const int max_split = can_split ? 8 : 1;
-    for (int s = 1; s <= max_split; ++s) {
-      if (s > 1 && (kblocks / s) < 8) break;            // keep each split's K loop long enough
-      double score = wave_eff(tiles * s, sms);
-      score *= (bn == 256 ? 1.0 : bn == 128 ? 0.93 : 0.80);   // narrower tiles re-read A more often
-      score *= 1.0 - 0.015 * (s - 1);                   // atomics and extra epilogues are not free
-      const double pad = static_cast<double>(N) / (static_cast<double>(tn) * bn);
-      score *= pad;
-      if (score > best_score) { best_score = score; best_bn = bn; best_split = s; }
+  for (int ctas : {2, 1}) {
+    if (ctas == 2 && !pair_ok) continue;
+    const int tm = (M + GEMM_BM * ctas - 1) / (GEMM_BM * ctas);
+    const double pad_m = static_cast<double>(M) / (static_cast<double>(tm) * GEMM_BM * ctas);
+    for (int bn : {256, 128, 64}) {
+      if (force_bn && bn != force_bn) continue;
+      if (bn == 64 && (gs.mode != 0 || ps != nullptr || ctas == 2)) continue;   // narrow tiles: small plain products only
+      const int tn = (N + bn - 1) / bn;
+      const long long tiles = static_cast<long long>(tm) * tn;
+      const int max_split = can_split ? 8 : 1;
+      for (int s = 1; s <= max_split; ++s) {
+        if (s > 1 && (kblocks / s) < 8) break;            // keep each split's K loop long enough
+        double score = wave_eff(tiles * s, sms / ctas);
+        score *= (bn == 256 ? 1.0 : bn == 128 ? 0.93 : 0.80);   // narrower tiles re-read A more often
+        score *= 1.0 - 0.015 * (s - 1);                   // atomics and extra epilogues are not free
+        score *= static_cast<double>(N) / (static_cast<double>(tn) * bn);
+        score *= pad_m * (ctas == 2 ? 1.12 : 1.0);        // a pair reads half the B tile per SM
+        if (score > best_score) { best_score = score; best_bn = bn; best_split = s; best_ctas = ctas; }
+      }
     }
   }
+  const int tiles_m = (M + GEMM_BM * best_ctas - 1) / (GEMM_BM * best_ctas);
   int kbps = (kblocks + best_split - 1) / best_split;
   int splits = (kblocks + kbps - 1) / kbps;
 
@@ -778,7 +897,7 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
                                           : static_cast<uint64_t>(b_mn ? K : N) * static_cast<uint64_t>(ldb);
     uint64_t dims[3], strides[3];
     uint32_t box[3];
-    if (!b_mn) { dims[0] = K; dims[1] = N; box[0] = GEMM_BK; box[1] = (p.epi == 1) ? 128 : best_bn; }
+    if (!b_mn) { dims[0] = K; dims[1] = N; box[0] = GEMM_BK; box[1] = (p.epi == 1) ? 128 : best_bn / best_ctas; }
     else       { dims[0] = N; dims[1] = K; box[0] = 64; box[1] = GEMM_BK; }
     dims[2] = nb; box[2] = 1;
     strides[0] = 2; strides[1] = static_cast<uint64_t>(ldb) * 2; strides[2] = gstride * 2;
@@ -787,9 +906,21 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
   if (!ok) return -5;
 
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * (gs.mode == 2 ? gs.n_groups : p.splits);
-  const int grid = static_cast<int>(total < sms ? total : sms);
+  const int units = sms / best_ctas;
+  const int grid = best_ctas * static_cast<int>(total < units ? total : units);
   cudaError_t e;
-  if (ps != nullptr) {
+  if (best_ctas == 2) {
+    MapSet<false> sa, sb;
+    sa.m[0] = ta.m[0];
+    sb.m[0] = tb.m[0];
+#define FMB_DISPATCH(BN, ST)                                                                         \
+  if (a_mn && b_mn)       e = launch_cfg<BN, ST, true, true, false, 2>(sa, sb, p, grid, stream);      \
+  else if (a_mn)          e = launch_cfg<BN, ST, true, false, false, 2>(sa, sb, p, grid, stream);     \
+  else if (b_mn)          e = launch_cfg<BN, ST, false, true, false, 2>(sa, sb, p, grid, stream);     \
+  else                    e = launch_cfg<BN, ST, false, false, false, 2>(sa, sb, p, grid, stream);
+    if (best_bn == 256) { FMB_DISPATCH(256, 6) } else { FMB_DISPATCH(128, 8) }
+#undef FMB_DISPATCH
+  } else if (ps != nullptr) {
 #define FMB_DISPATCH(BN, ST)                                                                         \
   if (a_mn && b_mn)       e = launch_cfg<BN, ST, true, true, true>(ta, tb, p, grid, stream);          \
   else if (a_mn)          e = launch_cfg<BN, ST, true, false, true>(ta, tb, p, grid, stream);         \

@@ -31,4 +31,25 @@ inline cudaError_t launch_pdl(void (*kernel)(P...), dim3 grid, dim3 block, size_
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(std::forward<A>(args))...);
 }
 
+// The same with thread-block clusters of `cluster_x` CTAs along x (the grid must be a multiple of it).
+template <typename... P, typename... A>
+inline cudaError_t launch_pdl_cluster(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, int cluster_x,
+                                      cudaStream_t stream, A&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = static_cast<unsigned>(cluster_x);
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(std::forward<A>(args))...);
+}
+
 }  // namespace fmb
