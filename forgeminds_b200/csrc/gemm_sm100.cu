@@ -11,6 +11,7 @@
 // without a transpose pass. Split-K (fp32 atomic accumulation) fills the machine when the output
 // has fewer tiles than SMs, which is the usual case for weight gradients.
 #include <cstdlib>
+#include <cstring>
 
 #include "ptx_sm100.cuh"
 #include "peer.cuh"
@@ -83,6 +84,10 @@ struct GemmParams {
   //      (aux_in has the layout of D). With epi_h = T > 0 the rows are (batch, t) pairs and the result is
   //      stored as [batch, group, t].
   int epi, epi_h, seg;
+  // Output through TMA (plain fp32 products): 1 = D += alpha * product as 32 x 32 reduce-add boxes staged in
+  // shared memory (replaces both "C == D, beta == 1" and the split-K atomics), 2 = the same as plain stores.
+  int d_tma;
+  int n_fast;               // tile order: column tiles vary fastest (default: row tiles)
   const void* aux_in;
   long long ld_aux_in;
   void* aux_out;
@@ -128,6 +133,9 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
       t.m_blk = (p.rot_m + own + r % rest) % p.tiles_m;
       t.n_blk = r / rest;
     }
+  } else if (p.n_fast) {              // consecutive CTAs share a row tile of A
+    t.m_blk = mn / p.tiles_n;
+    t.n_blk = mn - t.m_blk * p.tiles_n;
   } else {
     t.m_blk = mn % p.tiles_m;
     if (p.rot_m) t.m_blk = (t.m_blk + p.rot_m) % p.tiles_m;
@@ -151,7 +159,9 @@ struct GemmSmem {
   static constexpr uint32_t A_BYTES = GEMM_BM * GEMM_BK * 2;
   static constexpr uint32_t B_BYTES = (BN / CTAS) * GEMM_BK * 2;   // a CTA pair splits the B tile
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr uint32_t BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr uint32_t STG_OFFSET = STAGES * STAGE_BYTES;          // output staging: 4 warps x 2 boxes of 4 KB
+  static constexpr uint32_t STG_BYTES = 4 * 2 * 4096;
+  static constexpr uint32_t BAR_OFFSET = STG_OFFSET + STG_BYTES;
   static constexpr uint32_t TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;  // + alignment slack
 };
 
@@ -225,7 +235,8 @@ __device__ __forceinline__ void gather_rows(const GemmParams& p, int tid) {
 // p.tiles_m then counts 256-row tiles.
 template <int BN, int STAGES, bool A_MN, bool B_MN, bool PEER, int CTAS = 1>
 __global__ void __launch_bounds__(GEMM_THREADS + (PEER ? GATHER_THREADS : 0), 1)
-gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant__ MapSet<PEER> tmB, GemmParams p) {
+gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant__ MapSet<PEER> tmB,
+                 const __grid_constant__ CUtensorMap tmD, GemmParams p) {
   static_assert(CTAS == 1 || (CTAS == 2 && !PEER && BN >= 128), "CTA pairs: plain products with BN >= 128");
   using L = GemmSmem<BN, STAGES, CTAS>;
   constexpr int BM = GEMM_BM, BK = GEMM_BK;
@@ -261,6 +272,7 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
     mbar_fence_init();
     tma_prefetch_desc(&tmA.m[0]);
     tma_prefetch_desc(&tmB.m[0]);
+    if (p.d_tma) tma_prefetch_desc(&tmD);
   }
   if (warp == 1) {
     if constexpr (CTAS == 2) {
@@ -427,6 +439,8 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
     uint32_t acc = 0, acc_phase = 0;
     const float alpha = p.alpha_ptr != nullptr ? p.alpha * __ldg(p.alpha_ptr) : p.alpha;
     const float beta = p.beta;
+    const uint32_t stg_base = smem_base + L::STG_OFFSET + static_cast<uint32_t>(quarter) * 8192u;
+    uint32_t stg_i = 0;                           // boxes issued so far by this warp (selects the staging buffer)
     const long long d_es = p.d_f32 ? 4 : 2;
     const bool wide_d = (reinterpret_cast<uintptr_t>(p.D) & 31) == 0 && (p.ldd * d_es) % 32 == 0 &&
                         (p.group_stride_d * d_es) % 32 == 0;          // 32-byte stores stay aligned
@@ -506,8 +520,30 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
       const int n_chunks = cols_left >= BN ? BN / 32 : (cols_left + 31) / 32;     // uniform across the warp
       // One 32-column chunk of this thread's row: scale, add C, store (and the row dots of epi 3).
       auto finish_chunk = [&](int c, const uint32_t (&r)[32]) {
-        if (!row_ok) return;
         const int col0 = n_blk * BN + c * 32;
+        if (p.d_tma) {                            // uniform: the whole warp stages its 32 x 32 box, one lane sends it
+          const int row0 = m_blk * BM + quarter * 32;
+          if (row0 >= p.M) return;
+          const uint32_t buf = stg_base + ((stg_i & 1u) << 12);
+          ++stg_i;
+          if (lane == 0) tma_store_wait_read<1>();       // the box sent from this buffer two boxes ago has been read
+          __syncwarp();
+          const uint32_t row_addr = buf + static_cast<uint32_t>(lane) * 128u;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)                    // 128-byte swizzle: 16-byte chunk j of row r sits at j ^ (r % 8)
+            st_shared_v4(row_addr + (static_cast<uint32_t>(j ^ (lane & 7)) << 4),
+                         __float_as_uint(__uint_as_float(r[4 * j]) * alpha), __float_as_uint(__uint_as_float(r[4 * j + 1]) * alpha),
+                         __float_as_uint(__uint_as_float(r[4 * j + 2]) * alpha), __float_as_uint(__uint_as_float(r[4 * j + 3]) * alpha));
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (p.d_tma == 1) tma_reduce_add_2d(&tmD, buf, col0, row0);
+            else              tma_store_2d(&tmD, buf, col0, row0);
+            tma_store_commit();
+          }
+          return;
+        }
+        if (!row_ok) return;
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
@@ -662,6 +698,7 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (p.d_tma && lane == 0) tma_store_wait_all<0>();   // every box has been written before this CTA leaves
   }
 
   tc_fence_before();
@@ -685,8 +722,8 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
 
 // ------------------------------------------------------------------------------------ host side
 template <int BN, int STAGES, bool A_MN, bool B_MN, bool PEER, int CTAS = 1>
-static cudaError_t launch_cfg(const MapSet<PEER>& ta, const MapSet<PEER>& tb, const GemmParams& p, int grid,
-                              cudaStream_t stream) {
+static cudaError_t launch_cfg(const MapSet<PEER>& ta, const MapSet<PEER>& tb, const CUtensorMap& td,
+                              const GemmParams& p, int grid, cudaStream_t stream) {
   auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, PEER, CTAS>;
   static bool attr_set = false;
   constexpr int smem = GemmSmem<BN, STAGES, CTAS>::TOTAL;
@@ -696,8 +733,8 @@ static cudaError_t launch_cfg(const MapSet<PEER>& ta, const MapSet<PEER>& tb, co
     attr_set = true;
   }
   if constexpr (CTAS == 2)
-    return launch_pdl_cluster(kern, dim3(grid), dim3(GEMM_THREADS), smem, 2, stream, ta, tb, p);
-  return launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS + (PEER ? GATHER_THREADS : 0)), smem, stream, ta, tb, p);
+    return launch_pdl_cluster(kern, dim3(grid), dim3(GEMM_THREADS), smem, 2, stream, ta, tb, td, p);
+  return launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS + (PEER ? GATHER_THREADS : 0)), smem, stream, ta, tb, td, p);
 }
 
 static double wave_eff(long long work, int sms) {
@@ -885,6 +922,32 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
     else if (C == nullptr) { if (cudaMemsetAsync(D, 0, sizeof(float) * static_cast<size_t>(M) * ldd, stream) != cudaSuccess) return -3; }
     else return -4;
   }
+  // Tile order. CTAs that run at the same time should share operand tiles, and an operand larger than the
+  // L2 should be streamed from memory once: estimate the traffic of both orders and take the smaller.
+  p.n_fast = 0;
+  if (gs.mode == 0 && ps == nullptr) {
+    const double l2_budget = 64.0 * (1 << 20);
+    const double a_bytes = 2.0 * M * K, b_bytes = 2.0 * N * K;
+    const int units_c = sms / best_ctas;
+    const int tm_c = p.tiles_m, tn_c = p.tiles_n;
+    auto passes = [&](int tiles_fast, int tiles_slow) {      // how often the operand of the fast dimension is streamed
+      const int slow_per_wave = units_c / tiles_fast > 1 ? units_c / tiles_fast : 1;
+      return (tiles_slow + slow_per_wave - 1) / slow_per_wave;
+    };
+    const double cost_m = (a_bytes > l2_budget ? a_bytes * passes(tm_c, tn_c) : a_bytes) + b_bytes;
+    const double cost_n = (b_bytes > l2_budget ? b_bytes * passes(tn_c, tm_c) : b_bytes) + a_bytes;
+    if (cost_n < 0.9 * cost_m) p.n_fast = 1;
+  }
+  // Plain fp32 outputs leave through TMA boxes (whole 128-byte lines, no per-thread scattered stores).
+  static const bool dtma_env = [] { const char* v = getenv("FMB_GEMM_DTMA"); return v == nullptr || v[0] != '0'; }();
+  p.d_tma = 0;
+  CUtensorMap td;
+  memset(&td, 0, sizeof(td));
+  if (dtma_env && d_f32 && gs.mode == 0 && ps == nullptr && p.epi == 0) {
+    if (splits > 1 || (C == D && beta == 1.f)) { p.d_tma = 1; p.C = nullptr; p.atomic = 0; }
+    else if (C == nullptr || beta == 0.f) p.d_tma = 2;
+    if (p.d_tma && !make_tmap_2d(&td, D, M, N, ldd, 32, 32, 4, TmapSwizzle::B128)) return -5;
+  }
 
   MapSet<true> ta, tb;
   bool ok = true;
@@ -914,18 +977,18 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
     sa.m[0] = ta.m[0];
     sb.m[0] = tb.m[0];
 #define FMB_DISPATCH(BN, ST)                                                                         \
-  if (a_mn && b_mn)       e = launch_cfg<BN, ST, true, true, false, 2>(sa, sb, p, grid, stream);      \
-  else if (a_mn)          e = launch_cfg<BN, ST, true, false, false, 2>(sa, sb, p, grid, stream);     \
-  else if (b_mn)          e = launch_cfg<BN, ST, false, true, false, 2>(sa, sb, p, grid, stream);     \
-  else                    e = launch_cfg<BN, ST, false, false, false, 2>(sa, sb, p, grid, stream);
+  if (a_mn && b_mn)       e = launch_cfg<BN, ST, true, true, false, 2>(sa, sb, td, p, grid, stream);      \
+  else if (a_mn)          e = launch_cfg<BN, ST, true, false, false, 2>(sa, sb, td, p, grid, stream);     \
+  else if (b_mn)          e = launch_cfg<BN, ST, false, true, false, 2>(sa, sb, td, p, grid, stream);     \
+  else                    e = launch_cfg<BN, ST, false, false, false, 2>(sa, sb, td, p, grid, stream);
     if (best_bn == 256) { FMB_DISPATCH(256, 6) } else { FMB_DISPATCH(128, 8) }
 #undef FMB_DISPATCH
   } else if (ps != nullptr) {
 #define FMB_DISPATCH(BN, ST)                                                                         \
-  if (a_mn && b_mn)       e = launch_cfg<BN, ST, true, true, true>(ta, tb, p, grid, stream);          \
-  else if (a_mn)          e = launch_cfg<BN, ST, true, false, true>(ta, tb, p, grid, stream);         \
-  else if (b_mn)          e = launch_cfg<BN, ST, false, true, true>(ta, tb, p, grid, stream);         \
-  else                    e = launch_cfg<BN, ST, false, false, true>(ta, tb, p, grid, stream);
+  if (a_mn && b_mn)       e = launch_cfg<BN, ST, true, true, true>(ta, tb, td, p, grid, stream);          \
+  else if (a_mn)          e = launch_cfg<BN, ST, true, false, true>(ta, tb, td, p, grid, stream);         \
+  else if (b_mn)          e = launch_cfg<BN, ST, false, true, true>(ta, tb, td, p, grid, stream);         \
+  else                    e = launch_cfg<BN, ST, false, false, true>(ta, tb, td, p, grid, stream);
     if (best_bn == 256) { FMB_DISPATCH(256, 4) } else { FMB_DISPATCH(128, 6) }
 #undef FMB_DISPATCH
   } else {
@@ -933,10 +996,10 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
     sa.m[0] = ta.m[0];
     sb.m[0] = tb.m[0];
 #define FMB_DISPATCH(BN, ST)                                                                         \
-  if (a_mn && b_mn)       e = launch_cfg<BN, ST, true, true, false>(sa, sb, p, grid, stream);         \
-  else if (a_mn)          e = launch_cfg<BN, ST, true, false, false>(sa, sb, p, grid, stream);        \
-  else if (b_mn)          e = launch_cfg<BN, ST, false, true, false>(sa, sb, p, grid, stream);        \
-  else                    e = launch_cfg<BN, ST, false, false, false>(sa, sb, p, grid, stream);
+  if (a_mn && b_mn)       e = launch_cfg<BN, ST, true, true, false>(sa, sb, td, p, grid, stream);         \
+  else if (a_mn)          e = launch_cfg<BN, ST, true, false, false>(sa, sb, td, p, grid, stream);        \
+  else if (b_mn)          e = launch_cfg<BN, ST, false, true, false>(sa, sb, td, p, grid, stream);        \
+  else                    e = launch_cfg<BN, ST, false, false, false>(sa, sb, td, p, grid, stream);
     if (best_bn == 256) { FMB_DISPATCH(256, 4) } else if (best_bn == 128) { FMB_DISPATCH(128, 6) } else { FMB_DISPATCH(64, 8) }
 #undef FMB_DISPATCH
   }
