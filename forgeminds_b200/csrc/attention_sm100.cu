@@ -60,18 +60,6 @@ __device__ __forceinline__ bool named_bar_and(int id, int nthreads, bool pred) {
   return out != 0;
 }
 
-// tcgen05.wait::ld that also names the destination registers, so that no use of them can be
-// scheduled ahead of the wait.
-__device__ __forceinline__ void tmem_ld_fence(uint32_t (&r)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
-                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
-                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-               :
-               : "memory");
-}
-
 constexpr int ATT_ROW_WARPS = 8;      // two warps per TMEM lane quarter: each owns 64 of the 128 columns
 constexpr int ATT_FWD_THREADS = 32 * (2 + ATT_ROW_WARPS);
 constexpr int ATT_BWD_THREADS = 32 * (2 + ATT_ROW_WARPS + 4);
@@ -89,13 +77,15 @@ struct FwdSmem {
 };
 
 template <int HD_PAD>
-__global__ void __launch_bounds__(ATT_FWD_THREADS)
+__global__ void __launch_bounds__(ATT_FWD_THREADS, HD_PAD == 64 ? 2 : 1)   // head dim 64: two CTAs share an SM
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, AttnParams p) {
   using L = FwdSmem<HD_PAD>;
   constexpr int PANELS = L::PANELS;
-  constexpr uint32_t TMEM_COLS = 256;
-  constexpr uint32_t S_COL = 0, O_COL = 128;
+  // P (bf16, two values per 32-bit column) is handed to the P.V product in TMEM, as its A operand: it
+  // never goes through shared memory, whose bandwidth the operand reads of the MMAs already use up.
+  constexpr uint32_t TMEM_COLS = HD_PAD == 64 ? 256 : 512;
+  constexpr uint32_t S_COL = 0, O_COL = 128, P_COL = O_COL + HD_PAD;
   constexpr int OH = HD_PAD / 2;                 // output columns owned by one half
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -188,9 +178,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < ATT_BN / 16; ++kk) {
-          const uint64_t da = umma_smem_desc_sw128(sbase + L::P_OFF + (kk >> 2) * PANEL_BYTES + (kk & 3) * 32, 16, 1024);
           const uint64_t db = umma_smem_desc_sw128(sbase + L::V_OFF + st * L::TILE + kk * 2048, PANEL_BYTES, 1024);
-          umma_f16_ss(tmem + O_COL, da, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_f16_ts(tmem + O_COL, tmem + P_COL + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);   // 16 kv = 8 columns
         }
         umma_commit(kv_empty0 + 8 * st);
         if (j + 1 < n_kv) {
@@ -260,41 +249,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float m_new = fmaxf(m_run, fmaxf(mx, *get_slot) * p.scale_log2);
       const float alpha = exp2f(m_run - m_new);          // 0 on the first tile (m_run = -inf)
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t packed[32];
-      if (!masked) {
+      // 32 columns at a time: exponentials, row sum, bf16 pairs into this thread's P columns in TMEM
+      auto p_half = [&](const uint32_t (&r)[32], int c_first, int word0) {
+        uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float a0 = exp2f(fmaf(__uint_as_float(r0[i]), p.scale_log2, -m_new));
-          const float a1 = exp2f(fmaf(__uint_as_float(r0[i + 1]), p.scale_log2, -m_new));
-          const float b0 = exp2f(fmaf(__uint_as_float(r1[i]), p.scale_log2, -m_new));
-          const float b1 = exp2f(fmaf(__uint_as_float(r1[i + 1]), p.scale_log2, -m_new));
-          sum4[(i >> 1) & 1] += a0 + a1;
-          sum4[2 + ((i >> 1) & 1)] += b0 + b1;
+          float a0 = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_new));
+          float a1 = exp2f(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_new));
+          if (masked) {
+            if (c_first + i >= limit) a0 = 0.f;
+            if (c_first + i + 1 >= limit) a1 = 0.f;
+          }
+          sum4[(i >> 1) & 3] += a0 + a1;
           packed[i >> 1] = pack_bf16(a0, a1);
-          packed[16 + (i >> 1)] = pack_bf16(b0, b1);
         }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float a0 = exp2f(fmaf(__uint_as_float(r0[i]), p.scale_log2, -m_new));
-          float a1 = exp2f(fmaf(__uint_as_float(r0[i + 1]), p.scale_log2, -m_new));
-          float b0 = exp2f(fmaf(__uint_as_float(r1[i]), p.scale_log2, -m_new));
-          float b1 = exp2f(fmaf(__uint_as_float(r1[i + 1]), p.scale_log2, -m_new));
-          if (c_lo + i >= limit) a0 = 0.f;
-          if (c_lo + i + 1 >= limit) a1 = 0.f;
-          if (c_lo + 32 + i >= limit) b0 = 0.f;
-          if (c_lo + 33 + i >= limit) b1 = 0.f;
-          sum4[(i >> 1) & 1] += a0 + a1;
-          sum4[2 + ((i >> 1) & 1)] += b0 + b1;
-          packed[i >> 1] = pack_bf16(a0, a1);
-          packed[16 + (i >> 1)] = pack_bf16(b0, b1);
-        }
-      }
-#pragma unroll
-      for (int q8 = 0; q8 < 8; ++q8) {
-        uint4 v = make_uint4(packed[4 * q8], packed[4 * q8 + 1], packed[4 * q8 + 2], packed[4 * q8 + 3]);
-        *reinterpret_cast<uint4*>(smem + L::P_OFF + swz_tile_offset(row, half * 8 + q8)) = v;
-      }
+        tmem_st_32x16(t_lane + P_COL + half * 32 + word0, packed);
+      };
+      p_half(r0, c_lo, 0);
+      p_half(r1, c_lo + 32, 16);
       l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       m_run = m_new;
       // rescale this half's output columns only if some row of the warp moved its maximum
@@ -308,9 +280,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
           tmem_st_32x32(t_lane + O_COL + half * OH + c * 32, r);
         }
-        tmem_wait_st();
       }
-      fence_proxy_async_smem();
+      tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);

@@ -208,7 +208,7 @@ gemm8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           for (int c = 0; c < BN / 32; ++c) {
             uint32_t r[32];
             tmem_ld_32x32(t_row + c * 32, r);
-            tmem_wait_ld();
+            tmem_ld_fence(r);
 #pragma unroll
             for (int i = 0; i < 32; ++i) out[c][i] += __uint_as_float(r[i]) * s;
           }
@@ -234,7 +234,7 @@ gemm8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           if (col0 >= p.N) break;
           uint32_t r[32];
           tmem_ld_32x32(t_row + c * 32, r);
-          tmem_wait_ld();
+          tmem_ld_fence(r);
           if (!row_ok) continue;
           float v[32];
 #pragma unroll

@@ -460,7 +460,8 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
           uint32_t rg[32], ru[32];
           tmem_ld_32x32(t_row + c * 32, rg);
           tmem_ld_32x32(t_row + 128 + c * 32, ru);
-          tmem_wait_ld();
+          tmem_ld_fence(rg);
+          tmem_ld_fence(ru);
           if (!row_ok) continue;
           const int hc = n_blk * 128 + c * 32;                // hidden-unit column, < epi_h by construction
           __nv_bfloat16* gp = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + hc;
@@ -490,7 +491,7 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
           if (col0 >= p.N) break;
           uint32_t r[32];
           tmem_ld_32x32(t_row + c * 32, r);
-          tmem_wait_ld();
+          tmem_ld_fence(r);
           if (!row_ok) continue;
           const __nv_bfloat16* gin = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + static_cast<long long>(row) * p.ld_aux_in + col0;
           const __nv_bfloat16* uin = gin + p.epi_h;
@@ -673,12 +674,12 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
       if (n_chunks > 0) tmem_ld_32x32(t_row, ra);
 #pragma unroll 1
       for (int c = 0; c < n_chunks; c += 2) {
-        tmem_wait_ld();
+        tmem_ld_fence(ra);
         if (c + 1 < n_chunks) tmem_ld_32x32(t_row + (c + 1) * 32, rb);
         else release_acc();
         finish_chunk(c, ra);
         if (c + 1 < n_chunks) {
-          tmem_wait_ld();
+          tmem_ld_fence(rb);
           if (c + 2 < n_chunks) tmem_ld_32x32(t_row + (c + 2) * 32, ra);
           else release_acc();
           finish_chunk(c + 1, rb);
