@@ -237,7 +237,7 @@ template <int BN, int STAGES, bool A_MN, bool B_MN, bool PEER, int CTAS = 1>
 __global__ void __launch_bounds__(GEMM_THREADS + (PEER ? GATHER_THREADS : 0), 1)
 gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant__ MapSet<PEER> tmB,
                  const __grid_constant__ CUtensorMap tmD, GemmParams p) {
-  static_assert(CTAS == 1 || (CTAS == 2 && !PEER && BN >= 128), "CTA pairs: plain products with BN >= 128");
+  static_assert(CTAS == 1 || (CTAS == 2 && BN >= 128), "CTA pairs need BN >= 128");   // and no gathered operand
   using L = GemmSmem<BN, STAGES, CTAS>;
   constexpr int BM = GEMM_BM, BK = GEMM_BK;
   constexpr int BN_CTA = BN / CTAS;                  // columns of B that this CTA loads
@@ -823,7 +823,8 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
   const bool can_split = allow_split && d_f32 && (C == nullptr || C == D);
   // CTA pairs (256-row tiles over two SMs) serve plain products; FMB_GEMM_PAIR=0 turns them off.
   static const bool pair_env = [] { const char* v = getenv("FMB_GEMM_PAIR"); return v == nullptr || v[0] != '0'; }();
-  const bool pair_ok = pair_env && ps == nullptr && gs.mode == 0 && (es == nullptr || es->epi != 1) && sms % 2 == 0;
+  const bool pair_ok = pair_env && (ps == nullptr || ps->gather == 0) && gs.mode == 0 && (es == nullptr || es->epi != 1) &&
+                       sms % 2 == 0;
 
   // Pick the N tile, the split count and the CTAs per tile that fill the machine best.
   int best_bn = 256, best_split = 1, best_ctas = 1;
@@ -905,8 +906,8 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
     if (ps->d_ptrs != nullptr) {
       p.d_rows_per_rank = M / ps->world;
       for (int r = 0; r < ps->world; ++r) p.d_peer[r] = ps->d_ptrs[r];
-      if (p.rot_m == 0 && p.own_m_tiles == 0)
-        p.rot_m = ((ps->rank + 1) % ps->world) * (p.d_rows_per_rank / GEMM_BM);   // remote rows first
+      if (p.rot_m == 0 && p.own_m_tiles == 0 && p.d_rows_per_rank % (GEMM_BM * best_ctas) == 0)
+        p.rot_m = ((ps->rank + 1) % ps->world) * (p.d_rows_per_rank / (GEMM_BM * best_ctas));   // remote rows first
     }
   }
   p.epi = 0; p.epi_h = 0; p.seg = 0;
@@ -973,7 +974,15 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
   const int units = sms / best_ctas;
   const int grid = best_ctas * static_cast<int>(total < units ? total : units);
   cudaError_t e;
-  if (best_ctas == 2) {
+  if (best_ctas == 2 && ps != nullptr) {
+#define FMB_DISPATCH(BN, ST)                                                                         \
+  if (a_mn && b_mn)       e = launch_cfg<BN, ST, true, true, true, 2>(ta, tb, td, p, grid, stream);   \
+  else if (a_mn)          e = launch_cfg<BN, ST, true, false, true, 2>(ta, tb, td, p, grid, stream);  \
+  else if (b_mn)          e = launch_cfg<BN, ST, false, true, true, 2>(ta, tb, td, p, grid, stream);  \
+  else                    e = launch_cfg<BN, ST, false, false, true, 2>(ta, tb, td, p, grid, stream);
+    if (best_bn == 256) { FMB_DISPATCH(256, 6) } else { FMB_DISPATCH(128, 8) }
+#undef FMB_DISPATCH
+  } else if (best_ctas == 2) {
     MapSet<false> sa, sb;
     sa.m[0] = ta.m[0];
     sb.m[0] = tb.m[0];
