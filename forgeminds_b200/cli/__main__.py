@@ -1,17 +1,18 @@
-"""``python -m forgeminds_b200.cli {bench,kbench,matrix,audit} [options]``"""
+"""``python -m forgeminds_b200.cli {bench,kbench,gemmbench,matrix,audit,commbench} [options]``"""
 from __future__ import annotations
 
 import sys
 
-TOOLS = ("bench", "kbench", "matrix", "audit", "commbench")
+TOOLS = ("bench", "kbench", "gemmbench", "matrix", "audit", "commbench")
 
 
 def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     if not argv or argv[0] in ("-h", "--help") or argv[0] not in TOOLS:
-        print("usage: python -m forgeminds_b200.cli {bench|kbench|matrix|audit|commbench} [options]\n"
+        print("usage: python -m forgeminds_b200.cli {bench|kbench|gemmbench|matrix|audit|commbench} [options]\n"
               "  bench   training throughput of a GPT preset under any mesh / quant / offload setting\n"
               "  kbench  per-kernel timings against eager PyTorch\n"
+              "  gemmbench  the linear-layer products of a GPT block against cuBLAS\n"
               "  matrix  sweep of bench over quantisation modes\n"
               "  audit   host reads, kernel launches and top kernels of one training step\n"
               "  commbench  peer-memory kernels against their NCCL formulations (run under torchrun)")

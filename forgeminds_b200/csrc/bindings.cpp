@@ -697,6 +697,33 @@ void gemm_grouped_rows(const Tensor& a, const Tensor& b, Tensor& out, const Tens
                            tile_group.data_ptr<int>(), nullptr, b.stride(0), 0, st, cur_stream()), "gemm_grouped_rows");
 }
 
+// Batched product out[g] = alpha * a[g] @ op(b[g]) + beta * c[g] in one launch: a [G, M, K] (M a multiple of
+// 128), b [G, N, K] or, with b_mn, [G, K, N]; `tile_group[i]` = i / (M / 128) names the batch entry of row tile i.
+void gemm_batched(const Tensor& a, const Tensor& b, Tensor& out, const c10::optional<Tensor>& c, bool b_mn, double alpha,
+                  double beta, const Tensor& tile_group, const c10::optional<Tensor>& status) {
+  TORCH_CHECK(a.is_cuda() && a.dim() == 3 && b.dim() == 3 && out.dim() == 3 && a.is_contiguous() && b.is_contiguous() &&
+              out.is_contiguous() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16);
+  const int64_t G = a.size(0), M = a.size(1), K = a.size(2);
+  const int64_t N = b_mn ? b.size(2) : b.size(1);
+  TORCH_CHECK(b.size(0) == G && (b_mn ? b.size(1) : b.size(2)) == K && out.size(0) == G && out.size(1) == M &&
+              out.size(2) == N && M % 128 == 0);
+  TORCH_CHECK(tile_group.numel() >= G * M / 128 && tile_group.scalar_type() == at::kInt);
+  const bool f32 = out.scalar_type() == at::kFloat;
+  const void* cp = nullptr;
+  bool c_f32 = false;
+  if (c.has_value() && c->defined()) {
+    TORCH_CHECK(c->is_contiguous() && c->sizes() == out.sizes());
+    cp = c->data_ptr();
+    c_f32 = c->scalar_type() == at::kFloat;
+  }
+  c10::cuda::CUDAGuard guard(a.device());
+  int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
+  ok(fmb_gemm_bf16_grouped(a.data_ptr(), b.data_ptr(), out.data_ptr(), cp, static_cast<int>(G * M), static_cast<int>(N),
+                           static_cast<int>(K), 0, b_mn, K, b.stride(1), N, N, f32, c_f32, static_cast<float>(alpha),
+                           static_cast<float>(beta), 1, static_cast<int>(G), tile_group.data_ptr<int>(), nullptr,
+                           b.stride(0), 0, st, cur_stream()), "gemm_batched");
+}
+
 // Per-group weight gradient: out[g] [M, N] (+)= a[rows_g, M]^T @ b[rows_g, N]; `region` is [G, 3] int32
 // {first row, used, padded rows}. `accumulate` adds to `out` (fp32) instead of overwriting it.
 void gemm_grouped_wgrad(const Tensor& a, const Tensor& b, Tensor& out, const Tensor& region, bool accumulate,
@@ -816,6 +843,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_plan", &moe_plan);
   m.def("gemm_grouped_rows", &gemm_grouped_rows);
   m.def("gemm_grouped_wgrad", &gemm_grouped_wgrad);
+  m.def("gemm_batched", &gemm_batched);
   m.def("moe_tile_groups", &moe_tile_groups);
   m.def("moe_gather", &moe_gather);
   m.def("moe_combine", &moe_combine);

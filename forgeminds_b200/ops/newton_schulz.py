@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import torch
 
+from . import require, status_word
 from .functional import gemm
 
 NS_A, NS_B, NS_C = 3.4445, -4.7750, 2.0315
@@ -33,6 +34,8 @@ def newton_schulz_bf16(g: torch.Tensor, steps: int = 5):
     x = x.to(torch.bfloat16)
     x = (x / (x.norm(dim=(-2, -1), keepdim=True) + 1e-7)).contiguous()
     r, c = x.shape[-2], x.shape[-1]
+    if x.shape[0] > 1 and r % 128 == 0:
+        return _batched(x, steps, flip, shape)
     out = torch.empty_like(x)
     gram = torch.empty((r, r), dtype=torch.bfloat16, device=x.device)
     poly = torch.empty_like(gram)
@@ -48,4 +51,29 @@ def newton_schulz_bf16(g: torch.Tensor, steps: int = 5):
             out[i].copy_(cur)
     if flip:
         out = out.mT
+    return out.reshape(shape)
+
+
+_tile_groups = {}
+
+
+def _batched(x: torch.Tensor, steps: int, flip: bool, shape):
+    """All matrices of a stack in one launch per product (row tiles of entry g use B matrix g)."""
+    C = require()
+    G, r, c = x.shape
+    key = (G, r, x.device)
+    tg = _tile_groups.get(key)
+    if tg is None:
+        tg = torch.arange(G, dtype=torch.int32, device=x.device).repeat_interleave(r // 128).contiguous()
+        _tile_groups[key] = tg
+    st = status_word(x.device)
+    cur, nxt = x, torch.empty_like(x)
+    gram = torch.empty((G, r, r), dtype=torch.bfloat16, device=x.device)
+    poly = torch.empty_like(gram)
+    for _ in range(steps):
+        C.gemm_batched(cur, cur, gram, None, False, 1.0, 0.0, tg, st)
+        C.gemm_batched(gram, gram, poly, gram, False, NS_C, NS_B, tg, st)
+        C.gemm_batched(poly, cur, nxt, cur, True, 1.0, NS_A, tg, st)
+        cur, nxt = nxt, cur
+    out = cur.mT if flip else cur
     return out.reshape(shape)

@@ -159,3 +159,37 @@ def test_row_dots_from_the_gemm_epilogue(seg, seq, cuda_status):
     if seq:
         dots = dots.view(M // seq, seq, groups).transpose(1, 2)
     assert torch.allclose(rd, dots, rtol=2e-3, atol=2e-2)
+
+
+def test_batched_gemm_matches_bmm(cuda_status):
+    """One launch for a stack of products, with the scaled C term used by the Newton-Schulz polynomial."""
+    from forgeminds_b200 import ops
+    C = ops.require()
+    torch.manual_seed(3)
+    G, M, N, K = 3, 256, 200, 320
+    a = torch.randn(G, M, K, device="cuda").to(torch.bfloat16)
+    b = torch.randn(G, N, K, device="cuda").to(torch.bfloat16)
+    c = torch.randn(G, M, N, device="cuda").to(torch.bfloat16)
+    tg = torch.arange(G, dtype=torch.int32, device="cuda").repeat_interleave(M // 128).contiguous()
+    out = torch.empty(G, M, N, device="cuda", dtype=torch.bfloat16)
+    C.gemm_batched(a, b, out, c, False, 0.5, -2.0, tg, cuda_status)
+    want = 0.5 * torch.bmm(a.float(), b.float().transpose(1, 2)) - 2.0 * c.float()
+    assert (out.float() - want).norm() / want.norm() < 1e-2
+    bt = b.transpose(1, 2).contiguous()                       # [G, K, N]: the MN-major form of the same operand
+    C.gemm_batched(a, bt, out, None, True, 1.0, 0.0, tg, cuda_status)
+    want = torch.bmm(a.float(), b.float().transpose(1, 2))
+    assert (out.float() - want).norm() / want.norm() < 1e-2
+
+
+@pytest.mark.parametrize("shape", [(4, 256, 384), (3, 384, 256), (1, 256, 512)])
+def test_newton_schulz_stack_orthogonalises(shape, cuda_status):
+    from forgeminds_b200 import kernels as K
+    from forgeminds_b200.kernels import reference as _ref
+    torch.manual_seed(5)
+    g = torch.randn(*shape, device="cuda").to(torch.bfloat16)
+    got = K.newton_schulz(g, 5)
+    want = _ref.newton_schulz(g.float(), 5, torch.float32)
+    assert got.shape == g.shape and got.dtype == torch.bfloat16
+    assert (got.float() - want).norm() / want.norm() < 0.05
+    sv = torch.linalg.svdvals(got.float())
+    assert sv.min() > 0.4 and sv.max() < 1.4
