@@ -74,7 +74,7 @@ __device__ __forceinline__ void signal_all(const Peers& flags, int slot, int ran
     st_release_sys(static_cast<uint32_t*>(flags.p[threadIdx.x]) + slot * MAX_PEERS + rank, epoch);
   }
 }
-// Threads 0..world-1 wait for one source each; the whole block gets the verdict (contains __syncthreads).
+// Threads 0..world-1 wait for one source each; the whole block gets the result (contains __syncthreads).
 __device__ __forceinline__ bool wait_all(const Peers& flags, int slot, int rank, int world, uint32_t epoch,
                                          unsigned long long timeout_ns, int* status) {
   int ok = 1;

@@ -193,3 +193,38 @@ def test_newton_schulz_stack_orthogonalises(shape, cuda_status):
     assert (got.float() - want).norm() / want.norm() < 0.05
     sv = torch.linalg.svdvals(got.float())
     assert sv.min() > 0.4 and sv.max() < 1.4
+
+
+@pytest.mark.parametrize("env", [{"FMB_GEMM_PAIR": "0"}, {"FMB_GEMM_DTMA": "0"}])
+def test_gemm_switches_keep_the_single_cta_and_register_store_paths_correct(env):
+    """The switches are read once per process, so each setting runs in a child process."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import torch
+from forgeminds_b200.ops import functional as Fn
+from forgeminds_b200 import ops
+torch.manual_seed(0)
+for (M, N, K, a_mn, b_mn, acc) in [(512, 384, 640, False, False, False), (1024, 1024, 4096, True, True, True),
+                                   (304, 136, 72, True, False, False), (640, 200, 512, False, True, True)]:
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda").to(torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda").to(torch.bfloat16)
+    want = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+    if acc:
+        base = torch.randn(M, N, device="cuda")
+        out = base.clone()
+        Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, c=out, beta=1.0, allow_split=True)
+        want = want + base
+    else:
+        out = Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn).float()
+    torch.cuda.synchronize()
+    assert int(ops.status_word(torch.device("cuda")).item()) == 0
+    rel = ((out - want).norm() / want.norm()).item()
+    assert rel < (1e-5 if acc else 1e-2), (M, N, K, rel)
+print("ok")
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", code], env={**os.environ, **env, "PYTHONPATH": root}, capture_output=True,
+                         text=True, timeout=300)
+    assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-2000:]

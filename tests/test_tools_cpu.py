@@ -142,3 +142,13 @@ def test_deepspeed_engine_needs_the_library():
         pass
     with pytest.raises((ImportError, RuntimeError)):
         ds._deepspeed()
+
+
+def test_gemmbench_is_registered_and_refuses_to_run_without_a_gpu(capsys):
+    import torch
+    from forgeminds_b200.cli import __main__ as cli
+    from forgeminds_b200.cli import gemmbench
+    assert "gemmbench" in cli.TOOLS
+    if not torch.cuda.is_available():
+        assert gemmbench.main([]) == 1
+        assert "needs a GPU" in capsys.readouterr().out
