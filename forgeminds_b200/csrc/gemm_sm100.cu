@@ -189,39 +189,65 @@ __device__ __forceinline__ bool wait_count(const int* ctr, int want, unsigned lo
 }
 
 constexpr int GATHER_THREADS = 64;
+constexpr int GATHER_DEPTH = 16;
 
 // Executed by the two gather warps of every CTA: pull the other ranks' rows of the gathered operand into
-// this rank's buffer, 128-row block by block, nearest rank first. Row r of a block is copied by the CTA
-// with blockIdx.x == r (mod gridDim.x); each CTA adds the number of rows it finished to the block's counter.
+// this rank's buffer, nearest rank first, 128-row block by block. The remote rows form one list that the
+// CTAs share round robin; a CTA moves two rows at a time (up to 16 KB in flight: one NVLink round trip
+// is several microseconds) and then adds the rows it finished to their blocks' counters.
 __device__ __forceinline__ void gather_rows(const GemmParams& p, int tid) {
   const int vec_per_row = p.g_row_bytes >> 4;
-  const int blocks_per_src = p.g_rows_per_src >> 7;
-  for (int step = 1; step < p.world; ++step) {
-    const int src = (p.rank + step) % p.world;
-    if (p.g_slot >= 0 && !wait_epoch(p.flags + p.g_slot * MAX_PEERS + src, p.g_epoch, p.timeout_ns, p.status)) return;
-    for (int b = 0; b < blocks_per_src; ++b) {
-      const int blk = src * blocks_per_src + b;
-      int done = 0;
-      for (int r = blockIdx.x; r < 128; r += gridDim.x) {
-        const long long off = (static_cast<long long>(blk) * 128 + r) * p.g_ld * 2;
-        const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const char*>(p.g_src[src]) + off);
-        uint4* dp = reinterpret_cast<uint4*>(static_cast<char*>(p.g_local) + off);
-        for (int v0 = tid; v0 < vec_per_row; v0 += GATHER_THREADS * 8) {
-          uint4 buf[8];
+  const int rps = p.g_rows_per_src;
+  const int rows_total = (p.world - 1) * rps;
+  uint32_t waited = 0;                           // sources whose flag has been seen
+  auto locate = [&](int q, int& src, long long& off, int& blk) {
+    const int step = q / rps + 1, lr = q - (step - 1) * rps;
+    src = (p.rank + step) % p.world;
+    const long long grow = static_cast<long long>(src) * rps + lr;      // row of the full operand
+    off = grow * p.g_ld * 2;
+    blk = static_cast<int>(grow >> 7);
+  };
+  for (int q = blockIdx.x; q < rows_total; q += 2 * gridDim.x) {
+    int src0, src1 = 0, blk0, blk1 = 0;
+    long long off0, off1 = 0;
+    const bool two = q + static_cast<int>(gridDim.x) < rows_total;
+    locate(q, src0, off0, blk0);
+    if (two) locate(q + gridDim.x, src1, off1, blk1);
+    if (p.g_slot >= 0) {
+      if (!(waited & (1u << src0))) {
+        if (!wait_epoch(p.flags + p.g_slot * MAX_PEERS + src0, p.g_epoch, p.timeout_ns, p.status)) return;
+        waited |= 1u << src0;
+      }
+      if (two && !(waited & (1u << src1))) {
+        if (!wait_epoch(p.flags + p.g_slot * MAX_PEERS + src1, p.g_epoch, p.timeout_ns, p.status)) return;
+        waited |= 1u << src1;
+      }
+    }
+    const uint4* sp0 = reinterpret_cast<const uint4*>(static_cast<const char*>(p.g_src[src0]) + off0);
+    uint4* dp0 = reinterpret_cast<uint4*>(static_cast<char*>(p.g_local) + off0);
+    const uint4* sp1 = reinterpret_cast<const uint4*>(static_cast<const char*>(p.g_src[src1]) + off1);
+    uint4* dp1 = reinterpret_cast<uint4*>(static_cast<char*>(p.g_local) + off1);
+    constexpr int HALF = GATHER_DEPTH / 2;
+    for (int v0 = tid; v0 < vec_per_row; v0 += GATHER_THREADS * HALF) {
+      uint4 a[HALF], b[HALF];
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
-            if (v0 + u * GATHER_THREADS < vec_per_row) buf[u] = ld_peer_u4(sp + v0 + u * GATHER_THREADS);
-#pragma unroll
-          for (int u = 0; u < 8; ++u)
-            if (v0 + u * GATHER_THREADS < vec_per_row) dp[v0 + u * GATHER_THREADS] = buf[u];
+      for (int u = 0; u < HALF; ++u)
+        if (v0 + u * GATHER_THREADS < vec_per_row) {
+          a[u] = ld_peer_u4(sp0 + v0 + u * GATHER_THREADS);
+          if (two) b[u] = ld_peer_u4(sp1 + v0 + u * GATHER_THREADS);
         }
-        ++done;
-      }
-      if (done) {
-        __threadfence();
-        asm volatile("bar.sync 1, 64;" ::: "memory");
-        if (tid == 0) atomicAdd(p.g_ready + blk, done);
-      }
+#pragma unroll
+      for (int u = 0; u < HALF; ++u)
+        if (v0 + u * GATHER_THREADS < vec_per_row) {
+          dp0[v0 + u * GATHER_THREADS] = a[u];
+          if (two) dp1[v0 + u * GATHER_THREADS] = b[u];
+        }
+    }
+    __threadfence();
+    asm volatile("bar.sync 1, 64;" ::: "memory");
+    if (tid == 0) {
+      atomicAdd(p.g_ready + blk0, 1);
+      if (two) atomicAdd(p.g_ready + blk1, 1);
     }
   }
 }
@@ -544,6 +570,44 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
           }
           return;
         }
+        if constexpr (PEER) {
+          if (p.d_rows_per_rank > 0) {
+            // Reduce-scatter output: two chunks (64 bf16 columns = 128 bytes per row) are staged in shared
+            // memory, then eight lanes write one row's 128 contiguous bytes into slice `rank` of the
+            // owner's staging buffer, so what crosses NVLink are whole lines, not 16-byte pieces.
+            const int row0 = m_blk * BM + quarter * 32;
+            if (row0 >= p.M) return;                       // uniform across the warp
+            const uint32_t buf = stg_base + (((static_cast<uint32_t>(c) >> 1) & 1u) << 12);
+            const uint32_t row_addr = buf + static_cast<uint32_t>(lane) * 128u;
+            const int jb = (c & 1) * 4;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              st_shared_v4(row_addr + (static_cast<uint32_t>((jb + q) ^ (lane & 7)) << 4),
+                           pack_bf16(__uint_as_float(r[8 * q]) * alpha, __uint_as_float(r[8 * q + 1]) * alpha),
+                           pack_bf16(__uint_as_float(r[8 * q + 2]) * alpha, __uint_as_float(r[8 * q + 3]) * alpha),
+                           pack_bf16(__uint_as_float(r[8 * q + 4]) * alpha, __uint_as_float(r[8 * q + 5]) * alpha),
+                           pack_bf16(__uint_as_float(r[8 * q + 6]) * alpha, __uint_as_float(r[8 * q + 7]) * alpha));
+            if (!(c & 1) && c + 1 < n_chunks) return;      // the other half of the pair follows
+            __syncwarp();
+            const int pair_col0 = n_blk * BN + (c & ~1) * 32;
+            const int valid = min(64, p.N - pair_col0);    // existing columns of this pair (a multiple of 8)
+            const int owner = row0 / p.d_rows_per_rank;
+            __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.d_peer[owner]) +
+                                  (static_cast<long long>(p.rank) * p.d_rows_per_rank + (row0 - owner * p.d_rows_per_rank)) * p.ldd +
+                                  pair_col0;
+            const int j = lane & 7, rsub = lane >> 3;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int rr = it * 4 + rsub;
+              if (row0 + rr < p.M && j * 8 < valid) {
+                const uint4 val = ld_shared_v4(buf + static_cast<uint32_t>(rr) * 128u + (static_cast<uint32_t>(j ^ (rr & 7)) << 4));
+                *reinterpret_cast<uint4*>(base + static_cast<long long>(rr) * p.ldd + j * 8) = val;
+              }
+            }
+            __syncwarp();
+            return;
+          }
+        }
         if (!row_ok) return;
         float v[32];
 #pragma unroll
@@ -629,15 +693,7 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
           }
         } else {
           __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + ti.d_off + static_cast<long long>(row) * p.ldd + col0;
-          bool wide = wide_d;
-          if constexpr (PEER) {
-            if (p.d_rows_per_rank > 0) {          // slice `rank` of the staging buffer of the rank that owns this row
-              const int owner = row / p.d_rows_per_rank;
-              dp = reinterpret_cast<__nv_bfloat16*>(p.d_peer[owner]) +
-                   (static_cast<long long>(p.rank) * p.d_rows_per_rank + (row - owner * p.d_rows_per_rank)) * p.ldd + col0;
-              wide = false;
-            }
-          }
+          const bool wide = wide_d;
           if (full && wide) {                     // one 32-byte sector per store
 #pragma unroll
             for (int i = 0; i < 2; ++i)
