@@ -662,32 +662,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 1) { tc_fence_after(); tmem_dealloc<512>(tmem); }
 }
 
-// delta[b, h, t] = sum_d dO * O   (one warp per (b, t, h))
+// delta[b, h, t] = sum_d dO * O. `lpr` lanes (a power of two, 8 elements each per pass) share one (b, t, h)
+// row, so a warp reads 32 / lpr consecutive heads' rows as whole 16-byte pieces.
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
-                  int B, int T, int Hq, int hd, long long o_stride_t) {
+                  int B, int T, int Hq, int hd, long long o_stride_t, int lpr) {
   pdl_wait();
   pdl_launch_dependents();
-  const int lane = threadIdx.x & 31;
-  const long long item = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;   // (b, t, h)
-  if (item >= static_cast<long long>(B) * T * Hq) return;
-  const int h = static_cast<int>(item % Hq);
-  const long long bt = item / Hq;
+  const long long gtid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int sub = static_cast<int>(gtid % lpr);
+  const long long item = gtid / lpr;                                   // (b, t, h)
+  const bool live = item < static_cast<long long>(B) * T * Hq;
+  const int h = live ? static_cast<int>(item % Hq) : 0;
+  const long long bt = live ? item / Hq : 0;
   const __nv_bfloat16* orow = o + bt * o_stride_t + static_cast<long long>(h) * hd;
   const __nv_bfloat16* grow = d_o + bt * o_stride_t + static_cast<long long>(h) * hd;
   float s = 0.f;
-  for (int c = lane * 8; c < hd; c += 256) {
-    const uint4 a = *reinterpret_cast<const uint4*>(orow + c), g = *reinterpret_cast<const uint4*>(grow + c);
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+  if (live) {
+    for (int c = sub * 8; c < hd; c += lpr * 8) {
+      const uint4 a = *reinterpret_cast<const uint4*>(orow + c), g = *reinterpret_cast<const uint4*>(grow + c);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const float2 af = unpack_bf16(aw[q]), gf = unpack_bf16(gw[q]);
-      s += af.x * gf.x + af.y * gf.y;
+      for (int q = 0; q < 4; ++q) {
+        const float2 af = unpack_bf16(aw[q]), gf = unpack_bf16(gw[q]);
+        s += af.x * gf.x + af.y * gf.y;
+      }
     }
   }
-#pragma unroll
-  for (int ofs = 16; ofs > 0; ofs >>= 1) s += __shfl_xor_sync(0xffffffffu, s, ofs);
-  if (lane == 0) {
+  for (int ofs = lpr >> 1; ofs > 0; ofs >>= 1) s += __shfl_xor_sync(0xffffffffu, s, ofs);
+  if (live && sub == 0) {
     const long long b = bt / T, t = bt % T;
     delta[(b * Hq + h) * T + t] = s;
   }
@@ -779,9 +782,11 @@ extern "C" int fmb_attn_bwd(const void* q, const void* k, const void* v, const v
     return -5;
   if (!delta_ready) {     // else the caller computed delta[b, h, t] already (fused into the producer of dO)
     const long long items = static_cast<long long>(B) * T * Hq;
-    launch_pdl(attn_delta_kernel, dim3(static_cast<unsigned>((items * 32 + 255) / 256)), dim3(256), 0, stream,
+    int lpr = 1;
+    while (lpr < 32 && lpr * 8 < hd) lpr <<= 1;
+    launch_pdl(attn_delta_kernel, dim3(static_cast<unsigned>((items * lpr + 255) / 256)), dim3(256), 0, stream,
                static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, B, T, Hq, hd,
-               o_stride_t);
+               o_stride_t, lpr);
   }
   AttnBwdParams p;
   p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.hd = hd;
