@@ -42,7 +42,28 @@ rs_reduce_kernel(Peers grads, long long lo, long long n, float scale, float* __r
   const long long nvec = n >> 2;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   float* mine = static_cast<float*>(grads.p[rank]) + lo;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+  const bool store = world > 1 || scale != 1.f;
+  long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (world <= 2) {
+    // few sources: four vectors per source in flight per thread, or the loads cannot cover the latency
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+      float4 v[4][2];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+          if (r < world) v[u][r] = ld_peer_f4(static_cast<const float*>(grads.p[r]) + lo + ((i + u * stride) << 2));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float4 a = v[u][0];
+        if (world > 1) { a.x += v[u][1].x; a.y += v[u][1].y; a.z += v[u][1].z; a.w += v[u][1].w; }
+        a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+        if (store) reinterpret_cast<float4*>(mine)[i + u * stride] = a;
+        s += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+      }
+    }
+  }
+  for (; i < nvec; i += stride) {
     float4 v[MAX_PEERS];
 #pragma unroll
     for (int r = 0; r < MAX_PEERS; ++r)
@@ -52,7 +73,7 @@ rs_reduce_kernel(Peers grads, long long lo, long long n, float scale, float* __r
     for (int r = 1; r < MAX_PEERS; ++r)
       if (r < world) { a.x += v[r].x; a.y += v[r].y; a.z += v[r].z; a.w += v[r].w; }
     a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
-    if (world > 1 || scale != 1.f) reinterpret_cast<float4*>(mine)[i] = a;
+    if (store) reinterpret_cast<float4*>(mine)[i] = a;
     s += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
   }
 #pragma unroll
