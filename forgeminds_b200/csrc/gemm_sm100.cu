@@ -1,15 +1,19 @@
 // bf16 GEMM for sm_100a: D[M,N] = alpha * sum_k A(m,k) * B(n,k) + beta * C[M,N].
 //
-// One persistent CTA per SM, six warps with fixed roles:
+// Persistent, one CTA per SM, six warps with fixed roles:
 //   warp 0    one elected thread issues TMA tile loads into a ring of 128B-swizzled smem stages;
 //   warp 1    owns TMEM (two fp32 accumulators) and one elected thread issues tcgen05.mma;
-//   warps 2-5 read the finished accumulator back with tcgen05.ld (one TMEM lane quarter each),
-//             apply the epilogue and store, while the MMA warp already works on the other
-//             accumulator.
+//   warps 2-5 read the finished accumulator back with tcgen05.ld (one TMEM lane quarter each, the
+//             loads one 32-column chunk ahead of the stores), apply the epilogue and store, while the
+//             MMA warp already works on the other accumulator.
+// Plain products run as CTA pairs (cta_group::2): two CTAs of a cluster share one 256 x BN tile, each
+// loading its own 128 rows of A and half of B, so that every SM reads a third less from L2.
 // Operands may be K-major (row-major [rows, K]) or MN-major (row-major [K, rows]); this covers
 // the forward (K,K), input-gradient (K,MN) and weight-gradient (MN,MN) products of a linear layer
-// without a transpose pass. Split-K (fp32 atomic accumulation) fills the machine when the output
-// has fewer tiles than SMs, which is the usual case for weight gradients.
+// without a transpose pass. Split-K fills the machine when the output has fewer tiles than SMs, which
+// is the usual case for weight gradients; fp32 outputs (split or accumulated into C == D) leave as
+// TMA reduce-add boxes staged in shared memory. Peer instantiations gather an operand from the other
+// GPUs of an NVSwitch domain with two extra warps, or scatter bf16 partial tiles to their owners.
 #include <cstdlib>
 #include <cstring>
 
