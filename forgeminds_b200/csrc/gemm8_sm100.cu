@@ -156,13 +156,21 @@ gemm8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     const int quarter = warp & 3;
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
+    const long long d_es = p.d_f32 ? 4 : 2;
+    const bool wide_d = (reinterpret_cast<uintptr_t>(p.D) & 31) == 0 && (p.ldd * d_es) % 32 == 0;   // 32-byte stores stay aligned
     // 32 finished output values of one row, columns [col0, col0 + 32)
     auto store32 = [&](int row, int col0, const float (&v)[32]) {
       if (col0 >= p.N) return;
       const bool full = col0 + 32 <= p.N;
       if (p.d_f32) {
         float* dp = reinterpret_cast<float*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
-        if (full) {
+        if (full && wide_d) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            st_global_v8(dp + 8 * i, __float_as_uint(v[8 * i]), __float_as_uint(v[8 * i + 1]), __float_as_uint(v[8 * i + 2]),
+                         __float_as_uint(v[8 * i + 3]), __float_as_uint(v[8 * i + 4]), __float_as_uint(v[8 * i + 5]),
+                         __float_as_uint(v[8 * i + 6]), __float_as_uint(v[8 * i + 7]));
+        } else if (full) {
 #pragma unroll
           for (int i = 0; i < 8; ++i)
             reinterpret_cast<float4*>(dp)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -172,7 +180,14 @@ gemm8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         }
       } else {
         __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + col0;
-        if (full) {
+        if (full && wide_d) {                     // one 32-byte sector per store
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            st_global_v8(dp + 16 * i, pack_bf16(v[16 * i + 0], v[16 * i + 1]), pack_bf16(v[16 * i + 2], v[16 * i + 3]),
+                         pack_bf16(v[16 * i + 4], v[16 * i + 5]), pack_bf16(v[16 * i + 6], v[16 * i + 7]),
+                         pack_bf16(v[16 * i + 8], v[16 * i + 9]), pack_bf16(v[16 * i + 10], v[16 * i + 11]),
+                         pack_bf16(v[16 * i + 12], v[16 * i + 13]), pack_bf16(v[16 * i + 14], v[16 * i + 15]));
+        } else if (full) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint4 o;
@@ -228,25 +243,56 @@ gemm8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         tc_fence_after();
         const float sa = row_ok ? __ldg(p.sa + row) : 0.f;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        const int cols_left = p.N - n_blk * BN;
+        const int n_chunks = cols_left >= BN ? BN / 32 : (cols_left + 31) / 32;
+        auto finish_chunk = [&](int c, const uint32_t (&r)[32]) {
+          if (!row_ok) return;
           const int col0 = n_blk * BN + c * 32;
-          if (col0 >= p.N) break;
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + c * 32, r);
-          tmem_ld_fence(r);
-          if (!row_ok) continue;
           float v[32];
+          if (col0 + 32 <= p.N) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float x = KIND == 0 ? static_cast<float>(static_cast<int>(r[i])) : __uint_as_float(r[i]);
-            v[i] = x * sa * (col0 + i < p.N ? __ldg(p.sb + col0 + i) : 0.f);
+            for (int i = 0; i < 8; ++i) {
+              const float4 sb = __ldg(reinterpret_cast<const float4*>(p.sb + col0) + i);
+              const float sc[4] = {sb.x, sb.y, sb.z, sb.w};
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint32_t w = r[4 * i + q];
+                const float x = KIND == 0 ? static_cast<float>(static_cast<int>(w)) : __uint_as_float(w);
+                v[4 * i + q] = x * sa * sc[q];
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float x = KIND == 0 ? static_cast<float>(static_cast<int>(r[i])) : __uint_as_float(r[i]);
+              v[i] = x * sa * (col0 + i < p.N ? __ldg(p.sb + col0 + i) : 0.f);
+            }
           }
           store32(row, col0, v);
+        };
+        // TMEM reads run one chunk ahead of the stores; the accumulator goes back to the MMA warp as soon
+        // as its last chunk is in registers.
+        auto release_acc = [&]() {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_relaxed(tempty_bar(acc));
+        };
+        uint32_t ra[32], rb[32];
+        if (n_chunks > 0) tmem_ld_32x32(t_row, ra);
+#pragma unroll 1
+        for (int c = 0; c < n_chunks; c += 2) {
+          tmem_ld_fence(ra);
+          if (c + 1 < n_chunks) tmem_ld_32x32(t_row + (c + 1) * 32, rb);
+          else release_acc();
+          finish_chunk(c, ra);
+          if (c + 1 < n_chunks) {
+            tmem_ld_fence(rb);
+            if (c + 2 < n_chunks) tmem_ld_32x32(t_row + (c + 2) * 32, ra);
+            else release_acc();
+            finish_chunk(c + 1, rb);
+          }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        if (n_chunks <= 0) release_acc();
         acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -381,6 +427,89 @@ extern "C" int fmb_gemm8(const void* A, const void* B, void* D, int M, int N, in
 
 // Row quantiser. x: bf16 (dtype 0) or fp32 (1), [rows, cols] with pitch ldx. block > 0: fp8 scales per row and
 // `block` columns, scale shape [rows, ceil(cols / block)]; block == 0: one scale per row.
+// The same quantiser for rows whose width and pitch are multiples of 8 elements: every lane works on 8
+// consecutive elements (16-byte loads of bf16, 8-byte stores). Without blocks a warp makes two passes
+// over its row (maximum, then quantise); with 128-wide blocks a half warp owns one block and quantises
+// it from registers.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = unpack_bf16(w[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  } else {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+}
+template <int KIND>
+__device__ __forceinline__ uint2 quant8(const float (&v)[8], float inv) {
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float x = v[i] * inv;
+    uint32_t b;
+    if constexpr (KIND == 0) b = static_cast<uint32_t>(static_cast<uint8_t>(static_cast<int8_t>(fminf(fmaxf(rintf(x), -127.f), 127.f))));
+    else b = to_e4m3(x);
+    w[i >> 2] |= b << (8 * (i & 3));
+  }
+  return make_uint2(w[0], w[1]);
+}
+
+template <typename T, int KIND>
+__global__ void __launch_bounds__(256)
+quant_rows_vec_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale, long long rows, int cols,
+                      long long ldx, int block, int n_blocks) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const T* xr = x + row * ldx;
+  uint8_t* qr = q + row * cols;
+  constexpr float QMAX = KIND == 0 ? 127.f : 448.f;
+  if (block == 0) {
+    float amax = 0.f;
+    for (int c = lane * 8; c < cols; c += 256) {
+      float v[8];
+      load8(xr + c, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float s = fmaxf(amax, 1e-12f) / QMAX;
+    const float inv = 1.f / s;
+    if (lane == 0) scale[row] = s;
+    for (int c = lane * 8; c < cols; c += 256) {
+      float v[8];
+      load8(xr + c, v);
+      *reinterpret_cast<uint2*>(qr + c) = quant8<KIND>(v, inv);
+    }
+  } else {                                    // block == 128: 16 lanes x 8 elements
+    const int half = lane >> 4, sub = lane & 15;
+    for (int g0 = 0; g0 < n_blocks; g0 += 2) {
+      const int g = g0 + half, c = g * 128 + sub * 8;
+      const bool live = g < n_blocks && c < cols;
+      float v[8];
+      if (live) load8(xr + c, v);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      const float s = fmaxf(amax, 1e-12f) / QMAX;
+      if (g < n_blocks && sub == 0) scale[row * n_blocks + g] = s;
+      if (live) *reinterpret_cast<uint2*>(qr + c) = quant8<KIND>(v, 1.f / s);
+    }
+  }
+}
+
 extern "C" int fmb_quant_rows(const void* x, void* q, float* scale, long long rows, int cols, long long ldx, int dtype,
                               int kind, int block, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
@@ -388,9 +517,13 @@ extern "C" int fmb_quant_rows(const void* x, void* q, float* scale, long long ro
   const int n_blocks = block > 0 ? (cols + block - 1) / block : 1;
   const unsigned grid = static_cast<unsigned>((rows * 32 + 255) / 256);
   cudaError_t e;
+  const bool vec = cols % 8 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(q) & 7) == 0 && (block == 0 || block == 128);
 #define FMB_QR(T, KIND)                                                                                     \
-  e = launch_pdl(quant_rows_kernel<T, KIND>, dim3(grid), dim3(256), 0, stream, static_cast<const T*>(x),     \
-                 static_cast<uint8_t*>(q), scale, rows, cols, ldx, block, n_blocks)
+  e = vec ? launch_pdl(quant_rows_vec_kernel<T, KIND>, dim3(grid), dim3(256), 0, stream, static_cast<const T*>(x), \
+                       static_cast<uint8_t*>(q), scale, rows, cols, ldx, block, n_blocks)                    \
+          : launch_pdl(quant_rows_kernel<T, KIND>, dim3(grid), dim3(256), 0, stream, static_cast<const T*>(x), \
+                       static_cast<uint8_t*>(q), scale, rows, cols, ldx, block, n_blocks)
   if (dtype == FMB_BF16 && kind == 0) FMB_QR(__nv_bfloat16, 0);
   else if (dtype == FMB_BF16 && kind == 1) FMB_QR(__nv_bfloat16, 1);
   else if (dtype == FMB_F32 && kind == 0) FMB_QR(float, 0);
