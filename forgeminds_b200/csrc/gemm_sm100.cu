@@ -379,7 +379,10 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
                 tma_load_2d_pair(sA + j * (BK * 128), ma, bar, m_blk * BM + j * 64, a_y);
             }
             if constexpr (!B_MN) {
-              tma_load_3d_pair(sB, mb, bar, kb * BK, b_y, ti.zb);
+              // SwiGLU forward: the even CTA holds the 128 gate rows of the stacked weight, the odd CTA the
+              // 128 up rows, which makes accumulator columns [0,128) gate and [128,256) up
+              const int b_row = (BN == 256 && p.epi == 1) ? (cta_rank ? p.epi_h + n_blk * 128 : n_blk * 128) : b_y;
+              tma_load_3d_pair(sB, mb, bar, kb * BK, b_row, ti.zb);
             } else {
 #pragma unroll
               for (int j = 0; j < BN_CTA / 64; ++j)
@@ -485,34 +488,71 @@ gemm_bf16_kernel(const __grid_constant__ MapSet<PEER> tmA, const __grid_constant
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       if (BN == 256 && p.epi == 1) {
         // SwiGLU forward: accumulator columns [0,128) are gate, [128,256) up, of hidden units n_blk*128 ...
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t rg[32], ru[32];
-          tmem_ld_32x32(t_row + c * 32, rg);
-          tmem_ld_32x32(t_row + 128 + c * 32, ru);
-          tmem_ld_fence(rg);
-          tmem_ld_fence(ru);
-          if (!row_ok) continue;
+        const bool wide1 = wide_d && (reinterpret_cast<uintptr_t>(p.aux_out) & 31) == 0 && (p.ld_aux_out * 2) % 32 == 0 &&
+                           (p.epi_h * 2) % 32 == 0;
+        auto swiglu_chunk = [&](int c, const uint32_t (&rg)[32], const uint32_t (&ru)[32]) {
+          if (!row_ok) return;
           const int hc = n_blk * 128 + c * 32;                // hidden-unit column, < epi_h by construction
           __nv_bfloat16* gp = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<long long>(row) * p.ldd + hc;
           __nv_bfloat16* up = gp + p.epi_h;
           __nv_bfloat16* ap = reinterpret_cast<__nv_bfloat16*>(p.aux_out) + static_cast<long long>(row) * p.ld_aux_out + hc;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t og[4], ou[4], oa[4];
+          for (int i = 0; i < 2; ++i) {
+            uint32_t og[8], ou[8], oa[8];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < 8; ++q) {
               // round gate and up to bf16 first: the activation is what a separate kernel would compute from them
-              og[q] = pack_bf16(__uint_as_float(rg[8 * i + 2 * q]), __uint_as_float(rg[8 * i + 2 * q + 1]));
-              ou[q] = pack_bf16(__uint_as_float(ru[8 * i + 2 * q]), __uint_as_float(ru[8 * i + 2 * q + 1]));
+              og[q] = pack_bf16(__uint_as_float(rg[16 * i + 2 * q]), __uint_as_float(rg[16 * i + 2 * q + 1]));
+              ou[q] = pack_bf16(__uint_as_float(ru[16 * i + 2 * q]), __uint_as_float(ru[16 * i + 2 * q + 1]));
               const float2 g = unpack_bf16(og[q]), u = unpack_bf16(ou[q]);
               oa[q] = pack_bf16(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
             }
-            reinterpret_cast<uint4*>(gp)[i] = make_uint4(og[0], og[1], og[2], og[3]);
-            reinterpret_cast<uint4*>(up)[i] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
-            reinterpret_cast<uint4*>(ap)[i] = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+            if (wide1) {
+              st_global_v8(gp + 16 * i, og[0], og[1], og[2], og[3], og[4], og[5], og[6], og[7]);
+              st_global_v8(up + 16 * i, ou[0], ou[1], ou[2], ou[3], ou[4], ou[5], ou[6], ou[7]);
+              st_global_v8(ap + 16 * i, oa[0], oa[1], oa[2], oa[3], oa[4], oa[5], oa[6], oa[7]);
+            } else {
+              reinterpret_cast<uint4*>(gp)[2 * i] = make_uint4(og[0], og[1], og[2], og[3]);
+              reinterpret_cast<uint4*>(gp)[2 * i + 1] = make_uint4(og[4], og[5], og[6], og[7]);
+              reinterpret_cast<uint4*>(up)[2 * i] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+              reinterpret_cast<uint4*>(up)[2 * i + 1] = make_uint4(ou[4], ou[5], ou[6], ou[7]);
+              reinterpret_cast<uint4*>(ap)[2 * i] = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+              reinterpret_cast<uint4*>(ap)[2 * i + 1] = make_uint4(oa[4], oa[5], oa[6], oa[7]);
+            }
           }
+        };
+        auto release1 = [&]() {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (CTAS == 2) mbar_arrive_relaxed_cluster(mapa_shared(tempty_bar(acc), 0u));
+            else                     mbar_arrive_relaxed(tempty_bar(acc));
+          }
+        };
+        // gate / up chunk pairs are read one pair ahead of the stores
+        uint32_t ga[32], ua[32], gb[32], ub[32];
+        tmem_ld_32x32(t_row, ga);
+        tmem_ld_32x32(t_row + 128, ua);
+#pragma unroll 1
+        for (int c = 0; c < 4; c += 2) {
+          tmem_ld_fence(ga);
+          tmem_ld_fence(ua);
+          tmem_ld_32x32(t_row + (c + 1) * 32, gb);
+          tmem_ld_32x32(t_row + 128 + (c + 1) * 32, ub);
+          swiglu_chunk(c, ga, ua);
+          tmem_ld_fence(gb);
+          tmem_ld_fence(ub);
+          if (c + 2 < 4) {
+            tmem_ld_32x32(t_row + (c + 2) * 32, ga);
+            tmem_ld_32x32(t_row + 128 + (c + 2) * 32, ua);
+          } else {
+            release1();
+          }
+          swiglu_chunk(c + 1, gb, ub);
         }
+        acc ^= 1u;
+        if (acc == 0) acc_phase ^= 1u;
+        continue;
       } else if (p.epi == 2) {
         // SwiGLU backward: v = d(act); d(gate) = v*u*s*(1+g*(1-s)), d(up) = v*g*s with s = sigmoid(g)
 #pragma unroll 1
@@ -883,8 +923,7 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
   const bool can_split = allow_split && d_f32 && (C == nullptr || C == D);
   // CTA pairs (256-row tiles over two SMs) serve plain products; FMB_GEMM_PAIR=0 turns them off.
   static const bool pair_env = [] { const char* v = getenv("FMB_GEMM_PAIR"); return v == nullptr || v[0] != '0'; }();
-  const bool pair_ok = pair_env && (ps == nullptr || ps->gather == 0) && gs.mode == 0 && (es == nullptr || es->epi != 1) &&
-                       sms % 2 == 0;
+  const bool pair_ok = pair_env && (ps == nullptr || ps->gather == 0) && gs.mode == 0 && sms % 2 == 0;
 
   // Pick the N tile, the split count and the CTAs per tile that fill the machine best.
   int best_bn = 256, best_split = 1, best_ctas = 1;
