@@ -581,6 +581,11 @@ class Trainer:
         import torch.distributed.checkpoint as dcp
         root, path = self._paths(self.step)
         os.makedirs(path, exist_ok=True)
+        if getattr(self.raw, "_fm_tp", None) is not None and self.ctx.pc.tp > 1:
+            # the fused tensor-parallel blocks hold plain, already sharded tensors under the same keys on
+            # every rank, which torch.distributed.checkpoint takes for replicas and writes once
+            log(self.ctx, "[forgeminds_b200] warning: a checkpoint of fused tensor-parallel blocks keeps one rank's "
+                          "shards only; run with parallel.fused_comm=False (DTensor) when the run must be resumed")
         if self.use_ds:
             self.engine.save_checkpoint(root, tag=f"step_{self.step:07d}")
         else:
