@@ -1045,9 +1045,12 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
   CUtensorMap td;
   memset(&td, 0, sizeof(td));
   if (dtma_env && d_f32 && gs.mode == 0 && ps == nullptr && p.epi == 0) {
-    if (splits > 1 || (C == D && beta == 1.f)) { p.d_tma = 1; p.C = nullptr; p.atomic = 0; }
-    else if (C == nullptr || beta == 0.f) p.d_tma = 2;
-    if (p.d_tma && !make_tmap_2d(&td, D, M, N, ldd, 32, 32, 4, TmapSwizzle::B128)) return -5;
+    const int want = (splits > 1 || (C == D && beta == 1.f)) ? 1 : (C == nullptr || beta == 0.f) ? 2 : 0;
+    // an output that the driver refuses to describe (unusual pitch or extent) keeps the register path
+    if (want && make_tmap_2d(&td, D, M, N, ldd, 32, 32, 4, TmapSwizzle::B128)) {
+      p.d_tma = want;
+      if (want == 1) { p.C = nullptr; p.atomic = 0; }
+    }
   }
 
   MapSet<true> ta, tb;
