@@ -134,3 +134,40 @@ def test_chunk_tables_cover_the_shard_once_with_the_right_decay(two_ranks, monke
         lo_all = [st.shard_range(b, r) for b in st.buckets]
         mine = sum(n for _, n in lo_all)
         assert int(seen.sum()) <= mine                # nothing outside this rank's shards
+
+
+def _gather_plan(rank, world, rows_per_src, grid):
+    """Python statement of the row schedule of the GEMM's gather warps (csrc/gemm_sm100.cu, gather_rows):
+    the remote rows form one list, nearest rank first; CTA b takes rows b, b + grid, ... two at a time."""
+    rows_total = (world - 1) * rows_per_src
+    plan = []                                            # (cta, iteration, source rank, row of the full operand)
+    for cta in range(grid):
+        it = 0
+        q = cta
+        while q < rows_total:
+            for qq in (q, q + grid):
+                if qq < rows_total:
+                    step = qq // rows_per_src + 1
+                    src = (rank + step) % world
+                    plan.append((cta, it, src, src * rows_per_src + (qq - (step - 1) * rows_per_src)))
+            q += 2 * grid
+            it += 1
+    return plan
+
+
+@pytest.mark.parametrize("world,rank,rows_per_src,grid", [(2, 0, 256, 148), (8, 3, 1024, 148), (4, 3, 128, 37), (8, 7, 384, 5)])
+def test_gather_schedule_copies_every_remote_row_once_nearest_rank_first(world, rank, rows_per_src, grid):
+    plan = _gather_plan(rank, world, rows_per_src, grid)
+    rows = [r for *_, r in plan]
+    own = set(range(rank * rows_per_src, (rank + 1) * rows_per_src))
+    assert len(rows) == len(set(rows)) == (world - 1) * rows_per_src
+    assert not own & set(rows)
+    # every 128-row block of a remote shard receives exactly 128 arrivals (what the TMA producer waits for)
+    per_block = {}
+    for r in rows:
+        per_block[r >> 7] = per_block.get(r >> 7, 0) + 1
+    assert set(per_block.values()) == {128}
+    # inside one CTA the sources come in the order rank+1, rank+2, ... (the order the row tiles are computed in)
+    for cta in range(min(grid, 4)):
+        dist = [(src - rank) % world for c, _, src, _ in plan if c == cta]
+        assert dist == sorted(dist)
