@@ -50,8 +50,21 @@ def _fn():
 
 
 # ------------------------------------------------------------------------------ norms
+def _use_ops() -> bool:
+    """Whether the public functions go through the ``torch.library`` forms (``kernels/_ops.py``)."""
+    from . import _ops
+    return use_custom_ops() or _ops.env_default()
+
+
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
     """``x * rsqrt(mean(x^2) + eps) * w`` over the last dimension."""
+    if _use_ops():
+        from . import _ops
+        return _ops.rms_norm_op(x, w, float(eps))
+    return _rms_norm_eager(x, w, eps)
+
+
+def _rms_norm_eager(x, w, eps=1e-6):
     if x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384 and fast_ok(x, w):
         return _fn().rms_norm(x, w, eps)
     return _ref.rms_norm(x, w, eps)
@@ -59,6 +72,13 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6) -> torch.Tenso
 
 def add_rms_norm(x: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, eps: float = 1e-6):
     """Residual add and norm in one pass: returns ``(x + delta, rms_norm(x + delta, w))``."""
+    if _use_ops() and x.shape == delta.shape:
+        from . import _ops
+        return _ops.add_rms_norm_op(x, delta, w, float(eps))
+    return _add_rms_norm_eager(x, delta, w, eps)
+
+
+def _add_rms_norm_eager(x, delta, w, eps=1e-6):
     if x.shape == delta.shape and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384 and fast_ok(x, delta, w):
         return _fn().add_rms_norm(x, delta, w, eps)
     return _ref.add_rms_norm(x, delta, w, eps)
@@ -102,6 +122,13 @@ def qk_norm_rope(x: torch.Tensor, w: torch.Tensor, cos: torch.Tensor, sin: torch
 # ------------------------------------------------------------------------------ SwiGLU
 def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """``silu(gate) * up``"""
+    if _use_ops() and gate.shape == up.shape and gate.dtype == up.dtype:
+        from . import _ops
+        return _ops.swiglu_op(gate, up)
+    return _swiglu_eager(gate, up)
+
+
+def _swiglu_eager(gate, up):
     if gate.shape == up.shape and gate.shape[-1] % 8 == 0 and gate.dtype == up.dtype and fast_ok(gate, up):
         return _fn().swiglu(gate, up)
     return _ref.swiglu(gate, up)
