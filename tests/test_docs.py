@@ -6,7 +6,8 @@ import re
 import forgeminds_b200 as fm
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-DOCS = [os.path.join(ROOT, "docs", "documentation.md"), os.path.join(ROOT, "README.md")]
+DOCS = [os.path.join(ROOT, "docs", "documentation.md"), os.path.join(ROOT, "README.md"),
+        os.path.join(ROOT, "docs", "performance.md"), os.path.join(ROOT, "docs", "offload.md")]
 
 
 def _text(path):
@@ -53,6 +54,17 @@ def test_every_config_field_is_documented():
 
 def test_documented_cli_tools_exist():
     from forgeminds_b200.cli import __main__ as cli
-    text = _text(DOCS[0])
-    for tool in re.findall(r"python -m forgeminds_b200\.cli (\w+)", text):
-        assert tool in cli.TOOLS, tool
+    for path in DOCS:
+        for tool in re.findall(r"(?:python|torchrun[^`\n]*) -m forgeminds_b200\.cli (\w+)", _text(path)):
+            assert tool in cli.TOOLS, (path, tool)
+
+
+def test_profiles_and_guides_name_existing_files():
+    """Paths written as `dir/file.ext` in the guides and profile summaries exist in the tree."""
+    docs = DOCS + [os.path.join(ROOT, "profiles", f) for f in sorted(os.listdir(os.path.join(ROOT, "profiles")))]
+    missing = []
+    for path in docs:
+        for ref in re.findall(r"`((?:forgeminds_b200|tests|profiles|docs|examples)/[A-Za-z0-9_./-]+\.(?:py|md|cu|cuh|cpp|h))`", _text(path)):
+            if not os.path.exists(os.path.join(ROOT, ref)):
+                missing.append((os.path.basename(path), ref))
+    assert not missing, missing
