@@ -84,11 +84,17 @@ class Muon(torch.optim.Optimizer):
             super().add_param_group(g)
 
     @torch.no_grad()
-    def step(self, closure=None):
+    def step(self, closure=None, ctl: "Tensor | None" = None):
+        """``ctl`` (optional, 2 floats on the parameters' device: clip coefficient, apply flag) lets a
+        training loop enqueue the step before it has read the gradient norm on the host: every gradient
+        is multiplied by ``ctl[0]`` and, when ``ctl[1] < 0.5``, parameters, momentum buffers and AdamW
+        moments are left exactly as they were (a non-finite gradient cannot leak through a zero
+        weight, so the old values are selected, not blended)."""
         loss = None
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        self._ctl = None if ctl is None else (ctl[0], ctl[1] > 0.5)
         pg = getattr(self, "_dist_group", None)
         live = dist.is_available() and dist.is_initialized()
         world = dist.get_world_size(pg) if live else 1
@@ -98,7 +104,31 @@ class Muon(torch.optim.Optimizer):
                 self._muon(group, rank, world, pg)
             else:
                 self._adamw(group)
+        self._ctl = None
         return loss
+
+    @torch.no_grad()
+    def init_state(self) -> None:
+        """Create the (zero) state of every trainable parameter that has none yet, so that a state dict
+        taken before the first step has the entries a checkpoint loads into."""
+        for group in self.param_groups:
+            for p in group["params"]:
+                if not p.requires_grad or self.state.get(p):
+                    continue
+                if group["use_muon"]:
+                    self.state[p]["momentum_buffer"] = torch.zeros_like(p)
+                else:
+                    self.state[p].update(exp_avg=torch.zeros_like(p), exp_avg_sq=torch.zeros_like(p), step=0)
+
+    def _gated(self, new: Tensor, old: Tensor) -> Tensor:
+        """``new`` when the step applies, ``old`` when the device-side flag says skip."""
+        ctl = getattr(self, "_ctl", None)
+        return new if ctl is None else torch.where(ctl[1], new, old)
+
+    def _grad_of(self, p: Tensor) -> Tensor:
+        g = p.grad if p.grad is not None else torch.zeros_like(p)
+        ctl = getattr(self, "_ctl", None)
+        return g if ctl is None else g * ctl[0].to(g.dtype)
 
     # ------------------------------------------------------------------ Muon rule
     def _muon(self, group, rank, world, pg) -> None:
@@ -120,8 +150,8 @@ class Muon(torch.optim.Optimizer):
                 if "momentum_buffer" not in st:
                     st["momentum_buffer"] = torch.zeros_like(p)
                 buf = st["momentum_buffer"]
-                g = p.grad if p.grad is not None else torch.zeros_like(p)
-                buf.lerp_(g, 1 - mu)
+                g = self._grad_of(p)
+                buf.copy_(self._gated(buf.lerp(g, 1 - mu), buf))
                 direction = g.lerp(buf, mu) if group["nesterov"] else buf
                 stack.append(direction.reshape(shape2d).to(torch.float32))
             G = torch.stack(stack)
@@ -136,8 +166,8 @@ class Muon(torch.optim.Optimizer):
                 ortho = newton_schulz(G, steps=group["ns_steps"], dtype=ns_dtype)
             gain = max(1.0, shape2d[0] / shape2d[1]) ** 0.5
             for i, p in enumerate(members):
-                p.mul_(1 - lr * wd)
-                p.add_(ortho[i].reshape(p.shape).to(p.dtype), alpha=-lr * gain)
+                moved = p * (1 - lr * wd) - ortho[i].reshape(p.shape).to(p.dtype) * (lr * gain)
+                p.copy_(self._gated(moved, p))
 
     # ------------------------------------------------------------------ AdamW rule
     def _adamw(self, group) -> None:
@@ -147,16 +177,18 @@ class Muon(torch.optim.Optimizer):
         for p in group["params"]:
             if not p.requires_grad:
                 continue
-            g = p.grad if p.grad is not None else torch.zeros_like(p)
+            g = self._grad_of(p)
             st = self.state[p]
             if "exp_avg" not in st:
                 st["exp_avg"] = torch.zeros_like(p)
                 st["exp_avg_sq"] = torch.zeros_like(p)
                 st["step"] = 0
             st["step"] += 1
-            st["exp_avg"].lerp_(g, 1 - b1)
-            st["exp_avg_sq"].lerp_(g.square(), 1 - b2)
-            m_hat = st["exp_avg"] / (1 - b1 ** st["step"])
-            v_hat = st["exp_avg_sq"] / (1 - b2 ** st["step"])
-            p.mul_(1 - lr * wd)
-            p.add_(m_hat / (v_hat.sqrt() + eps), alpha=-lr)
+            m = st["exp_avg"].lerp(g, 1 - b1)
+            v = st["exp_avg_sq"].lerp(g.square(), 1 - b2)
+            st["exp_avg"].copy_(self._gated(m, st["exp_avg"]))
+            st["exp_avg_sq"].copy_(self._gated(v, st["exp_avg_sq"]))
+            m_hat = m / (1 - b1 ** st["step"])
+            v_hat = v / (1 - b2 ** st["step"])
+            moved = p * (1 - lr * wd) - m_hat / (v_hat.sqrt() + eps) * lr
+            p.copy_(self._gated(moved, p))

@@ -1,108 +1,125 @@
-"""Composable blocks backed by the fused kernels: :class:`RMSNorm` and :class:`SwiGLU`.
+"""Building blocks for user architectures that run on the fused kernels: :class:`RMSNorm`, :class:`SwiGLU`.
 
-Both are ordinary ``nn.Module``s usable in any architecture; on a B200 they call the CUDA kernels,
-elsewhere the equivalent PyTorch expressions. ``RMSNorm`` keeps ``torch.nn.RMSNorm``'s parameter
-name and shape; ``SwiGLU(split=True)`` holds one ``gate_up`` projection instead of ``w1``/``w3``.
-Interface as in the reference's ``forgemind/nn.py:82-217``.
+Drop-in ``nn.Module``s: on a B200 their forward goes through :mod:`forgeminds_b200.kernels` (hand-written
+sm_100a kernels, fp32 accumulation, one rounding at the store), anywhere else through the PyTorch
+statement of the same arithmetic. State-dict contract (the reference's ``forgemind/nn.py:82-217``):
+``RMSNorm`` has the single parameter ``weight [dim]`` of ``torch.nn.RMSNorm`` and loads from / into one;
+``SwiGLU`` has ``w1, w3, w2`` (``nn.Linear`` layout) or, when ``split=True``, ``gate_up, w2`` with
+``gate_up.weight = cat(w1.weight, w3.weight)``.
 """
 from __future__ import annotations
+
+from typing import Optional
 
 import torch
 import torch.nn as nn
 
-from .kernels import add_rms_norm, rms_norm, swiglu, swiglu_split
+from . import kernels as K
 
 __all__ = ["RMSNorm", "SwiGLU"]
 
 
+def _positive(name: str, value) -> int:
+    n = int(value)
+    if n < 1:
+        raise ValueError(f"{name} must be a positive integer, got {value!r}")
+    return n
+
+
 class RMSNorm(nn.Module):
-    """``x * rsqrt(mean(x^2) + eps) * weight`` over the last dimension."""
+    """Root-mean-square normalisation of the last dimension, ``y = x / sqrt(mean(x^2) + eps) * weight``.
+
+    ``forward_with_residual(x, r)`` fuses the residual add that usually precedes a pre-norm block: it
+    returns ``(norm(x + r), x + r)`` from a single pass over the row.
+    """
 
     def __init__(self, dim: int, eps: float = 1e-6, elementwise_affine: bool = True, device=None, dtype=None):
         super().__init__()
-        self.dim = int(dim)
-        if self.dim <= 0:
-            raise ValueError(f"RMSNorm needs dim > 0, got {dim}")
+        self.dim = _positive("RMSNorm dim", dim)
         self.eps = float(eps)
         self.elementwise_affine = bool(elementwise_affine)
-        if self.elementwise_affine:
-            self.weight = nn.Parameter(torch.ones(self.dim, device=device, dtype=dtype))
-        else:
-            self.register_parameter("weight", None)
+        gain = nn.Parameter(torch.ones(self.dim, device=device, dtype=dtype)) if self.elementwise_affine else None
+        self.register_parameter("weight", gain)
 
     def extra_repr(self) -> str:
-        return f"{self.dim}, eps={self.eps}, elementwise_affine={self.elementwise_affine}"
+        affine = "" if self.elementwise_affine else ", no weight"
+        return f"dim={self.dim}, eps={self.eps:g}{affine}"
 
-    def _scale(self, x):
-        if self.weight is None:
-            return torch.ones(self.dim, device=x.device, dtype=x.dtype)
-        return self.weight if self.weight.dtype == x.dtype else self.weight.to(x.dtype)
-
-    def _check(self, x) -> None:
+    def _gain_for(self, x: torch.Tensor) -> torch.Tensor:
         if x.shape[-1] != self.dim:
-            raise ValueError(f"RMSNorm({self.dim}) got last dim {x.shape[-1]}; the norm runs over the last "
-                             f"dimension of [..., {self.dim}]")
+            raise ValueError(f"input of shape {tuple(x.shape)} cannot be normalised by RMSNorm(dim={self.dim}): "
+                             "the last dimension must equal dim")
+        if self.weight is None:
+            return x.new_ones(self.dim)
+        return self.weight.to(x.dtype)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        self._check(x)
-        return rms_norm(x, self._scale(x), self.eps)
+        return K.rms_norm(x, self._gain_for(x), self.eps)
 
-    def forward_with_residual(self, x: torch.Tensor, residual: torch.Tensor | None = None):
-        """``(normed, x + residual)`` with the sum written once and normalised in the same pass."""
-        self._check(x)
+    def forward_with_residual(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None):
+        gain = self._gain_for(x)
         if residual is None:
-            residual = torch.zeros_like(x)
-        elif residual.shape != x.shape:
-            raise ValueError(f"residual shape {tuple(residual.shape)} does not match x {tuple(x.shape)}")
-        summed, normed = add_rms_norm(x, residual, self._scale(x), self.eps)
-        return normed, summed
+            return K.rms_norm(x, gain, self.eps), x
+        if tuple(residual.shape) != tuple(x.shape):
+            raise ValueError(f"residual {tuple(residual.shape)} and input {tuple(x.shape)} must have the same shape")
+        total, normed = K.add_rms_norm(x, residual, gain, self.eps)
+        return normed, total
 
 
 class SwiGLU(nn.Module):
-    """``w2(silu(w1 x) * w3 x)``; with ``split=True`` the gate and up projections are one GEMM."""
+    """Gated MLP ``w2(silu(w1 x) * (w3 x))``.
 
-    def __init__(self, dim: int, hidden: int | None = None, bias: bool = False, split: bool = False,
+    ``split=True`` keeps gate and up as the two halves of one ``gate_up`` projection, so the block is
+    two GEMMs instead of three and the activation reads one buffer. :meth:`to_split` converts an
+    existing module (in place, or as a copy) without changing what it computes.
+    """
+
+    def __init__(self, dim: int, hidden: Optional[int] = None, bias: bool = False, split: bool = False,
                  device=None, dtype=None):
         super().__init__()
-        self.dim = int(dim)
-        self.hidden = int(hidden if hidden is not None else 4 * dim)
-        if self.dim <= 0 or self.hidden <= 0:
-            raise ValueError(f"SwiGLU needs dim > 0 and hidden > 0, got dim={dim}, hidden={hidden}")
+        self.dim = _positive("SwiGLU dim", dim)
+        self.hidden = _positive("SwiGLU hidden", 4 * self.dim if hidden is None else hidden)
         self.split = bool(split)
-        kw = dict(bias=bias, device=device, dtype=dtype)
+        make = lambda fan_in, fan_out: nn.Linear(fan_in, fan_out, bias=bias, device=device, dtype=dtype)  # noqa: E731
         if self.split:
-            self.gate_up = nn.Linear(self.dim, 2 * self.hidden, **kw)
+            self.gate_up = make(self.dim, 2 * self.hidden)
         else:
-            self.w1 = nn.Linear(self.dim, self.hidden, **kw)
-            self.w3 = nn.Linear(self.dim, self.hidden, **kw)
-        self.w2 = nn.Linear(self.hidden, self.dim, **kw)
+            self.w1, self.w3 = make(self.dim, self.hidden), make(self.dim, self.hidden)
+        self.w2 = make(self.hidden, self.dim)
 
     def extra_repr(self) -> str:
-        return f"{self.dim} -> {self.hidden} -> {self.dim}, split={self.split}"
+        return f"dim={self.dim}, hidden={self.hidden}, layout={'gate_up|w2' if self.split else 'w1,w3|w2'}"
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.split:
-            return self.w2(swiglu_split(self.gate_up(x)))
-        return self.w2(swiglu(self.w1(x), self.w3(x)))
+            act = K.swiglu_split(self.gate_up(x))
+        else:
+            act = K.swiglu(self.w1(x), self.w3(x))
+        return self.w2(act)
 
     @torch.no_grad()
     def to_split(self, inplace: bool = True) -> "SwiGLU":
-        """Concatenate ``w1|w3`` into ``gate_up`` (same function, renamed parameters)."""
         if self.split:
             return self
-        if (self.w1.bias is None) != (self.w3.bias is None):
-            raise ValueError("to_split() needs both projections to have a bias, or neither")
-        target = self
+        gate, up = self.w1, self.w3
+        with_bias = gate.bias is not None
+        if with_bias != (up.bias is not None):
+            raise ValueError("cannot merge w1 and w3: one has a bias and the other does not")
+        ref = gate.weight
+        merged = SwiGLU(self.dim, self.hidden, bias=with_bias, split=True, device=ref.device, dtype=ref.dtype)
+        merged.gate_up.weight[:self.hidden] = gate.weight
+        merged.gate_up.weight[self.hidden:] = up.weight
+        if with_bias:
+            merged.gate_up.bias[:self.hidden] = gate.bias
+            merged.gate_up.bias[self.hidden:] = up.bias
         if not inplace:
-            target = SwiGLU(self.dim, self.hidden, bias=self.w2.bias is not None, split=False,
-                            device=self.w2.weight.device, dtype=self.w2.weight.dtype)
-            target.w2.load_state_dict(self.w2.state_dict())
-        fused = nn.Linear(self.dim, 2 * self.hidden, bias=self.w1.bias is not None,
-                          device=self.w1.weight.device, dtype=self.w1.weight.dtype)
-        fused.weight.copy_(torch.cat([self.w1.weight, self.w3.weight], dim=0))
-        if fused.bias is not None:
-            fused.bias.copy_(torch.cat([self.w1.bias, self.w3.bias], dim=0))
-        del target.w1, target.w3
-        target.gate_up = fused
-        target.split = True
-        return target
+            has_out_bias = self.w2.bias is not None
+            if has_out_bias != with_bias:
+                merged.w2 = nn.Linear(self.hidden, self.dim, bias=has_out_bias, device=ref.device, dtype=ref.dtype)
+            merged.w2.load_state_dict(self.w2.state_dict())
+            merged.train(self.training)
+            return merged
+        self.gate_up = merged.gate_up
+        del self.w1, self.w3
+        self.split = True
+        return self

@@ -45,27 +45,83 @@ def _round_up(n: int, m: int) -> int:
     return (n + m - 1) // m * m
 
 
+@dataclass
+class DpLayout:
+    """Place of this rank in the data-parallel group of its (pipeline stage, tensor-parallel rank).
+
+    The group has ``replicas * shard_world`` ranks, numbered ``replica * shard_world + shard_rank``
+    (the mesh order of ``forgemind/distributed.py:146-169``). Gradients are averaged over all of
+    them; optimizer state is split over the ``shard_world`` ranks of one replica and repeated in
+    every replica (HSDP), so ``replicas == 1`` is plain sharded data parallelism and
+    ``shard_world == 1`` plain replication."""
+    rank: int = 0
+    world: int = 1
+    shard_rank: int = 0
+    shard_world: int = 1
+    shard_group: object = None          # process group of the ranks of this replica (None: the whole group)
+
+    @property
+    def replicas(self) -> int:
+        return self.world // self.shard_world
+
+    @property
+    def replica(self) -> int:
+        return self.rank // self.shard_world
+
+    def replica_peers(self) -> range:
+        """Group ranks that hold the other shards of this replica (they receive this rank's weights)."""
+        lo = self.replica * self.shard_world
+        return range(lo, lo + self.shard_world)
+
+    @classmethod
+    def of(cls, ctx) -> "DpLayout":
+        pc = ctx.pc
+        s = max(1, int(pc.dp_shard))
+        if ctx.dp_world <= 1:
+            return cls()
+        if s == 1:                      # pure replication: the optimizer state is still split (ZeRO-1 style)
+            return cls(rank=ctx.dp_rank, world=ctx.dp_world, shard_rank=ctx.dp_rank, shard_world=ctx.dp_world,
+                       shard_group=ctx.dp_group)
+        grp = ctx.dp_group if pc.dp_replicate == 1 else ctx.shard_group
+        return cls(rank=ctx.dp_rank, world=ctx.dp_world, shard_rank=ctx.shard_rank, shard_world=s, shard_group=grp)
+
+
 class FlatParamStore:
-    def __init__(self, model, device, shard_world: int = 1, block_attr: str = "layers", symm=None):
+    def __init__(self, model, device, shard_world: int = 1, block_attr: str = "layers", symm=None,
+                 layout: "DpLayout | None" = None, apart=None):
         """``symm`` (a :class:`~forgeminds_b200.parallel.symm.SymmGroup`) puts the gradient and the bf16
         buffers into symmetric memory so that the peer-memory kernels can read / write them on every
-        rank; the buckets are then padded so that they split evenly over the group."""
+        rank; the buckets are then padded so that they split evenly over the shard ranks of ``layout``
+        (default: every rank of the group holds a different shard).
+
+        ``apart(param) -> bool`` moves matching parameters out of their block's bucket into the last
+        bucket (``rest``). Tensor parallelism uses it for parameters that are replicated over the
+        tensor-parallel ranks (block norms): the ``rest`` bucket then holds exactly the replicated
+        part of the model, whose share of the gradient norm is counted once, not once per rank."""
         self.device = torch.device(device)
         self.symm = symm
-        self.shard_world = max(1, int(symm.world if symm is not None else shard_world))
+        if layout is None:
+            w = max(1, int(symm.world if symm is not None else shard_world))
+            layout = DpLayout(rank=symm.rank if symm is not None else 0, world=w,
+                              shard_rank=symm.rank if symm is not None else 0, shard_world=w,
+                              shard_group=symm.group if symm is not None else None)
+        self.layout = layout
+        self.shard_world = layout.shard_world
         groups: list = []
         seen = set()
         blocks = getattr(model, block_attr, None)
         block_list = list(blocks.values()) if hasattr(blocks, "values") else list(blocks or [])
-        in_block = set()
+        moved = []
         for i, blk in enumerate(block_list):
             ps = [p for p in blk.parameters() if p.requires_grad and id(p) not in seen]
             for p in ps:
                 seen.add(id(p))
-                in_block.add(id(p))
+            if apart is not None:
+                moved += [p for p in ps if apart(p)]
+                ps = [p for p in ps if not apart(p)]
             if ps:
                 groups.append((f"block{i}", ps))
-        rest = [p for p in model.parameters() if p.requires_grad and id(p) not in seen]
+        rest = moved + [p for p in model.parameters() if p.requires_grad and id(p) not in seen]
         if rest:
             groups.append(("rest", rest))
         self.buckets: list = []
@@ -128,13 +184,13 @@ class FlatParamStore:
         updates its own part of every bucket (the bf16 working weights are complete everywhere); call
         this before reading parameters as fp32: checkpoints, ``state_dict``, evaluation on the
         PyTorch path."""
-        sg = self.symm
-        if sg is None or sg.world == 1:
+        lay = self.layout
+        if self.symm is None or lay.shard_world == 1:
             return
         for b in self.buckets:
-            lo, n = self.shard_range(b, sg.rank)
+            lo, n = self.shard_range(b, lay.shard_rank)
             dist.all_gather_into_tensor(self.bucket_view(self.master, b), self.master[lo:lo + n].clone(),
-                                        group=sg.group)
+                                        group=lay.shard_group)
 
     def rebind(self) -> None:
         """Re-attach ``.grad`` views (something set them to ``None``)."""
@@ -271,9 +327,10 @@ class BucketReducer:
 
     ``launch(bucket)`` is called when a block has finished its last backward of the step (module
     backward hook): the reduction of that bucket then overlaps the backward of the earlier blocks.
-    ``finish()`` makes the compute stream wait for all of them. Uses NCCL/Gloo ``all_reduce``; the
-    peer-memory kernels of :mod:`forgeminds_b200.parallel.symm` replace it when symmetric buffers
-    are available.
+    ``finish()`` makes the compute stream wait for all of them. Uses NCCL/Gloo ``all_reduce``. Inside
+    one NVSwitch domain the trainer uses :class:`forgeminds_b200.parallel.peer.PeerReducer` (same
+    interface, pull reduce-scatter over symmetric memory) instead; this class serves larger groups,
+    CPU runs and ``fused_comm=False``.
     """
 
     def __init__(self, store: FlatParamStore, group, world: int):

@@ -6,10 +6,10 @@ Two implementations live behind each entry point:
   and DTensor tensor parallelism, exactly what the reference wires up in
   ``forgemind/parallel/native.py:21-113``. It is what runs on CPU/Gloo and what the fused paths are
   measured against;
-* the **sm_100a engine** (:mod:`forgeminds_b200.parallel.sharded`, ``.tp``): flat fp32 master shards
-  with bf16 working weights, gradient reduction, clipping and AdamW fused into peer-memory kernels.
-  ``apply_fsdp`` / ``apply_ddp`` pick it when the model runs on the native kernels and
-  ``ParallelConfig.fused_comm`` is on.
+* the **sm_100a engine** (:mod:`forgeminds_b200.engine.native` with :mod:`forgeminds_b200.parallel.flat`,
+  ``.peer`` and ``.tp``): a flat fp32 master store with bf16 working weights, gradient reduction,
+  clipping and AdamW in peer-memory kernels, tensor parallelism fused with its collectives. The
+  trainer selects it; the functions here are what everything else runs on.
 """
 from __future__ import annotations
 
@@ -97,14 +97,17 @@ def apply_fsdp(model, ctx: DistContext, bf16=True, cpu_offload=False, reshard=Tr
 
 def apply_ddp(model, ctx: DistContext):
     """``DistributedDataParallel`` over the flattened data-parallel group; rank-local experts are
-    kept out of the reducer when expert parallelism is on."""
+    kept out of the reducer when expert parallelism is on. Buffers are not re-broadcast at every
+    forward: the only buffers of the models here are RoPE tables, which every rank computes itself, and
+    an in-place broadcast would invalidate the graphs of the micro-batches a pipeline schedule keeps
+    in flight."""
     from torch.nn.parallel import DistributedDataParallel as DDP
     if ctx.pc.ep > 1:
         skip = [n for n, _ in model.named_parameters() if ".experts." in n]
         DDP._set_params_and_buffers_to_ignore_for_model(model, skip)
     unused = has_moe(model) and ctx.pc.ep == 1 and not ctx.pc.ddp_static_graph
     return DDP(model, device_ids=[ctx.local_rank] if ctx.device.type == "cuda" else None,
-               process_group=ctx.dp_group, gradient_as_bucket_view=True,
+               process_group=ctx.dp_group, gradient_as_bucket_view=True, broadcast_buffers=False,
                static_graph=ctx.pc.ddp_static_graph, find_unused_parameters=unused)
 
 

@@ -17,6 +17,16 @@ With ``W`` ranks on one NVSwitch domain the step after the last backward is thre
 Weights stay resident in bf16 on every GPU (a 354 M-parameter model is 0.7 GB of 180 GB), so the
 forward needs no all-gather at all; the reference's FSDP2 gathers every block's parameters before
 its forward and again before its backward (``forgemind/parallel/native.py:52-68``).
+
+Hybrid sharding (``dp_replicate x dp_shard``, the reference's 2-D ``fully_shard`` mesh,
+``forgemind/parallel/native.py:54-57``) uses the same three kernels on the whole data-parallel group:
+rank ``(r, s)`` pulls shard ``s`` of every bucket from all ``R * S`` buffers (reduce-scatter inside
+the shard group and the sum over the replicas are one pass, fixed rank order), keeps the moments of
+shard ``s`` only, and pushes the new bf16 weights to the ``S`` ranks of its own replica.
+
+With pipeline or tensor parallelism every (stage, tensor rank) coordinate runs this over its own
+data-parallel group; the end-of-step scalars are exchanged over a second, world-wide group so that
+the norm covers the whole model (see :class:`PeerAdamW.reduce_step`).
 """
 from __future__ import annotations
 
@@ -37,20 +47,26 @@ class PeerReducer:
             raise ValueError("PeerReducer needs a FlatParamStore built on a SymmGroup")
         self.store, self.sg = store, store.symm
         self.world = self.sg.world
+        self.layout = store.layout
         self.stream = torch.cuda.Stream(device=store.device, priority=-1)
         self.partials = torch.zeros(len(store.buckets) * BLOCKS_PER_BUCKET, dtype=torch.float32, device=store.device)
         self.slot0 = self.sg.reserve_slots(len(store.buckets))
         self._index = {b.name: i for i, b in enumerate(store.buckets)}
         self._launched: list = []
         self.enabled = True
+        self.local_only = False      # timing diagnostics: same kernels, this rank's memory only (see detach)
 
     def _reduce(self, b: Bucket) -> None:
         C = ops.require()
         st, sg = self.store, self.sg
         i = self._index[b.name]
-        lo, n = st.shard_range(b, sg.rank)
+        lo, n = st.shard_range(b, self.layout.shard_rank)
         part = self.partials[i * BLOCKS_PER_BUCKET:(i + 1) * BLOCKS_PER_BUCKET]
         slot = self.slot0 + i
+        if self.local_only:
+            C.comm_rs_reduce([st.grad_symm.ptrs[sg.rank]], lo, n, 1.0 / self.world, part, [sg.flags.ptrs[sg.rank]], slot,
+                             sg.next_epoch(slot), 0, sg.timeout_ms, sg.status)
+            return
         C.comm_rs_reduce(st.grad_symm.ptrs, lo, n, 1.0 / self.world, part, sg.flags.ptrs, slot, sg.next_epoch(slot),
                          sg.rank, sg.timeout_ms, sg.status)
 
@@ -73,34 +89,49 @@ class PeerReducer:
             if b.name not in done:
                 self._reduce(b)
 
+    def weigh(self, factors: dict) -> None:
+        """Multiply the sum-of-squares partials of the named buckets (``{bucket name: factor}``, ``"*"`` for
+        all others). Used when several ranks hold the same reduced values (replicas of a hybrid-sharded
+        group, parameters replicated over tensor-parallel ranks) and the norm is then summed over all
+        of them."""
+        default = factors.get("*", 1.0)
+        for i, b in enumerate(self.store.buckets):
+            f = factors.get(b.name, default)
+            if f != 1.0:
+                self.partials[i * BLOCKS_PER_BUCKET:(i + 1) * BLOCKS_PER_BUCKET].mul_(f)
+
 
 class PeerAdamW(FlatAdamW):
     """AdamW whose state is sharded over the ranks of the store's :class:`SymmGroup` (steps 2 and 3)."""
 
-    def __init__(self, store: FlatParamStore, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1):
+    def __init__(self, store: FlatParamStore, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
+                 scalars=None):
+        """``scalars``: the :class:`SymmGroup` over which the end-of-step scalars are exchanged (default:
+        the store's own group). Pass a world-wide group when the model is also split over pipeline
+        stages or tensor-parallel ranks."""
         sg = store.symm
         if sg is None:
             raise ValueError("PeerAdamW needs a FlatParamStore built on a SymmGroup")
-        super().__init__(store, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, shard_rank=sg.rank,
-                         shard_world=max(sg.world, 1))
-        self.sg = sg
-        if sg.world == 1:                        # FlatAdamW sized and exposed the state already
-            pass
+        lay = store.layout
+        super().__init__(store, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, shard_rank=lay.shard_rank,
+                         shard_world=max(lay.shard_world, 1))
+        self.sg, self.layout = sg, lay
+        self.sx = scalars if scalars is not None else sg
         self.stats = torch.zeros(4, dtype=torch.float32, device=store.device)
-        self.slot_step = sg.reserve_slots(2)
-        self.slot_done = self.slot_step + 1
+        self.slot_step = self.sx.reserve_slots(1)
+        self.slot_done = sg.reserve_slots(1)
         self._tables = None
         self._tables_wd = None
         self._full = None
 
     # ------------------------------------------------------------------ chunk tables
     def _build_tables(self, wd: float):
-        st, sg = self.store, self.sg
+        st, lay = self.store, self.layout
         chunk = int(ops.require().comm_adam_chunk())
         off, soff, ln, wds = [], [], [], []
         for b in st.buckets:
-            lo, n = st.shard_range(b, sg.rank)
-            s_base = b.start // sg.world
+            lo, n = st.shard_range(b, lay.shard_rank)
+            s_base = b.start // lay.shard_world
             for seg_off, seg_n, dec in self._segments(b):
                 a = max(b.start + seg_off, lo)
                 e = min(b.start + seg_off + seg_n, lo + n)
@@ -117,15 +148,35 @@ class PeerAdamW(FlatAdamW):
         self._tables_wd = wd
 
     # ------------------------------------------------------------------ step 2
-    def reduce_step(self, reducer: PeerReducer, loss: torch.Tensor, max_norm: float, skip_nonfinite: bool):
+    def reduce_step(self, reducer: PeerReducer, loss: torch.Tensor, max_norm: float, skip_nonfinite: bool,
+                    loss_weight: float = 1.0):
         """Enqueue the end-of-step exchange. Returns the device tensor ``[norm, mean loss, finite]``
-        and fills ``ctl`` for :meth:`step`."""
-        sg = self.sg
+        and fills ``ctl`` for :meth:`step`.
+
+        The kernel adds the ranks' sums of squares and averages their losses over the ``scalars``
+        group. When that group is wider than the data-parallel one, the caller weighs the partials
+        (:meth:`PeerReducer.weigh`) so that every gradient element is counted once, and passes
+        ``loss_weight`` so that the average comes out as the mean over the data-parallel ranks
+        (0 on ranks that hold no loss, e.g. all but the last pipeline stage)."""
+        sx = self.sx
         loss32 = loss.detach().to(torch.float32).reshape(1)
-        ops.require().comm_step_reduce(reducer.partials, None, loss32, sg.xchg.ptrs, sg.flags.ptrs, self.slot_step,
-                                       sg.next_epoch(self.slot_step), sg.rank, float(max_norm or 0.0),
-                                       bool(skip_nonfinite), self.stats, self.ctl, sg.timeout_ms, sg.status)
+        if loss_weight != 1.0:
+            loss32 = loss32 * float(loss_weight)
+        xchg, flags, me = sx.xchg.ptrs, sx.flags.ptrs, sx.rank
+        if self.local_only:
+            xchg, flags, me = [xchg[sx.rank]], [flags[sx.rank]], 0
+        ops.require().comm_step_reduce(reducer.partials, None, loss32, xchg, flags, self.slot_step,
+                                       sx.next_epoch(self.slot_step), me, float(max_norm or 0.0),
+                                       bool(skip_nonfinite), self.stats, self.ctl, sx.timeout_ms, sx.status)
         return self.stats[:3]
+
+    local_only = False
+
+    def detach(self, reducer: PeerReducer) -> None:
+        """Timing diagnostics, one way: from now on the three kernels of the step touch this rank's
+        memory only (peer tables of length one), so a step costs what it would cost with free
+        communication. The ranks' weights drift apart afterwards; use it last."""
+        self.local_only = reducer.local_only = True
 
     # ------------------------------------------------------------------ step 3
     @torch.no_grad()
@@ -140,9 +191,15 @@ class PeerAdamW(FlatAdamW):
             self._build_tables(wd)
         off, soff, ln, wds = self._tables
         bc1, bc2 = 1 - b1 ** self.steps, 1 - b2 ** self.steps
-        ops.require().comm_adamw_push(st.master, st.grad, self.exp_avg, self.exp_avg_sq, st.shadow_symm.ptrs, off, soff,
+        ptrs = st.shadow_symm.ptrs
+        if self.local_only:
+            ptrs = [ptrs[sg.rank]]
+        elif self.layout.replicas > 1:           # hybrid sharding: the other replicas compute the same shard themselves
+            ptrs = [ptrs[r] for r in self.layout.replica_peers()]
+        ops.require().comm_adamw_push(st.master, st.grad, self.exp_avg, self.exp_avg_sq, ptrs, off, soff,
                                       ln, wds, lr, b1, b2, self.defaults["eps"], bc1, bc2, self.ctl)
-        sg.barrier(self.slot_done)
+        if not self.local_only:
+            sg.barrier(self.slot_done)
         return None
 
     # ------------------------------------------------------------------ checkpoints
@@ -150,16 +207,16 @@ class PeerAdamW(FlatAdamW):
         """Expose the whole optimizer state per parameter (``torch.optim.AdamW`` layout) by gathering
         the moment shards into temporary full-size buffers. Pair with :meth:`release_full` (after a
         save) or :meth:`scatter_full` (after a load)."""
-        st, sg = self.store, self.sg
-        if sg.world == 1:
+        st, lay = self.store, self.layout
+        if lay.shard_world == 1:
             return
         full_m = torch.zeros(st.total, dtype=torch.float32, device=st.device)
         full_v = torch.zeros(st.total, dtype=torch.float32, device=st.device)
         for b in st.buckets:
-            n = b.size // sg.world
-            s0 = b.start // sg.world
-            dist.all_gather_into_tensor(st.bucket_view(full_m, b), self.exp_avg[s0:s0 + n], group=sg.group)
-            dist.all_gather_into_tensor(st.bucket_view(full_v, b), self.exp_avg_sq[s0:s0 + n], group=sg.group)
+            n = b.size // lay.shard_world
+            s0 = b.start // lay.shard_world
+            dist.all_gather_into_tensor(st.bucket_view(full_m, b), self.exp_avg[s0:s0 + n], group=lay.shard_group)
+            dist.all_gather_into_tensor(st.bucket_view(full_v, b), self.exp_avg_sq[s0:s0 + n], group=lay.shard_group)
         self._full = (full_m, full_v)
         for p in st.params:
             lo = st._offset[p]
@@ -175,7 +232,7 @@ class PeerAdamW(FlatAdamW):
         """Take this rank's shard back out of the full-size state (after ``load_state_dict``)."""
         if self._full is None:
             return
-        st, sg = self.store, self.sg
+        st, lay = self.store, self.layout
         full_m, full_v = self._full
         steps = 0
         for p in st.params:                      # load_state_dict replaced the views by copies
@@ -190,8 +247,8 @@ class PeerAdamW(FlatAdamW):
             if "step" in state:
                 steps = max(steps, int(float(state["step"])))
         for b in st.buckets:
-            lo, n = st.shard_range(b, sg.rank)
-            s0 = b.start // sg.world
+            lo, n = st.shard_range(b, lay.shard_rank)
+            s0 = b.start // lay.shard_world
             self.exp_avg[s0:s0 + n].copy_(full_m[lo:lo + n])
             self.exp_avg_sq[s0:s0 + n].copy_(full_v[lo:lo + n])
         self.steps = steps
@@ -199,7 +256,7 @@ class PeerAdamW(FlatAdamW):
         self.release_full()
 
     def load_state_dict(self, state_dict) -> None:
-        if self.sg.world == 1:
+        if self.layout.shard_world == 1:
             return super().load_state_dict(state_dict)
         if self._full is None:
             self.gather_full()

@@ -24,7 +24,7 @@ import torch.distributed as dist
 
 from .. import ops
 
-N_SLOTS = 128           # flag slots per group; slot s uses flags[s * MAX_PEERS + source_rank]
+N_SLOTS = 1024          # flag slots per group; slot s uses flags[s * MAX_PEERS + source_rank]
 
 
 @dataclass
@@ -46,10 +46,12 @@ def max_peers() -> int:
 class SymmGroup:
     """Allocator and flag bookkeeping for one process group on one device."""
 
-    def __init__(self, group, device, timeout_ms: float = 5000.0, nvls: bool = False):
+    def __init__(self, group, device, timeout_ms: float = 5000.0, nvls: bool = False, solo: bool = False):
+        """``group=None`` means the default (world) group; ``solo=True`` makes a group of this rank alone
+        even inside a multi-process job (a data-parallel dimension of size one)."""
         self.group = group
         self.device = torch.device(device)
-        self.world = dist.get_world_size(group) if (group is not None or dist.is_initialized()) else 1
+        self.world = 1 if solo else (dist.get_world_size(group) if (group is not None or dist.is_initialized()) else 1)
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         if self.world > max_peers():
             raise ValueError(f"peer-memory kernels address at most {max_peers()} ranks (one NVSwitch domain), "

@@ -44,7 +44,7 @@ BF16 = torch.bfloat16
 def usable(ctx) -> bool:
     pc = ctx.pc
     return bool(getattr(pc, "fused_comm", True)) and ctx.device.type == "cuda" and ops.available() \
-        and 1 < pc.tp <= 8 and pc.pp == 1 and pc.ep == 1
+        and 1 < pc.tp <= 8 and pc.ep == 1
 
 
 class TPState:
@@ -112,12 +112,17 @@ def _main_grad_or_new(param, shape, device):
 
 
 class _GatherLinear(torch.autograd.Function):
-    """``all_gather_rows(x_shard) @ W_local.T`` -> ``[M, N_local]`` (column-parallel layer)."""
+    """``all_gather_rows(x_shard) @ cat(W_local...).T`` -> ``[M, sum N_local]`` (column-parallel layers that
+    share their input: q|k|v, gate|up). The weights stay separate parameters; when a flat parameter store
+    laid their bf16 copies and gradient buffers out back to back the product reads and writes them in
+    place, otherwise the concatenation is cached and the gradient is split."""
 
     @staticmethod
-    def forward(ctx, x_shard, weight, tp: TPState):
-        from ..ops.functional import bf16_of
-        w = bf16_of(_plain(weight, "a column-parallel weight"))
+    def forward(ctx, x_shard, tp: TPState, *weights):
+        from ..ops.functional import fused_bf16
+        for wt in weights:
+            _plain(wt, "a column-parallel weight")
+        w = fused_bf16(weights)
         ms, k = x_shard.shape
         act, _, _, ready = tp.buffers(ms, k)
         epoch = tp.publish(act, tp.slot_act, x_shard)
@@ -125,33 +130,44 @@ class _GatherLinear(torch.autograd.Function):
         y = torch.empty((m, w.shape[0]), dtype=BF16, device=x_shard.device)
         tp.gemm(act.local.view(m, k), w, y, gather=1, gather_buf=act, ready=ready, wait=(tp.slot_act, epoch))
         ctx.save_for_backward(x_shard, w)
-        ctx.tp, ctx.weight = tp, weight
+        ctx.tp, ctx.weights = tp, weights
         return y
 
     @staticmethod
     @once_differentiable
     def backward(ctx, dy):
+        from ..ops.functional import fused_main_grad
         x_shard, w = ctx.saved_tensors
-        tp, weight = ctx.tp, ctx.weight
+        tp, weights = ctx.tp, ctx.weights
         ms, k = x_shard.shape
         m = ms * tp.world
         act, _, staging, ready = tp.buffers(ms, k)
         dy = dy.contiguous()
-        dw = None
-        if ctx.needs_input_grad[1]:
+        grads = [None] * len(weights)
+        if any(ctx.needs_input_grad[2:]):
             # dW[N_l, K] = dy[M, N_l].T @ gather(x)[M, K]: the gathered operand is on the reduction side
             epoch = tp.publish(act, tp.slot_act, x_shard)
-            out, is_main = _main_grad_or_new(weight, w.shape, dy.device)
-            tp.gemm(dy, act.local.view(m, k), out, a_mn=True, b_mn=True, accumulate=is_main, gather=2, gather_buf=act,
-                    ready=ready, wait=(tp.slot_act, epoch))
-            dw = None if is_main else out.to(weight.dtype)
+            main = fused_main_grad(weights)
+            out = main if main is not None else torch.empty(w.shape, dtype=torch.float32, device=dy.device)
+            tp.gemm(dy, act.local.view(m, k), out, a_mn=True, b_mn=True, accumulate=main is not None, gather=2,
+                    gather_buf=act, ready=ready, wait=(tp.slot_act, epoch))
+            if main is None:
+                lo = 0
+                for i, wt in enumerate(weights):
+                    piece = out[lo:lo + wt.shape[0]]
+                    lo += wt.shape[0]
+                    own = getattr(wt, "_fm_main_grad", None)
+                    if own is not None:
+                        own.add_(piece)
+                    elif ctx.needs_input_grad[2 + i]:
+                        grads[i] = piece.to(wt.dtype)
         dx = None
         if ctx.needs_input_grad[0]:
             # dx_shard = reduce_scatter_rows(dy @ W_local)
             tp.gemm(dy, w, staging.local.view(m, k), b_mn=True, d_buf=staging)
             tp.barrier()
             dx = tp.reduce(staging, ms, k)
-        return dx, dw, None
+        return (dx, None, *grads)
 
 
 class _LinearScatter(torch.autograd.Function):
@@ -202,8 +218,11 @@ class _LinearScatter(torch.autograd.Function):
         return dh, dw, (dout if ctx.has_res else None), None
 
 
-def gather_linear(x_shard, weight, tp: TPState):
-    return _GatherLinear.apply(x_shard, weight, tp)
+def gather_linear(x_shard, weights, tp: TPState):
+    """``weights``: one weight or a tuple of weights whose outputs are concatenated."""
+    if isinstance(weights, torch.Tensor):
+        weights = (weights,)
+    return _GatherLinear.apply(x_shard, tp, *weights)
 
 
 def linear_scatter(h, weight, residual, tp: TPState):
@@ -310,8 +329,7 @@ def block_forward(blk, x_shard, state: TPState):
     hd = at.hd
     nq, nkv = at.wq.weight.shape[0] // hd, at.wk.weight.shape[0] // hd
     xn = Fn.rms_norm(x_shard, blk.attn_norm.weight, blk.attn_norm.eps)
-    wqkv = torch.cat([at.wq.weight, at.wk.weight, at.wv.weight], dim=0)     # autograd splits the gradient again
-    qkv = gather_linear(xn, wqkv, state)                       # [M, (nq + 2 nkv) * hd]
+    qkv = gather_linear(xn, (at.wq.weight, at.wk.weight, at.wv.weight), state)     # [M, (nq + 2 nkv) * hd]
     B, T = blk._fm_bt
     qkv = qkv.view(B, T, -1)
     cos, sin = rope_tables(T, hd, at.theta, qkv.device, torch.float32)
@@ -319,8 +337,7 @@ def block_forward(blk, x_shard, state: TPState):
     o = Fn.attention_qkv(qkv, nq, nkv, hd, True)               # [B, T, nq * hd]
     h = linear_scatter(o.reshape(B * T, nq * hd), at.wo.weight, x_shard, state)
     hn = Fn.rms_norm(h, blk.ffn_norm.weight, blk.ffn_norm.eps)
-    w13 = torch.cat([ff.w1.weight, ff.w3.weight], dim=0)
-    gu = gather_linear(hn, w13, state)                         # [M, 2 * hidden_local]
+    gu = gather_linear(hn, (ff.w1.weight, ff.w3.weight), state)                   # [M, 2 * hidden_local]
     act = Fn.swiglu_split(gu)
     return linear_scatter(act, ff.w2.weight, h, state)
 

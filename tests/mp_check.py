@@ -226,6 +226,92 @@ def sc_collectives(world):
     fm.barrier()
 
 
+def sc_flat_pp_dp(world):
+    """Flat-store engine under pipeline x data parallelism: every gradient bucket is reduced exactly once
+    per optimizer step (from the last micro-batch's backward of the last accumulation step, never
+    earlier), and the run equals the library engine's."""
+    losses = {}
+    for flat in (True, False):
+        os.environ["FORGEMINDS_FLAT_ENGINE"] = "1" if flat else "0"
+        cfg = _cfg(pp=2, **({"dp_shard": world // 2} if flat else {"dp_replicate": world // 2}))
+        cfg.parallel.pp_microbatches = 4
+        cfg.train.grad_accum = 2
+        cfg.train.max_steps = 6
+        mc = _mc()
+        ds = fm.SyntheticLM(mc.vocab_size, mc.max_seq, n=1024)
+        tr = fm.Trainer(lambda ctx: fm.GPT(mc), cfg, ds, micro_batch=8)
+        assert (tr.eng.name == "native") == flat
+        launches = []
+        if flat:
+            real = tr.reducer.launch
+            backwards = [0]
+            scope = tr.eng.sync_scope
+
+            def counted_scope(final, forward=False, _scope=scope):
+                backwards[0] += 0 if forward else 1
+                return _scope(final, forward)
+            tr.pp.grad_sync = counted_scope
+
+            def spy(bucket, _real=real):
+                launches.append((bucket.name, backwards[0]))
+                return _real(bucket)
+            tr.reducer.launch = spy
+        hist = []
+        for _ in range(6):
+            launches.clear()
+            if flat:
+                backwards[0] = 0
+            hist.append(tr.train_step()["loss"])
+            if flat:
+                blocks = [b.name for b in tr.store.buckets if b.name.startswith("block")]
+                assert sorted(n for n, _ in launches) == sorted(blocks), launches
+                assert all(k == 2 * 4 for _, k in launches), launches       # the 8th backward of the step
+        tr.close()
+        losses[flat] = hist
+    if dist.get_rank() >= world // 2:                 # the last stage holds the loss
+        assert max(abs(a - b) for a, b in zip(losses[True], losses[False])) < 1e-4, losses
+
+
+def sc_tp_ckpt(world):
+    """Plain tensors that hold one tensor-parallel slice per rank are stored as one sharded tensor and
+    come back slice by slice (what the fused tensor-parallel blocks rely on for their checkpoints)."""
+    import tempfile
+    import torch.distributed.checkpoint as dcp
+    from forgeminds_b200.engine import checkpoint as ckpt
+    ctx = fm.init_distributed(fm.ParallelConfig(tp=world))
+    rank = ctx.tp_rank
+    torch.manual_seed(0)
+    whole_col, whole_row, vec = torch.randn(8 * world, 6), torch.randn(5, 4 * world), torch.randn(6)
+
+    def build(fill):
+        m = torch.nn.Module()
+        m.col = torch.nn.Parameter(whole_col[rank * 8:(rank + 1) * 8].clone() if fill else torch.zeros(8, 6))
+        m.row = torch.nn.Parameter(whole_row[:, rank * 4:(rank + 1) * 4].clone() if fill else torch.zeros(5, 4))
+        m.vec = torch.nn.Parameter(vec.clone() if fill else torch.zeros(6))
+        m.col._tp_shard_dim, m.row._tp_shard_dim = 0, 1
+        return m
+    src = build(True)
+    opt_state = {"state": {"col": {"exp_avg": src.col.detach() * 2, "step": torch.tensor(3.0)},
+                           "vec": {"exp_avg": src.vec.detach() * 2, "step": torch.tensor(3.0)}}, "param_groups": []}
+    msd, osd = ckpt.as_sharded(src, dict(src.named_parameters()), opt_state, ctx.mesh["tp"])
+    assert tuple(msd["col"].shape) == (8 * world, 6) and tuple(msd["row"].shape) == (5, 4 * world)
+    box = [tempfile.mkdtemp() if dist.get_rank() == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    dcp.save({"model": msd, "optim": osd}, checkpoint_id=box[0])
+    dst = build(False)
+    blank = {"state": {"col": {"exp_avg": torch.zeros(8, 6), "step": torch.tensor(0.0)},
+                       "vec": {"exp_avg": torch.zeros(6), "step": torch.tensor(0.0)}}, "param_groups": []}
+    msd2, osd2 = ckpt.as_sharded(dst, {k: v.detach() for k, v in dst.named_parameters()}, blank, ctx.mesh["tp"])
+    state = {"model": msd2, "optim": osd2}
+    dcp.load(state, checkpoint_id=box[0])
+    local = ckpt.as_local(state)
+    assert torch.equal(local["model"]["col"], src.col.detach()) and torch.equal(dst.col.detach(), src.col.detach())
+    assert torch.equal(local["model"]["row"], src.row.detach())
+    assert torch.equal(local["model"]["vec"], vec)
+    assert torch.equal(local["optim"]["state"]["col"]["exp_avg"], src.col.detach() * 2)
+    assert float(local["optim"]["state"]["col"]["step"]) == 3.0
+
+
 SCENARIOS = {k[3:]: v for k, v in list(globals().items()) if k.startswith("sc_")}
 
 

@@ -240,15 +240,15 @@ def ep_fused():
             holder._fm_ep.sg.check()
             if cap_factor > 0.0:
                 continue
-            assert (x.grad.float() - xr.grad.float()).norm() / xr.grad.float().norm() < 0.08
+            assert (x.grad.float() - xr.grad.float()).norm() / xr.grad.float().norm() < 0.02
             a, b = part.router.gate.weight.grad.float(), whole.router.gate.weight.grad.float()
-            assert (a - b).norm() / b.norm() < 0.08
+            assert (a - b).norm() / b.norm() < 0.02
             for name in ("w1", "w3", "w2"):
                 full = getattr(whole.experts, name).grad.float().clone()
                 dist.all_reduce(full)              # an expert sees the tokens of every rank
                 mine = getattr(part.experts, name).grad.float()
                 ref = full[rank * el:(rank + 1) * el]
-                assert (mine - ref).norm() / ref.norm() < 0.08, name
+                assert (mine - ref).norm() / ref.norm() < 0.02, name
     dist.barrier()
     if rank == 0:
         print("OK ep_fused", flush=True)
@@ -337,7 +337,7 @@ def tp_grads():
                 want = want.narrow(dim, rank * n, n)
             got = p.grad.float()
             rel = (got - want).norm() / want.norm().clamp(min=1e-6)
-            assert rel < 8e-2, f"step {step} {name}: relative gradient error {rel.item():.3f}"
+            assert rel < 2e-2, f"step {step} {name}: relative gradient error {rel.item():.3f}"
     dist.barrier()
     if rank == 0:
         print("OK tp_grads", flush=True)
@@ -363,9 +363,140 @@ def tp_fused():
     a, b = losses[True], losses[False]
     assert a[-1] < 0.85 * a[0], a
     assert max(abs(x - y) for x, y in zip(a[:4], b[:4])) < 0.03, (a, b)           # same trajectory at the start
-    assert all(abs(x - y) < 0.05 + 0.12 * y for x, y in zip(a, b)), (a, b)        # two bf16 paths drift apart slowly
+    assert all(abs(x - y) < 0.02 + 0.02 * y for x, y in zip(a, b)), (a, b)        # two bf16 paths drift apart slowly
     if rank == 0:
         print("OK tp_fused", flush=True)
+
+
+class _FixedFeed:
+    """Hands the trainer the same batch at every call (each data-parallel rank has its own)."""
+
+    def __init__(self, ids):
+        self.ids = ids
+        self.epoch, self.batches = 0, 0
+
+    def next(self):
+        return self.ids[:, :-1], self.ids[:, 1:]
+
+    def close(self):
+        pass
+
+    def resume(self, *a):
+        pass
+
+
+def _mesh_equiv(world, rank, dev, label, check_ckpt=False, **par):
+    """Gradients, global norm, losses and updates of the sm_100a engine on a mesh against a whole fp32
+    PyTorch model that sees the batches of all data-parallel ranks."""
+    import tempfile
+    mc = fm.GPTConfig(vocab_size=512, dim=256, n_layers=4, n_heads=8, n_kv_heads=4, max_seq=128, ffn_hidden=512)
+    cfg = fm.ForgeConfig()
+    cfg.parallel.__dict__.update(par)
+    box = [tempfile.mkdtemp() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    cfg.train.__dict__.update(max_steps=8, grad_accum=1, lr=2e-3, warmup_steps=2, bf16=True, resume=False,
+                              log_every=1000, prefetch=False, ckpt_every=0, ckpt_dir=box[0], grad_clip=1.0)
+    if cfg.parallel.pp > 1:
+        cfg.parallel.pp_microbatches = 2
+    tr = fm.Trainer(lambda ctx: fm.GPT(mc), cfg, fm.SyntheticLM(512, 128, n=64), micro_batch=4)
+    ctx, eng, st = tr.ctx, tr.eng, tr.store
+    assert eng.name == "native" and st is not None, label
+    assert tr.peer, label
+    # the oracle: same seed -> same initial weights, fp32 PyTorch operators, every data-parallel rank's batch
+    torch.manual_seed(cfg.train.seed)
+    oracle = fm.GPT(fm.GPTConfig(**{**mc.__dict__, "native": False})).to(dev)
+    batches = [torch.randint(0, 512, (4, 129), device=dev, generator=torch.Generator(device=dev).manual_seed(40 + d))
+               for d in range(ctx.dp_world)]
+    tr.feed.close()
+    tr.feed = _FixedFeed(batches[ctx.dp_rank])
+    named = dict(oracle.named_parameters())
+    decay = [p for p in oracle.parameters() if p.ndim >= 2]
+    rest = [p for p in oracle.parameters() if p.ndim < 2]
+    ref_opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": rest, "weight_decay": 0.0}],
+                                lr=2e-3, betas=cfg.train.betas, eps=cfg.train.eps)
+
+    def oracle_step():
+        ref_opt.zero_grad(set_to_none=True)
+        loss = sum(oracle(b[:, :-1], labels=b[:, 1:])[0] for b in batches) / len(batches)
+        loss.backward()
+        return loss.item(), torch.nn.utils.get_total_norm([p.grad for p in oracle.parameters()]).item()
+
+    # ---- one backward: every reduced gradient element that this rank owns
+    want_loss, want_norm = oracle_step()
+    ids, y = tr.feed.next()
+    ce = eng.micro_step(ids, y, last=True)
+    eng._sum_partial_grads()
+    if eng.reducer is not None:
+        eng.reducer.finish()
+    torch.cuda.synchronize()
+    expected = torch.zeros_like(st.grad)
+    for name, p in tr.raw.named_parameters():
+        g = named[name].grad.float()
+        dim = getattr(p, "_tp_shard_dim", None)
+        if dim is not None:
+            g = g.narrow(dim, ctx.tp_rank * p.shape[dim], p.shape[dim])
+        lo = st._offset[p]
+        expected[lo:lo + p.numel()] = g.reshape(-1)
+    worst = 0.0
+    for b in st.buckets:
+        lo, n = st.shard_range(b, st.layout.shard_rank)
+        got, want = st.grad[lo:lo + n], expected[lo:lo + n]
+        if want.norm() == 0:
+            continue
+        rel = ((got - want).norm() / want.norm()).item()
+        worst = max(worst, rel)
+        assert rel < 2e-2, f"{label}: bucket {b.name}: relative gradient error {rel:.4f}"
+    has_loss = cfg.parallel.pp == 1 or ctx.pp_rank == cfg.parallel.pp - 1
+    if has_loss:
+        mine = oracle(batches[ctx.dp_rank][:, :-1], labels=batches[ctx.dp_rank][:, 1:])[0].item()
+        assert abs(ce.item() - mine) < 2e-2, (label, ce.item(), mine)
+    eng.zero_grad()
+    # ---- optimizer steps: global norm, mean loss and the trajectory
+    for step in range(4):
+        want_loss, want_norm = oracle_step()
+        torch.nn.utils.clip_grad_norm_(oracle.parameters(), 1.0)
+        for g in ref_opt.param_groups:
+            g["lr"] = tr.lr_at(step)
+        ref_opt.step()
+        m = tr.train_step()
+        assert m["skipped"] == 0, (label, m)
+        assert abs(m["grad_norm"] - want_norm) < 2e-2 * want_norm, (label, step, m["grad_norm"], want_norm)
+        assert abs(m["loss"] - want_loss) < 3e-2, (label, step, m["loss"], want_loss)
+    if check_ckpt:
+        tr.save()
+        cfg.train.resume = True
+        again = fm.Trainer(lambda ctx: fm.GPT(mc), cfg, fm.SyntheticLM(512, 128, n=64), micro_batch=4)
+        assert again.step == tr.step
+        again.feed.close()
+        again.feed = _FixedFeed(batches[ctx.dp_rank])
+        a, b = tr.train_step(), again.train_step()
+        assert abs(a["loss"] - b["loss"]) < 1e-3 and abs(a["grad_norm"] - b["grad_norm"]) < 1e-2 * a["grad_norm"], (a, b)
+        a, b = tr.train_step(), again.train_step()         # the optimizer state came back too
+        assert abs(a["loss"] - b["loss"]) < 2e-3, (label, a["loss"], b["loss"])
+        again.close()
+    tr.close()
+    if rank == 0:
+        print(f"  {label}: worst bucket gradient error {worst:.4f}", flush=True)
+
+
+def mesh_equiv():
+    """Every mesh the box has GPUs for, against the whole fp32 model (2 % on gradients and the norm)."""
+    rank, world, dev = _init()
+    if world == 2:
+        _mesh_equiv(world, rank, dev, "dp_shard=2", dp_shard=2)
+        _mesh_equiv(world, rank, dev, "tp=2", check_ckpt=True, tp=2)
+        _mesh_equiv(world, rank, dev, "pp=2 (1f1b)", pp=2)
+        _mesh_equiv(world, rank, dev, "pp=2 (gpipe)", pp=2, pp_schedule="gpipe")
+    elif world == 4:
+        _mesh_equiv(world, rank, dev, "dp_replicate=2 x dp_shard=2", check_ckpt=True, dp_replicate=2, dp_shard=2)
+        _mesh_equiv(world, rank, dev, "tp=2 x dp_shard=2", tp=2, dp_shard=2)
+        _mesh_equiv(world, rank, dev, "pp=2 x dp_shard=2", pp=2, dp_shard=2)
+        _mesh_equiv(world, rank, dev, "pp=2 x tp=2", check_ckpt=True, pp=2, tp=2)
+    else:
+        _mesh_equiv(world, rank, dev, "pp=2 x dp_shard=2 x tp=2", check_ckpt=True, pp=2, dp_shard=world // 4, tp=2)
+        _mesh_equiv(world, rank, dev, "dp_replicate=2 x dp_shard=4", dp_replicate=2, dp_shard=world // 2)
+    if rank == 0:
+        print("OK mesh_equiv", flush=True)
 
 
 def _mesh_run(world, rank, label, steps=8, quant="none", optimizer="adamw", **par):

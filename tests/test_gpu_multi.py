@@ -20,8 +20,9 @@ def _run(scenario: str, nproc: int, port: int, timeout: int = 420):
 
 
 needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-# number of ranks of the multi-process scenarios: 2, or 4 when FMB_TEST_RANKS=4 and the box has them
-RANKS = 4 if (os.environ.get("FMB_TEST_RANKS") == "4" and torch.cuda.device_count() >= 4) else 2
+# number of ranks of the multi-process scenarios: 2, or FMB_TEST_RANKS (4 or 8) when the box has that many GPUs
+_ASK = int(os.environ.get("FMB_TEST_RANKS", "2") or 2)
+RANKS = _ASK if (_ASK in (4, 8) and torch.cuda.device_count() >= _ASK) else 2
 
 
 @needs2
@@ -57,6 +58,12 @@ def test_expert_parallel_over_peer_memory_two_ranks():
 @needs2
 def test_missing_rank_is_reported_not_waited_for_forever():
     _run("peer_failure", RANKS, 29617)
+
+
+@needs2
+def test_every_mesh_matches_the_whole_fp32_model():
+    """2 ranks: dp, tp, pp (both schedules); 4: HSDP, tp x dp, pp x dp, pp x tp; 8: pp x dp x tp and HSDP 2 x 4."""
+    _run("mesh_equiv", RANKS, 29619, timeout=900)
 
 
 @needs2
