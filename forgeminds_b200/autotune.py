@@ -1,38 +1,54 @@
-"""Measure the cheap switches of a training step and report the fastest combination.
+"""Try the cheap knobs of a training step, time each, and say which combination is fastest.
 
-``autotune(target)`` times a baseline step of a :class:`~forgeminds_b200.forge.Forge` or
-:class:`~forgeminds_b200.trainer.Trainer` and then a handful of variants (precision, fused kernels,
-accumulation, rebuilt trainers for knobs that cannot be flipped on a live object); out-of-memory and
-other failures are recorded as data, nothing is changed unless ``apply=True``. ``tune_batch_size``
-sweeps micro-batch sizes by *per-sample* cost. ``autotune_kernels`` times the fused kernels of this
-device with CUDA events. Interface of the reference's ``forgemind/autotune.py:48-372``.
+Nothing here guesses: every candidate is run for a few steps and timed; a candidate that runs out of
+memory or raises is written down as a result, not propagated. Entry points (the reference's
+``forgemind/autotune.py:48-372``):
+
+* :func:`autotune` -- baseline plus variants of a live :class:`~forgeminds_b200.forge.Forge` (autocast
+  dtype, fused kernels patched in, accumulation off) and of trainers rebuilt through ``build(**knobs)``
+  for settings that cannot be flipped on a live object; stays within ``budget_s`` seconds;
+* :func:`tune_batch_size` -- grows the micro-batch while the cost *per sample* keeps falling;
+* :func:`apply_fast_defaults` -- the process-wide switches that are free on this hardware;
+* :func:`autotune_kernels` -- device timings of the fused kernels (a health check: they have no launch
+  parameters to sweep);
+* ``python -m forgeminds_b200.autotune`` -- the same on a small GPT from the command line.
 """
 from __future__ import annotations
 
-import contextlib
+import gc
 import json
 import os
 import statistics
 import time
-from dataclasses import dataclass, field
+from dataclasses import asdict, dataclass, field
+from typing import Callable, Optional
 
 import torch
 
 __all__ = ["Trial", "Report", "time_call", "apply_fast_defaults", "tune_batch_size", "autotune",
            "autotune_kernels"]
 
+INF = float("inf")
+
 
 @dataclass
 class Trial:
+    """One timed candidate. ``ok`` is false when it did not run to the end; ``oom`` says why, if memory."""
     label: str
     ok: bool = True
-    ms: float = float("inf")
+    ms: float = INF
     note: str = ""
     oom: bool = False
 
-    def __str__(self) -> str:
-        status = "oom" if self.oom else ("ok" if self.ok else "fail")
-        return f"{self.label:38s} {status:5s} {self.ms:9.2f} ms  {self.note}"
+    @property
+    def outcome(self) -> str:
+        if self.oom:
+            return "OOM"
+        return "done" if self.ok else "error"
+
+    def row(self, width: int) -> str:
+        took = f"{self.ms:10.3f}" if self.ms < INF else f"{'-':>10s}"
+        return f"{self.label:<{width}s}  {self.outcome:<5s}  {took}  {self.note}".rstrip()
 
 
 @dataclass
@@ -47,240 +63,311 @@ class Report:
         return trial
 
     def table(self) -> str:
-        return "\n".join([f"{'trial':38s} {'stat':5s} {'median':>9s}  note", *map(str, self.trials)])
+        width = max([len(t.label) for t in self.trials] + [9])
+        head = f"{'candidate':<{width}s}  {'end':<5s}  {'median ms':>10s}  remarks"
+        return "\n".join([head, "-" * len(head)] + [t.row(width) for t in self.trials])
 
     def speedup(self) -> float:
-        best = self.best.get("ms")
-        return self.baseline_ms / best if (self.baseline_ms and best) else 1.0
+        winner = self.best.get("ms")
+        if not winner or not self.baseline_ms or winner == INF or self.baseline_ms == INF:
+            return 1.0
+        return self.baseline_ms / winner
 
     def to_dict(self) -> dict:
-        return {"device": self.device, "best": self.best, "baseline_ms": self.baseline_ms,
-                "speedup": self.speedup(), "trials": [vars(t) for t in self.trials]}
+        return {"device": self.device, "baseline_ms": self.baseline_ms, "best": dict(self.best),
+                "speedup": self.speedup(), "trials": [asdict(t) for t in self.trials]}
 
 
-def _is_oom(exc: BaseException) -> bool:
-    if isinstance(exc, getattr(torch.cuda, "OutOfMemoryError", ())):
+def _out_of_memory(err: BaseException) -> bool:
+    oom_type = getattr(torch.cuda, "OutOfMemoryError", None)
+    if oom_type is not None and isinstance(err, oom_type):
         return True
-    return "out of memory" in str(exc).lower()
+    return "out of memory" in f"{err}".lower()
 
 
-def time_call(fn, warmup: int = 2, repeats: int = 5, sync: bool = True) -> float:
-    """Median wall time of ``fn()`` in milliseconds after ``warmup`` untimed calls."""
-    wait = torch.cuda.synchronize if (sync and torch.cuda.is_available()) else (lambda: None)
-    for _ in range(max(0, warmup)):
+def _drain_gpu() -> None:
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+
+
+def _free_cached() -> None:
+    gc.collect()
+    if torch.cuda.is_available():
+        try:
+            torch.cuda.empty_cache()
+        except RuntimeError:
+            pass
+
+
+def time_call(fn: Callable[[], object], warmup: int = 2, repeats: int = 5, sync: bool = True) -> float:
+    """Milliseconds per call of ``fn`` (median of ``repeats`` calls, after ``warmup`` calls that are not
+    timed). With ``sync`` every timed call ends with a device synchronisation, so the figure includes the
+    GPU work the call enqueued."""
+    settle = _drain_gpu if sync else (lambda: None)
+    for _ in range(max(0, int(warmup))):
         fn()
-    wait()
-    samples = []
-    for _ in range(max(1, repeats)):
-        t0 = time.perf_counter()
+    settle()
+    laps = []
+    for _ in range(max(1, int(repeats))):
+        begin = time.perf_counter()
         fn()
-        wait()
-        samples.append((time.perf_counter() - t0) * 1e3)
-    return statistics.median(samples)
+        settle()
+        laps.append(1e3 * (time.perf_counter() - begin))
+    return statistics.median(laps)
 
 
 def apply_fast_defaults(device=None, allow_tf32: bool = True, allocator: bool = True) -> dict:
-    """Turn on the settings that are almost always free; returns what was changed."""
-    changed = {}
+    """Switch on what costs nothing: TF32 for stray fp32 matmuls, cuDNN autotuning, and (for processes
+    started after this one) the expandable-segments allocator. Returns a dict of what was touched."""
+    did: dict = {}
     if allow_tf32:
-        with contextlib.suppress(Exception):
-            torch.backends.cuda.matmul.allow_tf32 = True
-            torch.backends.cudnn.allow_tf32 = True
+        try:
             torch.set_float32_matmul_precision("high")
-            changed["tf32"] = True
-    if torch.cuda.is_available():
-        with contextlib.suppress(Exception):
-            torch.backends.cudnn.benchmark = True
-            changed["cudnn_benchmark"] = True
-        if allocator and "PYTORCH_CUDA_ALLOC_CONF" not in os.environ:
-            os.environ["PYTORCH_CUDA_ALLOC_CONF"] = "expandable_segments:True"
-            changed["expandable_segments"] = "(set, takes effect on next process)"
-    changed["threads"] = torch.get_num_threads()
-    return changed
+            torch.backends.cudnn.allow_tf32 = True
+            torch.backends.cuda.matmul.allow_tf32 = True
+            did["tf32"] = True
+        except (RuntimeError, AttributeError):
+            did["tf32"] = False
+    on_gpu = torch.cuda.is_available() and (device is None or torch.device(device).type == "cuda")
+    if on_gpu:
+        torch.backends.cudnn.benchmark = True
+        did["cudnn_benchmark"] = True
+        if allocator:
+            if os.environ.get("PYTORCH_CUDA_ALLOC_CONF"):
+                did["allocator"] = "left as configured: " + os.environ["PYTORCH_CUDA_ALLOC_CONF"]
+            else:
+                os.environ["PYTORCH_CUDA_ALLOC_CONF"] = "expandable_segments:True"
+                did["allocator"] = "expandable_segments:True exported; child processes and the next run use it"
+    did["cpu_threads"] = torch.get_num_threads()
+    return did
 
 
-def tune_batch_size(step_fn, candidates=(1, 2, 4, 8, 16, 32), *, warmup: int = 1, repeats: int = 3,
-                    min_gain: float = 0.02, footprint=None, report: "Report | None" = None):
-    """Largest micro-batch that still lowers the cost per sample; stops at the first size without a
-    gain of ``min_gain`` or at the first out-of-memory. Returns ``(size, ms_per_step)``."""
-    report = report or Report()
-    best = (None, float("inf"), float("inf"))       # size, ms, ms per sample
+def tune_batch_size(step_fn: Callable[[int], object], candidates=(1, 2, 4, 8, 16, 32), *, warmup: int = 1,
+                    repeats: int = 3, min_gain: float = 0.02, footprint=None,
+                    report: Optional[Report] = None):
+    """Walk up ``candidates`` while a bigger micro-batch is cheaper per sample by at least ``min_gain``.
+
+    ``step_fn(size)`` runs one step at that size; ``footprint(size)``, when given, is called first (allocate
+    the batch there, so that a size that cannot even be staged counts as not fitting). The walk ends at
+    the first size that does not fit in memory or brings no gain. Returns ``(size, ms per step)`` of the
+    winner; other exceptions propagate."""
+    log = report if report is not None else Report()
+    winner_size, winner_ms, winner_unit = None, INF, INF
     for size in candidates:
-        trial = Trial(label=f"micro_batch={size}")
+        entry = Trial(label=f"micro_batch={size}")
+        log.add(entry)
         try:
             if footprint is not None:
                 footprint(size)
-            ms = time_call(lambda: step_fn(size), warmup=warmup, repeats=repeats)
-        except BaseException as exc:      # noqa: BLE001 -- running out of memory is a result here
-            if not _is_oom(exc):
+            took = time_call(lambda: step_fn(size), warmup=warmup, repeats=repeats)
+        except BaseException as err:  # noqa: BLE001 - an allocation failure is an answer, anything else is a bug
+            if not _out_of_memory(err):
                 raise
-            trial.ok, trial.oom, trial.note = False, True, "did not fit"
-            report.add(trial)
+            entry.ok, entry.oom, entry.note = False, True, "does not fit in device memory; search ends"
             break
-        per = ms / size
-        better = best[0] is None or per < best[2] * (1.0 - min_gain)
-        trial.ms, trial.note = ms, f"{per:.3f} ms/sample" + (", best so far" if better else ", no gain -> stop")
-        report.add(trial)
-        if not better:
+        unit = took / size
+        entry.ms = took
+        improved = winner_size is None or unit < (1.0 - min_gain) * winner_unit
+        entry.note = f"{unit:.3f} ms per sample" + ("" if improved else f" (less than {min_gain:.0%} better; search ends)")
+        if not improved:
             break
-        best = (size, ms, per)
-        if torch.cuda.is_available():
-            with contextlib.suppress(Exception):
-                torch.cuda.empty_cache()
-    return (best[0] or candidates[0]), best[1]
+        winner_size, winner_ms, winner_unit = size, took, unit
+        _free_cached()
+    if winner_size is None:
+        return candidates[0], winner_ms
+    return winner_size, winner_ms
+
+
+class _Knob:
+    """A reversible change to a live object: attribute overrides and/or a pair of callbacks."""
+
+    def __init__(self, label: str, result: dict, target=None, attrs: Optional[dict] = None, enter=None, leave=None,
+                 note: str = ""):
+        self.label, self.result, self.note = label, result, note
+        self.target, self.attrs, self.enter, self.leave = target, attrs or {}, enter, leave
+        self._old: dict = {}
+
+    def __enter__(self):
+        for name, value in self.attrs.items():
+            self._old[name] = getattr(self.target, name)
+            setattr(self.target, name, value)
+        if self.enter is not None:
+            self.enter()
+        return self
+
+    def __exit__(self, *exc):
+        if self.leave is not None:
+            self.leave()
+        for name, value in self._old.items():
+            setattr(self.target, name, value)
+        self._old.clear()
+        return False
+
+
+def _forge_knobs(forge, precision: bool, fused: bool, accum: bool) -> list:
+    knobs = []
+    if precision and forge.device.type == "cuda":
+        from .forge import _Amp
+        for name in ("bf16", "fp16"):
+            if name != forge.precision:
+                knobs.append(_Knob(f"precision={name}", {"precision": name}, forge,
+                                   {"precision": name, "amp": _Amp(name, forge.device)}))
+    if fused:
+        from . import kernels
+        if kernels.available():
+            from .kernels.apply import enable, revert
+            patched_before = any(getattr(m, "_fm_norm", False) or getattr(m, "_fm_mlp", False)
+                                 for m in forge.raw_model.modules())
+            knobs.append(_Knob("fused_kernels=on", {"fused_ops": True}, note="RMSNorm and SwiGLU modules call the kernels",
+                               enter=lambda: enable(forge.raw_model),
+                               leave=(lambda: None) if patched_before else (lambda: revert(forge.raw_model))))
+    if accum and forge.accum > 1:
+        from .forge import _Window
+        knobs.append(_Knob("accum=1", {"accum": 1}, forge, {"accum": 1, "window": _Window()},
+                           note="cost of one micro-batch plus an update"))
+    return knobs
 
 
 def autotune(target, loader=None, *, build=None, budget_s: float = 60.0, apply: bool = False,
              precision: bool = True, accum: bool = True, compiled: bool = False, fused: bool = True,
-             report: "Report | None" = None) -> Report:
+             report: Optional[Report] = None) -> Report:
+    """Time ``target`` (a ``Forge`` fed from ``loader``, or anything with ``train_step()``) as it is and
+    under each applicable variant; ``build(**knobs)`` returns a fresh trainer for variants that need one
+    (``bf16``, ``ac="full"``, ``compile`` when ``compiled``). Candidates that would start after
+    ``budget_s`` seconds are listed as skipped. ``apply=True`` leaves the winning attribute values on
+    ``target``. The winner and its time are in ``report.best``."""
     from .forge import Forge
-    report = report or Report()
-    report.device = str(getattr(target, "device", "cpu"))
-    started = time.time()
-    is_forge = isinstance(target, Forge)
-    batch = next(iter(loader)) if (is_forge and loader is not None) else None
+    rep = report if report is not None else Report()
+    rep.device = str(getattr(target, "device", "cpu"))
+    deadline = time.monotonic() + float(budget_s)
+    live_forge = isinstance(target, Forge)
+    sample = next(iter(loader)) if (live_forge and loader is not None) else None
 
-    def runner(obj):
-        if is_forge and batch is not None:
-            return lambda: obj.step(batch)
-        return lambda: obj.train_step()
+    def one_step(obj):
+        if isinstance(obj, Forge) and sample is not None:
+            return lambda: obj.step(sample)
+        return obj.train_step
 
-    def measure(label, before=None, after=None, note="", obj=None):
-        if time.time() - started > budget_s:
-            report.add(Trial(label, ok=False, note="skipped: budget"))
-            return float("inf")
+    def clock(label: str, obj, note: str = "", scope=None) -> float:
+        entry = rep.add(Trial(label, note=note))
+        if time.monotonic() > deadline:
+            entry.ok, entry.note = False, "not run: time budget used up"
+            return INF
         try:
-            if before:
-                before()
-            trial = Trial(label, ms=time_call(runner(obj or target), warmup=1, repeats=3), note=note)
-        except BaseException as exc:      # noqa: BLE001
-            trial = Trial(label, ok=False, oom=_is_oom(exc), note=str(exc).replace("\n", " ")[:60])
-        finally:
-            if after:
-                after()
-        report.add(trial)
-        return trial.ms
+            if scope is not None:
+                with scope:
+                    entry.ms = time_call(one_step(obj), warmup=1, repeats=3)
+            else:
+                entry.ms = time_call(one_step(obj), warmup=1, repeats=3)
+        except BaseException as err:  # noqa: BLE001 - failures are rows of the report
+            entry.ok, entry.oom = False, _out_of_memory(err)
+            entry.note = " ".join(f"{type(err).__name__}: {err}".split())[:70]
+            _free_cached()
+        return entry.ms
 
-    def override(**values):
-        saved = {}
+    rep.baseline_ms = clock("baseline", target)
+    lead_ms, lead = rep.baseline_ms, {}
 
-        def before():
-            for k, v in values.items():
-                saved[k] = getattr(target, k)
-                setattr(target, k, v)
-
-        def after():
-            for k, v in saved.items():
-                setattr(target, k, v)
-        return before, after
-
-    report.baseline_ms = best_ms = measure("baseline")
-    best: dict = {}
-
-    if is_forge:
-        if precision and report.device.startswith("cuda"):
-            for name, dt in (("bf16", torch.bfloat16), ("fp16", torch.float16)):
-                ms = measure(f"precision={name}", *override(precision=name, amp_dtype=dt))
-                if ms < best_ms:
-                    best_ms, best = ms, {"precision": name}
-        if fused:
-            from .kernels import available
-            if available():
-                from .kernels.apply import enable, revert
-                memo = {}
-
-                def fuse():
-                    memo["already"] = any(getattr(m, "_fm_norm", False) or getattr(m, "_fm_mlp", False)
-                                          for m in target.raw_model.modules())
-                    enable(target.raw_model)
-
-                def unfuse():
-                    if not memo.get("already"):
-                        revert(target.raw_model)
-                ms = measure("fused_kernels=on", fuse, unfuse, note="rmsnorm+swiglu kernels")
-                if ms < best_ms:
-                    best_ms, best = ms, {"fused_ops": True}
-        if accum and getattr(target, "accum", 1) > 1:
-            ms = measure("accum=1 (per-micro-batch cost)", *override(accum=1, micro=0))
-            if ms and ms < best_ms:
-                best_ms, best = ms, {"accum": 1}
+    if live_forge:
+        for knob in _forge_knobs(target, precision, fused, accum):
+            took = clock(knob.label, target, knob.note, scope=knob)
+            if took < lead_ms:
+                lead_ms, lead = took, dict(knob.result)
 
     if build is not None:
-        variants = ([("bf16", {"bf16": True})] if precision else []) + [("ac=full", {"ac": "full"})]
+        rebuilds = []
+        if precision:
+            rebuilds.append({"bf16": True})
+        rebuilds.append({"ac": "full"})
         if compiled:
-            variants.append(("compile", {"compile": True}))
-        for label, over in variants:
+            rebuilds.append({"compile": True})
+        for knobs in rebuilds:
+            label = "rebuilt with " + ", ".join(f"{k}={v}" for k, v in knobs.items())
             try:
-                rebuilt = build(**over)
-            except BaseException as exc:      # noqa: BLE001
-                report.add(Trial(f"build {label}", ok=False, note=str(exc)[:60]))
+                fresh = build(**knobs)
+            except BaseException as err:  # noqa: BLE001
+                rep.add(Trial(label, ok=False, oom=_out_of_memory(err),
+                              note=" ".join(f"build failed: {err}".split())[:70]))
                 continue
-            ms = measure(f"{label} (rebuilt)", note=str(over), obj=rebuilt)
-            if ms < best_ms:
-                best_ms, best = ms, dict(over)
-            with contextlib.suppress(Exception):
-                if hasattr(rebuilt, "close"):
-                    rebuilt.close()
-            del rebuilt
-            if torch.cuda.is_available():
-                with contextlib.suppress(Exception):
-                    torch.cuda.empty_cache()
+            took = clock(label, fresh)
+            if took < lead_ms:
+                lead_ms, lead = took, dict(knobs)
+            closer = getattr(fresh, "close", None)
+            if callable(closer):
+                try:
+                    closer()
+                except Exception:  # noqa: BLE001
+                    pass
+            del fresh
+            _free_cached()
 
-    report.best = dict(best, ms=best_ms)
-    if apply and best:
-        for k, v in best.items():
-            setattr(target, k, v)
-    return report
+    rep.best = {**lead, "ms": lead_ms}
+    if apply:
+        for name, value in lead.items():
+            if name == "precision" and live_forge:
+                from .forge import _Amp
+                target.amp = _Amp(value, target.device)
+            setattr(target, name, value)
+    return rep
 
 
 def autotune_kernels(candidates=None, iters: int = 20, cache: bool = True) -> dict:
-    """Time the fused kernels on this GPU (``{"skipped": ...}`` without one). The kernels have no
-    launch parameters to sweep; the numbers are a health check and a baseline for comparisons."""
+    """Device timings (ms, fwd only) of the element-wise kernels at a 4096-wide model's shapes, or
+    ``{"skipped": reason}`` where they cannot run. ``candidates`` / ``cache`` are accepted for
+    compatibility: these kernels size their launch from the row width, there is nothing to search."""
     from . import kernels
     if not kernels.available():
-        return {"skipped": "needs a CUDA device of compute capability 10 and the native extension",
-                "device": str(torch.device("cpu"))}
-    d = 4096
-    x = torch.randn(8192, d, device="cuda", dtype=torch.bfloat16)
-    w = torch.randn(d, device="cuda")
-    gu = torch.randn(8192, 2 * 11008 // 16 * 16, device="cuda", dtype=torch.bfloat16)
-    out = {}
-    for name, fn in (("rms_norm", lambda: kernels.rms_norm(x, w, 1e-6)),
-                     ("swiglu_split", lambda: kernels.swiglu_split(gu))):
+        return {"skipped": "the sm_100a kernels need a compute-capability-10 GPU and the built extension",
+                "device": "cpu" if not torch.cuda.is_available() else torch.cuda.get_device_name()}
+    rows, width, hidden = 8192, 4096, 11008
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(rows, width, device="cuda", dtype=torch.bfloat16, generator=gen)
+    delta = torch.randn(rows, width, device="cuda", dtype=torch.bfloat16, generator=gen)
+    gain = torch.ones(width, device="cuda")
+    gate_up = torch.randn(rows, 2 * hidden, device="cuda", dtype=torch.bfloat16, generator=gen)
+    cases = {
+        "rms_norm": lambda: kernels.rms_norm(x, gain, 1e-6),
+        "add_rms_norm": lambda: kernels.add_rms_norm(x, delta, gain, 1e-6),
+        "swiglu_split": lambda: kernels.swiglu_split(gate_up),
+    }
+    result = {"device": torch.cuda.get_device_name(), "shapes": {"rows": rows, "dim": width, "hidden": hidden}}
+    for name, call in cases.items():
         try:
-            out[name] = {"ms": time_call(fn, warmup=3, repeats=iters)}
-        except Exception as exc:
-            out[name] = {"ms": float("nan"), "note": str(exc)[:80]}
-    out["device"] = torch.cuda.get_device_name()
-    return out
+            result[name] = {"ms": time_call(call, warmup=3, repeats=iters)}
+        except Exception as err:  # noqa: BLE001
+            result[name] = {"ms": float("nan"), "note": f"{err}"[:80]}
+    return result
 
 
 def _main(argv=None) -> int:
     import argparse
     from .forge import Forge
     from .models import GPT, GPTConfig
-    ap = argparse.ArgumentParser(description="autotune a training step on this device")
-    ap.add_argument("--preset", default="tiny")
+    ap = argparse.ArgumentParser(prog="python -m forgeminds_b200.autotune",
+                                 description="Time a small GPT training step under the cheap knobs of this library.")
+    ap.add_argument("--preset", default="tiny", choices=["tiny", "small", "medium"])
     ap.add_argument("--seq", type=int, default=128)
     ap.add_argument("--micro-batch", type=int, default=4)
-    ap.add_argument("--budget", type=float, default=60.0)
-    ap.add_argument("--apply", action="store_true")
-    ap.add_argument("--kernels", action="store_true")
-    a = ap.parse_args(argv)
-    if a.kernels:
-        print(json.dumps(autotune_kernels(), indent=1))
+    ap.add_argument("--budget", type=float, default=60.0, help="seconds")
+    ap.add_argument("--apply", action="store_true", help="keep the winning settings on the Forge object")
+    ap.add_argument("--kernels", action="store_true", help="only time the fused kernels")
+    opts = ap.parse_args(argv)
+    if opts.kernels:
+        print(json.dumps(autotune_kernels(), indent=2))
         return 0
-    dim = {"tiny": 128, "small": 256, "medium": 512}.get(a.preset, 128)
-    mc = GPTConfig(vocab_size=512, dim=dim, n_layers=4, n_heads=max(2, dim // 32), n_kv_heads=max(1, dim // 64),
-                   max_seq=a.seq)
-    forge = Forge(GPT(mc), None, precision="bf16" if torch.cuda.is_available() else "fp32",
-                  loss_fn=lambda out, b: out[0] if isinstance(out, (tuple, list)) else out)
-    x = torch.randint(0, mc.vocab_size, (a.micro_batch, a.seq))
-    y = torch.randint(0, mc.vocab_size, (a.micro_batch, a.seq))
-    print("fast defaults:", apply_fast_defaults())
-    rep = autotune(forge, [(x, y)], budget_s=a.budget, apply=a.apply)
+    width = {"tiny": 128, "small": 256, "medium": 512}[opts.preset]
+    mc = GPTConfig(vocab_size=512, dim=width, n_layers=4, n_heads=max(2, width // 32), n_kv_heads=max(1, width // 64),
+                   max_seq=opts.seq)
+    on_gpu = torch.cuda.is_available()
+    forge = Forge(GPT(mc), None, precision="bf16" if on_gpu else "fp32", quiet=True, async_batches=False,
+                  forward_fn=lambda m, b: m(b[0], labels=b[1]))
+    gen = torch.Generator().manual_seed(0)
+    tokens = torch.randint(0, mc.vocab_size, (opts.micro_batch, opts.seq + 1), generator=gen)
+    print("process defaults:", json.dumps(apply_fast_defaults()))
+    rep = autotune(forge, [(tokens[:, :-1], tokens[:, 1:])], budget_s=opts.budget, apply=opts.apply)
     print(rep.table())
-    print(f"baseline {rep.baseline_ms:.2f} ms -> best {rep.best.get('ms', 0):.2f} ms ({rep.speedup():.2f}x) {rep.best}")
+    print(f"baseline {rep.baseline_ms:.2f} ms; fastest {rep.best['ms']:.2f} ms "
+          f"({rep.speedup():.2f}x) with {({k: v for k, v in rep.best.items() if k != 'ms'}) or 'the baseline settings'}")
     return 0
 
 

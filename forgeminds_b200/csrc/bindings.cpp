@@ -478,6 +478,16 @@ void comm_adamw_push(Tensor& master, const Tensor& grad, Tensor& m, Tensor& v, c
      "comm_adamw_push");
 }
 
+void comm_push_cast(const Tensor& master, const std::vector<int64_t>& shadow_ptrs, const Tensor& off, const Tensor& len) {
+  PtrTable s(shadow_ptrs);
+  TORCH_CHECK(master.is_cuda() && master.scalar_type() == at::kFloat && off.is_cuda() && len.is_cuda() &&
+              off.scalar_type() == at::kLong && len.scalar_type() == at::kInt && off.numel() == len.numel(),
+              "push_cast: fp32 master, int64 offsets and int32 lengths on the device");
+  c10::cuda::CUDAGuard guard(master.device());
+  ok(fmb_comm_push_cast(master.data_ptr<float>(), s.p, s.world, reinterpret_cast<const long long*>(off.data_ptr<int64_t>()),
+                        len.data_ptr<int>(), static_cast<int>(off.numel()), cur_stream()), "comm_push_cast");
+}
+
 // Product with operands / output spread over the ranks (see fmb_gemm_bf16_peer). `gather` = 1 / 2: `a` / `b` is this
 // rank's full-size symmetric buffer of the gathered operand and `gather_ptrs` every rank's; `ready` holds one int
 // per 128 rows of it. With `d_ptrs`, `d` is this rank's bf16 staging buffer [world * rows_per_rank, N].
@@ -821,6 +831,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("comm_step_reduce", &comm_step_reduce);
   m.def("comm_adamw_push", &comm_adamw_push);
   m.def("comm_barrier", &comm_barrier);
+  m.def("comm_push_cast", &comm_push_cast);
   m.def("gemm_swiglu_fwd", &gemm_swiglu_fwd);
   m.def("gemm_swiglu_bwd", &gemm_swiglu_bwd);
   m.def("gemm_rowdot", &gemm_rowdot);

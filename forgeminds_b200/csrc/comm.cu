@@ -15,6 +15,8 @@
 //                        the device for the optimizer kernel
 //   adamw_push_kernel    AdamW on this rank's shard (chunk table: any mix of decay / no-decay runs)
 //                        whose bf16 result is stored straight into every rank's working weights
+//   push_cast_kernel     fp32 -> bf16 of a list of ranges into every rank's working weights (updates that
+//                        were computed by other kernels, e.g. Muon on the matrices this rank owns)
 //   barrier_kernel       all ranks have reached this point of their streams
 //
 // The reference gets these steps from FSDP2's NCCL reduce-scatter / all-gather, a foreach norm, a
@@ -187,6 +189,27 @@ adamw_push_kernel(float* __restrict__ master, const float* __restrict__ grad, fl
   }
 }
 
+// ------------------------------------------------------------------ push of updated weights (no optimizer math)
+// For updates computed elsewhere (Muon's orthogonalised step on the matrices this rank owns): chunk c covers
+// `len[c]` fp32 master elements (a multiple of 8) from flat offset `off[c]`; they are rounded to bf16 once and
+// stored at the same offset of every rank's working weights.
+__global__ void __launch_bounds__(256)
+push_cast_kernel(const float* __restrict__ master, Peers shadows, int world, const long long* __restrict__ off,
+                 const int* __restrict__ len) {
+  const long long o = off[blockIdx.x];
+  const int n = len[blockIdx.x];
+  for (int i = threadIdx.x * 8; i < n; i += 256 * 8) {
+    const float4 a = *reinterpret_cast<const float4*>(master + o + i);
+    const float4 b = *reinterpret_cast<const float4*>(master + o + i + 4);
+    uint4 w;
+    w.x = pack_bf16(a.x, a.y); w.y = pack_bf16(a.z, a.w);
+    w.z = pack_bf16(b.x, b.y); w.w = pack_bf16(b.z, b.w);
+#pragma unroll
+    for (int r = 0; r < MAX_PEERS; ++r)
+      if (r < world) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(shadows.p[r]) + o + i) = w;
+  }
+}
+
 __global__ void barrier_kernel(Peers flags, int slot, uint32_t epoch, int rank, int world,
                                unsigned long long timeout_ns, int* status) {
   signal_all(flags, slot, rank, world, epoch);
@@ -269,6 +292,16 @@ extern "C" int fmb_comm_adamw_push(float* master, const float* grad, float* m, f
     return -2;
   adamw_push_kernel<<<n_chunks, 256, 0, stream>>>(master, grad, m, v, s, world, off, soff, len, wd, lr, beta1, beta2,
                                                   eps, bc1, bc2, ctl);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int fmb_comm_push_cast(const float* master, const void* const* shadow_ptrs, int world, const long long* off,
+                                  const int* len, int n_chunks, cudaStream_t stream) {
+  Peers s;
+  if (!fill(s, shadow_ptrs, world) || master == nullptr) return -2;
+  if (n_chunks <= 0) return 0;
+  if (reinterpret_cast<uintptr_t>(master) & 15) return -2;
+  push_cast_kernel<<<n_chunks, 256, 0, stream>>>(master, s, world, off, len);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -153,6 +153,10 @@ int fmb_comm_adamw_push(float* master, const float* grad, float* m, float* v, co
                         int world, const long long* off, const long long* soff, const int* len, const float* wd,
                         int n_chunks, float lr, float beta1, float beta2, float eps, float bc1, float bc2,
                         const float* ctl, cudaStream_t stream);
+// fp32 master ranges (chunk table off/len on the device, len a multiple of 8) -> bf16 at the same offsets of every
+// rank's working-weight buffer.
+int fmb_comm_push_cast(const float* master, const void* const* shadow_ptrs, int world, const long long* off,
+                       const int* len, int n_chunks, cudaStream_t stream);
 int fmb_comm_adam_chunk(void);
 int fmb_comm_signal(const void* const* flag_ptrs, int slot, unsigned epoch, int rank, int world, cudaStream_t stream);
 // Product whose operands / output are spread over the ranks (gemm_sm100.cu): see the comment at the definition.

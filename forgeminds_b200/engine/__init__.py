@@ -11,8 +11,9 @@ from __future__ import annotations
 __all__ = ["choose", "flat_store_blockers"]
 
 
-def flat_store_blockers(cfg, model) -> list:
-    """Reasons (strings) why a run that uses the sm_100a block kernels still cannot use the flat-store engine."""
+def flat_store_blockers(cfg, model, kernels: bool = True) -> list:
+    """Reasons (strings) why a run cannot use the flat-store engine. ``kernels``: the blocks run on the
+    sm_100a kernels (false only when the engine is forced on for CPU tests)."""
     tc, pc, oc, qc = cfg.train, cfg.parallel, cfg.offload, cfg.quant
     why = []
     if oc.optimizer:
@@ -27,8 +28,11 @@ def flat_store_blockers(cfg, model) -> list:
         why.append(f"quant.mode={qc.mode!r} freezes the base weights")
     if pc.tp > 1 and isinstance(getattr(model, "_fm_tp", None), str):
         why.append("tensor parallelism fell back to DTensor")
-    if pc.ep > 1:
-        why.append("expert parallelism runs on the module engine")
+    if pc.ep > 1 and kernels and getattr(model, "_fm_ep", None) is None:
+        why.append("expert parallelism without the fused dispatch / combine kernels (parallel.fused_comm off, "
+                   "more than 8 ranks per group, or experts offloaded)")
+    if pc.ep > 1 and oc.experts:
+        why.append("offload.experts keeps the experts in host memory")
     return why
 
 
@@ -36,12 +40,15 @@ def choose(owner, model):
     """``FORGEMINDS_FLAT_ENGINE=1`` selects the flat-store engine even where the sm_100a kernels cannot
     run (CPU, Gloo): the blocks then run PyTorch operators, gradients are reduced with ``all_reduce``
     and the optimizer takes its PyTorch statement. The multi-process CPU tests use this to exercise
-    the engine's bookkeeping (bucket hooks under pipeline schedules, skip flags, checkpoints)."""
+    the engine's bookkeeping (bucket hooks under pipeline schedules, skip flags, checkpoints).
+    ``FORGEMINDS_FLAT_ENGINE=0`` keeps a run on the library engine (blocks still on the kernels), which is
+    how the GPU tests obtain the trajectory to compare with."""
     import os
     from .library import LibraryEngine
-    forced = os.environ.get("FORGEMINDS_FLAT_ENGINE") == "1" and hasattr(model, "layers")
-    if (owner.native or forced) and not owner.use_ds:
-        blockers = flat_store_blockers(owner.cfg, model)
+    switch = os.environ.get("FORGEMINDS_FLAT_ENGINE", "")
+    forced = switch == "1" and hasattr(model, "layers")
+    if (owner.native or forced) and not owner.use_ds and switch != "0":
+        blockers = flat_store_blockers(owner.cfg, model, kernels=bool(owner.native))
         if not blockers:
             from .native import NativeEngine
             return NativeEngine(owner, model)

@@ -35,7 +35,7 @@ from ..distributed import log
 from ..parallel.flat import BucketReducer, DpLayout, FlatAdamW, FlatParamStore
 
 
-PEER_MUON = False         # owner-computes Muon over peer memory (parallel/peer_muon.py)
+PEER_MUON = True          # owner-computes Muon over peer memory (parallel/peer_muon.py)
 
 
 def same_host(ctx) -> bool:
@@ -65,11 +65,21 @@ class NativeEngine:
         self.wide = ctx.world > ctx.dp_world            # model-parallel dimensions besides data parallelism
         self._sync_now = True
         self.muon = None
+        # expert parallelism: a rank's experts are its own -- their gradients already cover the tokens of the
+        # whole expert-parallel group and are only summed over the ranks that hold the same experts
+        self.edp_group, self.edp_size = None, 1
+        if pc.ep > 1:
+            for name, p in model.named_parameters():
+                if ".experts." in name:
+                    p._fm_local = True
+            if ctx.edp_group is not None and dist.get_world_size(ctx.edp_group) > 1:
+                self.edp_group, self.edp_size = ctx.edp_group, dist.get_world_size(ctx.edp_group)
         self.peer = self._try_peer(model, dp)
         if not self.peer:
             self.store = FlatParamStore(model, ctx.device, apart=self._apart())
             self.opt = FlatAdamW(self.store, lr=tc.lr, betas=tc.betas, eps=tc.eps, weight_decay=tc.weight_decay)
-            self.reducer = BucketReducer(self.store, ctx.dp_group, ctx.dp_world) if dp else None
+            self.reducer = BucketReducer(self.store, ctx.dp_group, ctx.dp_world, local_group=self.edp_group) \
+                if dp else None
             if tc.optimizer == "muon":
                 self.muon = owner._muon(model, tc)
         self._norm_sq = torch.zeros(1, dtype=torch.float32, device=ctx.device)
@@ -106,7 +116,7 @@ class NativeEngine:
         else:
             self.opt = PeerAdamW(self.store, lr=tc.lr, betas=tc.betas, eps=tc.eps, weight_decay=tc.weight_decay,
                                  scalars=self.sx)
-        self.reducer = PeerReducer(self.store)
+        self.reducer = PeerReducer(self.store, local_group=self.edp_group)
         return True
 
     def _hook_blocks(self, model) -> None:
@@ -114,14 +124,15 @@ class NativeEngine:
             return
         by_name = {b.name: b for b in self.store.buckets}
         for i, blk in enumerate(model.layers.values()):
-            bucket = by_name.get(f"block{i}")
-            if bucket is not None:
-                blk.register_full_backward_hook(self._on_block_done(bucket))
+            mine = [by_name[n] for n in (f"block{i}", f"experts{i}") if n in by_name]
+            if mine:
+                blk.register_full_backward_hook(self._on_block_done(mine))
 
-    def _on_block_done(self, bucket):
+    def _on_block_done(self, buckets):
         def fire(module, grad_in, grad_out):
             if self._sync_now:
-                self.reducer.launch(bucket)
+                for bucket in buckets:
+                    self.reducer.launch(bucket)
         return fire
 
     # ------------------------------------------------------------------ micro-batches
@@ -172,6 +183,15 @@ class NativeEngine:
                 sq = sq - r_sq * (1.0 - 1.0 / self.tp)
             sq = sq.clone()
             dist.all_reduce(sq, group=ctx.tp_group)
+        if self.pc.ep > 1 and ctx.world > 1:
+            # every expert-parallel rank holds different experts: their squares add up over the group
+            own = torch.zeros((), dtype=torch.float32, device=ctx.device)
+            for b in st.buckets:
+                if b.local:
+                    own = own + st.grad_sq_norm(self._rest_sq, st.bucket_view(st.grad, b))[0]
+            spread = own.clone()
+            dist.all_reduce(spread, group=ctx.ep_group)
+            sq = sq - own + spread
         if self.pc.pp > 1:
             sq = ctx.sum_over_pp(sq)
         norm = sq.clamp(min=0).sqrt()
@@ -192,9 +212,13 @@ class NativeEngine:
         early = not (tc.skip_spike_factor > 0)
         if self.peer:
             lay = self.layout
-            if self.wide or lay.replicas > 1:
+            if self.wide or lay.replicas > 1 or self.edp_size > 1:
                 f = 1.0 / lay.replicas
-                self.reducer.weigh({"*": f, "rest": f / self.tp})
+                factors = {"*": f, "rest": f / self.tp}
+                for b in self.store.buckets:
+                    if b.local:                      # as many copies as ranks holding the same experts
+                        factors[b.name] = 1.0 / self.edp_size
+                self.reducer.weigh(factors)
             weight = 1.0
             if self.wide:
                 # the kernel averages over the world: the ranks of the last stage hold the loss, once per

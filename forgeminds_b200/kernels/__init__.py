@@ -121,7 +121,10 @@ def qk_norm_rope(x: torch.Tensor, w: torch.Tensor, cos: torch.Tensor, sin: torch
 
 # ------------------------------------------------------------------------------ SwiGLU
 def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
-    """``silu(gate) * up``"""
+    """``silu(gate) * up`` for two tensors of the same shape (no broadcasting: a mismatch is almost
+    always a wiring mistake and would silently multiply the cost)."""
+    if gate.shape != up.shape:
+        raise ValueError(f"swiglu needs gate and up of one shape, got {tuple(gate.shape)} and {tuple(up.shape)}")
     if _use_ops() and gate.shape == up.shape and gate.dtype == up.dtype:
         from . import _ops
         return _ops.swiglu_op(gate, up)
@@ -136,6 +139,8 @@ def _swiglu_eager(gate, up):
 
 def swiglu_split(x: torch.Tensor) -> torch.Tensor:
     """``silu(x[..., :h]) * x[..., h:]`` for the output of a fused gate|up projection."""
+    if x.shape[-1] % 2:
+        raise ValueError(f"swiglu_split halves the last dimension into gate and up; it is odd here: {tuple(x.shape)}")
     if x.shape[-1] % 16 == 0 and fast_ok(x):
         return _fn().swiglu_split(x)
     return _ref.swiglu_split(x)

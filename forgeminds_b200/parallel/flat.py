@@ -39,6 +39,10 @@ class Bucket:
     params: list = field(default_factory=list)
     decay: list = field(default_factory=list)     # (offset_in_bucket, numel, weight_decay on/off)
     ready: "torch.cuda.Event | None" = None
+    local: bool = False         # parameters that only this rank holds (its experts): never reduced over the group,
+                                # optimizer state kept whole
+    moff: int = 0               # offset of this bucket's part of the optimizer moments (elements)
+    msize: int = 0              # its length: size / shard_world, or size for a local bucket
 
 
 def _round_up(n: int, m: int) -> int:
@@ -119,23 +123,30 @@ class FlatParamStore:
             if apart is not None:
                 moved += [p for p in ps if apart(p)]
                 ps = [p for p in ps if not apart(p)]
+            own = [p for p in ps if getattr(p, "_fm_local", False)]       # this rank's experts
+            ps = [p for p in ps if not getattr(p, "_fm_local", False)]
             if ps:
-                groups.append((f"block{i}", ps))
+                groups.append((f"block{i}", ps, False))
+            if own:
+                groups.append((f"experts{i}", own, True))
         rest = moved + [p for p in model.parameters() if p.requires_grad and id(p) not in seen]
         if rest:
-            groups.append(("rest", rest))
+            groups.append(("rest", rest, False))
         self.buckets: list = []
-        cursor = 0
-        for name, ps in groups:
-            b = Bucket(name=name, start=cursor, size=0, params=ps)
+        cursor = mcursor = 0
+        for name, ps, local in groups:
+            b = Bucket(name=name, start=cursor, size=0, params=ps, local=local)
             off = 0
             for p in ps:
                 b.decay.append((off, p.numel(), p.ndim >= 2))
                 off += _round_up(p.numel(), ALIGN)
-            b.size = _round_up(off, ALIGN * self.shard_world)
+            b.size = _round_up(off, ALIGN * (1 if local else self.shard_world))
+            b.moff, b.msize = mcursor, (b.size if local else b.size // self.shard_world)
             cursor += b.size
+            mcursor += b.msize
             self.buckets.append(b)
         self.total = cursor
+        self.moment_total = mcursor
         self.master = torch.zeros(self.total, dtype=torch.float32, device=self.device)
         if symm is not None:
             self.grad_symm = symm.alloc(self.total, torch.float32)
@@ -175,7 +186,9 @@ class FlatParamStore:
             p._fm_shadow = (p._fm_shadow[0], p._version)
 
     def shard_range(self, b: Bucket, rank: int):
-        """(flat offset, length) of ``rank``'s part of bucket ``b``."""
+        """(flat offset, length) of ``rank``'s part of bucket ``b`` (all of it for a local bucket)."""
+        if b.local:
+            return b.start, b.size
         n = b.size // self.shard_world
         return b.start + rank * n, n
 
@@ -188,9 +201,17 @@ class FlatParamStore:
         if self.symm is None or lay.shard_world == 1:
             return
         for b in self.buckets:
+            if b.local:
+                continue
             lo, n = self.shard_range(b, lay.shard_rank)
-            dist.all_gather_into_tensor(self.bucket_view(self.master, b), self.master[lo:lo + n].clone(),
-                                        group=lay.shard_group)
+            whole = self.bucket_view(self.master, b)
+            if all(self.shard_range(b, r)[1] == n for r in range(lay.shard_world)):
+                dist.all_gather_into_tensor(whole, self.master[lo:lo + n].clone(), group=lay.shard_group)
+            else:                      # shards of unequal length (cut along parameter boundaries): sum of disjoint parts
+                mine = self.master[lo:lo + n].clone()
+                whole.zero_()
+                self.master[lo:lo + n].copy_(mine)
+                dist.all_reduce(whole, group=lay.shard_group)
 
     def rebind(self) -> None:
         """Re-attach ``.grad`` views (something set them to ``None``)."""
@@ -231,7 +252,7 @@ class FlatAdamW(torch.optim.Optimizer):
                               {"params": rest, "weight_decay": 0.0}) if g["params"]]
         super().__init__(groups, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
         self.shard_rank, self.shard_world = shard_rank, shard_world
-        n = store.total // shard_world if shard_world > 1 else store.total
+        n = store.moment_total if shard_world > 1 else store.total
         dev = store.device
         self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
@@ -333,15 +354,30 @@ class BucketReducer:
     CPU runs and ``fused_comm=False``.
     """
 
-    def __init__(self, store: FlatParamStore, group, world: int):
+    def __init__(self, store: FlatParamStore, group, world: int, local_group=None):
+        """``local_group``: ranks that hold replicas of this rank's local buckets (the same expert shard in
+        other expert-parallel groups), or ``None`` when there are none."""
         self.store, self.group, self.world = store, group, world
+        self.local_group = local_group
         self.cuda = store.device.type == "cuda"
         self.stream = torch.cuda.Stream(device=store.device) if self.cuda else None
         self._launched: list = []
         self.enabled = True
 
+    def _finish_local(self, b: Bucket) -> None:
+        """A bucket that only this rank (and its replicas) holds already sums the tokens of every rank that
+        routed to it: add the replicas, then scale like every other gradient (mean over the group)."""
+        view = self.store.bucket_view(self.store.grad, b)
+        if self.local_group is not None and dist.get_world_size(self.local_group) > 1:
+            dist.all_reduce(view, group=self.local_group)
+        view.div_(self.world)
+
     def launch(self, b: Bucket) -> None:
         if not self.enabled or self.world <= 1:
+            return
+        if b.local:
+            self._finish_local(b)
+            self._launched.append(b.name)
             return
         view = self.store.bucket_view(self.store.grad, b)
         if self.cuda:
@@ -360,7 +396,9 @@ class BucketReducer:
         self._launched.clear()
         if self.enabled and self.world > 1:
             for b in self.store.buckets:         # anything whose hook did not fire (unused parameters)
-                if b.name not in done:
+                if b.name not in done and b.local:
+                    self._finish_local(b)
+                elif b.name not in done:
                     view = self.store.bucket_view(self.store.grad, b)
                     if self.cuda:
                         dist.all_reduce(view, op=dist.ReduceOp.AVG, group=self.group)

@@ -42,9 +42,12 @@ BLOCKS_PER_BUCKET = 296          # grid of one bucket's pull-reduce (also its nu
 class PeerReducer:
     """Drop-in for :class:`BucketReducer` that runs step 1 above."""
 
-    def __init__(self, store: FlatParamStore):
+    def __init__(self, store: FlatParamStore, local_group=None):
+        """``local_group``: ranks holding replicas of this rank's local buckets (same experts, other
+        expert-parallel group); their gradients are summed with one ``all_reduce`` per bucket."""
         if store.symm is None:
             raise ValueError("PeerReducer needs a FlatParamStore built on a SymmGroup")
+        self.local_group = local_group
         self.store, self.sg = store, store.symm
         self.world = self.sg.world
         self.layout = store.layout
@@ -63,7 +66,11 @@ class PeerReducer:
         lo, n = st.shard_range(b, self.layout.shard_rank)
         part = self.partials[i * BLOCKS_PER_BUCKET:(i + 1) * BLOCKS_PER_BUCKET]
         slot = self.slot0 + i
-        if self.local_only:
+        if b.local and self.local_group is not None and dist.get_world_size(self.local_group) > 1:
+            dist.all_reduce(st.bucket_view(st.grad, b), group=self.local_group)
+        if self.local_only or b.local:
+            # this rank's memory only: scale, sum of squares (a local bucket holds the rank's own experts,
+            # whose gradient already covers the tokens of every rank that routed to them)
             C.comm_rs_reduce([st.grad_symm.ptrs[sg.rank]], lo, n, 1.0 / self.world, part, [sg.flags.ptrs[sg.rank]], slot,
                              sg.next_epoch(slot), 0, sg.timeout_ms, sg.status)
             return
@@ -128,23 +135,27 @@ class PeerAdamW(FlatAdamW):
     def _build_tables(self, wd: float):
         st, lay = self.store, self.layout
         chunk = int(ops.require().comm_adam_chunk())
-        off, soff, ln, wds = [], [], [], []
-        for b in st.buckets:
-            lo, n = st.shard_range(b, lay.shard_rank)
-            s_base = b.start // lay.shard_world
-            for seg_off, seg_n, dec in self._segments(b):
-                a = max(b.start + seg_off, lo)
-                e = min(b.start + seg_off + seg_n, lo + n)
-                while a < e:
-                    step = min(chunk, e - a)
-                    off.append(a)
-                    soff.append(s_base + (a - lo))
-                    ln.append(step)
-                    wds.append(wd if dec else 0.0)
-                    a += step
         dev = st.device
-        self._tables = (torch.tensor(off, dtype=torch.int64, device=dev), torch.tensor(soff, dtype=torch.int64, device=dev),
-                        torch.tensor(ln, dtype=torch.int32, device=dev), torch.tensor(wds, dtype=torch.float32, device=dev))
+        tables = []
+        for local in (False, True):            # shards whose result goes to every peer; buckets only this rank holds
+            off, soff, ln, wds = [], [], [], []
+            for b in st.buckets:
+                if b.local != local:
+                    continue
+                lo, n = st.shard_range(b, lay.shard_rank)
+                for seg_off, seg_n, dec in self._segments(b):
+                    a = max(b.start + seg_off, lo)
+                    e = min(b.start + seg_off + seg_n, lo + n)
+                    while a < e:
+                        step = min(chunk, e - a)
+                        off.append(a)
+                        soff.append(b.moff + (a - lo))
+                        ln.append(step)
+                        wds.append(wd if dec else 0.0)
+                        a += step
+            tables.append((torch.tensor(off, dtype=torch.int64, device=dev), torch.tensor(soff, dtype=torch.int64, device=dev),
+                           torch.tensor(ln, dtype=torch.int32, device=dev), torch.tensor(wds, dtype=torch.float32, device=dev)))
+        self._tables = tables
         self._tables_wd = wd
 
     # ------------------------------------------------------------------ step 2
@@ -189,15 +200,17 @@ class PeerAdamW(FlatAdamW):
         wd = max(float(g["weight_decay"]) for g in self.param_groups)
         if self._tables is None or self._tables_wd != wd:
             self._build_tables(wd)
-        off, soff, ln, wds = self._tables
         bc1, bc2 = 1 - b1 ** self.steps, 1 - b2 ** self.steps
-        ptrs = st.shadow_symm.ptrs
+        everyone = st.shadow_symm.ptrs
+        me = [everyone[sg.rank]]
         if self.local_only:
-            ptrs = [ptrs[sg.rank]]
+            everyone = me
         elif self.layout.replicas > 1:           # hybrid sharding: the other replicas compute the same shard themselves
-            ptrs = [ptrs[r] for r in self.layout.replica_peers()]
-        ops.require().comm_adamw_push(st.master, st.grad, self.exp_avg, self.exp_avg_sq, ptrs, off, soff,
-                                      ln, wds, lr, b1, b2, self.defaults["eps"], bc1, bc2, self.ctl)
+            everyone = [everyone[r] for r in self.layout.replica_peers()]
+        for (off, soff, ln, wds), ptrs in zip(self._tables, (everyone, me)):
+            if off.numel():
+                ops.require().comm_adamw_push(st.master, st.grad, self.exp_avg, self.exp_avg_sq, ptrs, off, soff,
+                                              ln, wds, lr, b1, b2, self.defaults["eps"], bc1, bc2, self.ctl)
         if not self.local_only:
             sg.barrier(self.slot_done)
         return None
@@ -213,8 +226,11 @@ class PeerAdamW(FlatAdamW):
         full_m = torch.zeros(st.total, dtype=torch.float32, device=st.device)
         full_v = torch.zeros(st.total, dtype=torch.float32, device=st.device)
         for b in st.buckets:
-            n = b.size // lay.shard_world
-            s0 = b.start // lay.shard_world
+            n, s0 = b.msize, b.moff
+            if b.local:
+                st.bucket_view(full_m, b).copy_(self.exp_avg[s0:s0 + n])
+                st.bucket_view(full_v, b).copy_(self.exp_avg_sq[s0:s0 + n])
+                continue
             dist.all_gather_into_tensor(st.bucket_view(full_m, b), self.exp_avg[s0:s0 + n], group=lay.shard_group)
             dist.all_gather_into_tensor(st.bucket_view(full_v, b), self.exp_avg_sq[s0:s0 + n], group=lay.shard_group)
         self._full = (full_m, full_v)
@@ -248,7 +264,7 @@ class PeerAdamW(FlatAdamW):
                 steps = max(steps, int(float(state["step"])))
         for b in st.buckets:
             lo, n = st.shard_range(b, lay.shard_rank)
-            s0 = b.start // lay.shard_world
+            s0 = b.moff
             self.exp_avg[s0:s0 + n].copy_(full_m[lo:lo + n])
             self.exp_avg_sq[s0:s0 + n].copy_(full_v[lo:lo + n])
         self.steps = steps

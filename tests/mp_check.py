@@ -272,6 +272,30 @@ def sc_flat_pp_dp(world):
         assert max(abs(a - b) for a, b in zip(losses[True], losses[False])) < 1e-4, losses
 
 
+def sc_flat_ep(world):
+    """Flat-store engine with expert parallelism: every rank's experts sit in buckets of their own that
+    are scaled, not reduced, and the run equals the library engine's (DDP that ignores the experts +
+    ``sync_expert_grads``)."""
+    losses, norms = {}, {}
+    for flat in (True, False):
+        os.environ["FORGEMINDS_FLAT_ENGINE"] = "1" if flat else "0"
+        cfg = _cfg(dp_replicate=world, ep=world)
+        cfg.train.grad_accum = 2
+        cfg.train.max_steps = 6
+        mc = _mc(n_experts=4, n_layers=2)
+        ds = fm.SyntheticLM(mc.vocab_size, mc.max_seq, n=1024)
+        tr = fm.Trainer(lambda ctx: fm.GPT(mc, fm.moe_kwargs(ctx, cfg)), cfg, ds, micro_batch=8)
+        assert (tr.eng.name == "native") == flat
+        if flat:
+            kinds = {b.name: b.local for b in tr.store.buckets}
+            assert kinds == {"block0": False, "experts0": True, "block1": False, "experts1": True, "rest": False}, kinds
+        hist = [tr.train_step() for _ in range(6)]
+        tr.close()
+        losses[flat], norms[flat] = [h["loss"] for h in hist], [h["grad_norm"] for h in hist]
+    assert max(abs(a - b) for a, b in zip(losses[True], losses[False])) < 1e-4, losses
+    assert max(abs(a - b) / b for a, b in zip(norms[True], norms[False])) < 1e-4, norms
+
+
 def sc_tp_ckpt(world):
     """Plain tensors that hold one tensor-parallel slice per rank are stored as one sharded tensor and
     come back slice by slice (what the fused tensor-parallel blocks rely on for their checkpoints)."""

@@ -499,6 +499,80 @@ def mesh_equiv():
         print("OK mesh_equiv", flush=True)
 
 
+def muon_peer():
+    """Owner-computes Muon over peer memory follows the replicated Muon (all_reduce of the gradients, every
+    rank orthogonalising a share), and its sharded momentum survives a checkpoint."""
+    import tempfile
+    rank, world, dev = _init()
+    box = [tempfile.mkdtemp() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    mc = fm.GPTConfig(vocab_size=512, dim=256, n_layers=2, n_heads=8, n_kv_heads=4, max_seq=128, ffn_hidden=512)
+    losses = {}
+
+    def build(fused, steps, resume=False):
+        cfg = fm.ForgeConfig()
+        cfg.parallel.dp_shard = world
+        cfg.parallel.fused_comm = fused
+        cfg.train.__dict__.update(max_steps=steps, grad_accum=2, lr=2e-3, warmup_steps=2, bf16=True, resume=resume,
+                                  log_every=1000, prefetch=False, ckpt_every=0, ckpt_dir=box[0], optimizer="muon")
+        return fm.Trainer(lambda ctx: fm.GPT(mc), cfg, fm.SyntheticLM(512, 128, n=512), micro_batch=4)
+
+    for fused in (True, False):
+        tr = build(fused, 10)
+        assert tr.peer == fused and (type(tr.opt).__name__ == "PeerMuon") == fused, type(tr.opt).__name__
+        if fused:
+            owned = torch.tensor([len(tr.opt._mine)], device=dev)
+            dist.all_reduce(owned)
+            n_mat = sum(1 for n, p in tr.raw.named_parameters() if p.ndim >= 2 and "layers." in n)
+            assert owned.item() == n_mat, (owned.item(), n_mat)          # every matrix has exactly one owner
+        hist = [tr.train_step() for _ in range(6)]
+        if fused:
+            tr.save()
+            again = build(True, 10, resume=True)
+            assert again.step == 6
+            a, b = tr.train_step(), again.train_step()
+            assert abs(a["loss"] - b["loss"]) < 2e-3, (a["loss"], b["loss"])
+            a, b = tr.train_step(), again.train_step()                  # ... and so did the momentum
+            assert abs(a["loss"] - b["loss"]) < 4e-3, (a["loss"], b["loss"])
+            again.close()
+        tr.close()
+        losses[fused] = [h["loss"] for h in hist]
+        assert all(h["skipped"] == 0 for h in hist)
+    a, b = losses[True], losses[False]
+    assert a[-1] < 0.9 * a[0], a
+    assert max(abs(x - y) for x, y in zip(a, b)) < 0.03, (a, b)
+    if rank == 0:
+        print("OK muon_peer", flush=True)
+
+
+def ep_trainer():
+    """Expert parallelism on the flat-store engine (experts in rank-local buckets, dense gradients through
+    the peer reduce-scatter) follows the module engine (DDP that skips the experts + torch AdamW)."""
+    rank, world, dev = _init()
+    out = {}
+    for flat in (True, False):
+        os.environ["FORGEMINDS_FLAT_ENGINE"] = "" if flat else "0"
+        cfg = fm.ForgeConfig()
+        cfg.parallel.__dict__.update(dp_replicate=world, ep=world)
+        cfg.train.__dict__.update(max_steps=8, grad_accum=2, lr=2e-3, warmup_steps=2, bf16=True, resume=False,
+                                  log_every=1000, prefetch=False, ckpt_every=0)
+        mc = fm.GPTConfig(vocab_size=512, dim=256, n_layers=2, n_heads=8, n_kv_heads=4, max_seq=128, ffn_hidden=512,
+                          n_experts=2 * world, top_k=2, z_coef=0.0)
+        tr = fm.Trainer(lambda ctx: fm.GPT(mc, fm.moe_kwargs(ctx, cfg)), cfg, fm.SyntheticLM(512, 128, n=512), micro_batch=4)
+        assert (tr.eng.name == "native") == flat and tr.peer == flat, (tr.eng.name, tr.peer)
+        assert getattr(tr.raw, "_fm_ep", None) is not None
+        hist = tr.fit()
+        tr.close()
+        out[flat] = ([h["loss"] for h in hist], [h["grad_norm"] for h in hist])
+    os.environ.pop("FORGEMINDS_FLAT_ENGINE", None)
+    (la, na), (lb, nb) = out[True], out[False]
+    assert la[-1] < 0.9 * la[0], la
+    assert abs(na[0] - nb[0]) < 2e-2 * nb[0], (na, nb)                       # same gradient before the first update
+    assert max(abs(x - y) for x, y in zip(la, lb)) < 0.03, (la, lb)
+    if rank == 0:
+        print("OK ep_trainer", flush=True)
+
+
 def _mesh_run(world, rank, label, steps=8, quant="none", optimizer="adamw", **par):
     cfg = fm.ForgeConfig()
     cfg.parallel.__dict__.update(par)

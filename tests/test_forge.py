@@ -117,3 +117,17 @@ def test_loss_extraction_rules():
     with pytest.raises(ValueError):
         fm.Forge(_model(), None, offload="everything")
     assert "Forge(" in repr(f)
+
+
+def test_launch_spawns_ranks_that_train_identical_replicas():
+    """``fm.launch(nproc=2)`` on CPU: see tests/forge_mp_check.py."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1")
+    for k in ("WORLD_SIZE", "RANK", "LOCAL_RANK", "MASTER_PORT"):
+        env.pop(k, None)
+    out = subprocess.run([sys.executable, os.path.join(here, "forge_mp_check.py"), "29643"], capture_output=True,
+                         text=True, timeout=300, env=env)
+    assert out.returncode == 0 and "FORGE_MP_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-4000:]

@@ -67,6 +67,16 @@ def test_every_mesh_matches_the_whole_fp32_model():
 
 
 @needs2
+def test_owner_computes_muon_over_peer_memory():
+    _run("muon_peer", RANKS, 29620, timeout=600)
+
+
+@needs2
+def test_expert_parallel_trainer_on_the_flat_engine():
+    _run("ep_trainer", RANKS, 29621, timeout=600)
+
+
+@needs2
 def test_mesh_and_feature_combinations_train():
     _run("mesh_smoke", RANKS, 29618, timeout=900)
 

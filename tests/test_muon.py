@@ -92,3 +92,110 @@ def test_bucketed_equals_per_matrix_and_trains():
         loss.backward()
         opt.step()
     assert loss.item() < 0.7 * first
+
+
+# ------------------------------------------------------------------ the published Muon recipe as an oracle
+# Keller Jordan's reference optimizer (github.com/KellerJordan/Muon, MIT licence), restated here from its
+# public description: quintic Newton-Schulz with coefficients (3.4445, -4.7750, 2.0315) on the matrix scaled
+# to unit Frobenius norm, iterated on the wide orientation; momentum as an exponential average; Nesterov
+# blend; update scaled by sqrt(max(1, rows / cols)); decoupled weight decay.
+def _kj_orthogonalize(G, steps):
+    a, b, c = 3.4445, -4.7750, 2.0315
+    X = G.clone()
+    tall = G.size(-2) > G.size(-1)
+    if tall:
+        X = X.mT
+    X = X / (X.norm(dim=(-2, -1), keepdim=True) + 1e-7)
+    for _ in range(steps):
+        A = X @ X.mT
+        B = b * A + c * A @ A
+        X = a * X + B @ X
+    return X.mT if tall else X
+
+
+def _kj_update(grad, momentum, beta=0.95, ns_steps=5, nesterov=True):
+    momentum.lerp_(grad, 1 - beta)
+    direction = grad.lerp(momentum, beta) if nesterov else momentum
+    update = _kj_orthogonalize(direction, ns_steps)
+    return update * max(1, grad.size(-2) / grad.size(-1)) ** 0.5
+
+
+class _KJMuon:
+    def __init__(self, params, lr, weight_decay, momentum=0.95):
+        self.params, self.lr, self.wd, self.mu = list(params), lr, weight_decay, momentum
+        self.bufs = [torch.zeros_like(p) for p in self.params]
+
+    @torch.no_grad()
+    def step(self):
+        for p, buf in zip(self.params, self.bufs):
+            update = _kj_update(p.grad, buf, beta=self.mu)
+            p.mul_(1 - self.lr * self.wd)
+            p.add_(update.reshape(p.shape), alpha=-self.lr)
+
+
+@pytest.mark.parametrize("shape", [(24, 8), (8, 24), (16, 16)])
+def test_matches_the_published_recipe_over_several_steps(shape):
+    torch.manual_seed(3)
+    ours = nn.Parameter(torch.randn(*shape))
+    theirs = nn.Parameter(ours.detach().clone())
+    a = fm.Muon([ours], lr=0.02, weight_decay=0.05, ns_dtype=torch.float32)
+    b = _KJMuon([theirs], lr=0.02, weight_decay=0.05)
+    for k in range(4):
+        g = torch.randn(*shape, generator=torch.Generator().manual_seed(10 + k))
+        ours.grad, theirs.grad = g.clone(), g.clone()
+        a.step()
+        b.step()
+        assert torch.allclose(ours, theirs, atol=2e-5), (k, (ours - theirs).abs().max())
+    assert torch.allclose(a.state[ours]["momentum_buffer"], b.bufs[0], atol=1e-6)
+
+
+def test_newton_schulz_pushes_singular_values_towards_one():
+    torch.manual_seed(0)
+    g = torch.randn(48, 32)
+    s = torch.linalg.svdvals(newton_schulz(g, 5, torch.float32))
+    assert s.min() > 0.6 and s.max() < 1.25, (s.min(), s.max())          # the quintic's fixed band around 1
+    assert torch.allclose(newton_schulz(g, 5, torch.float32), _kj_orthogonalize(g, 5), atol=1e-5)
+
+
+def test_bf16_iteration_stays_close_to_fp32():
+    torch.manual_seed(1)
+    g = torch.randn(4, 32, 64)
+    lo = newton_schulz(g, 5, torch.bfloat16).float()
+    hi = newton_schulz(g, 5, torch.float32)
+    assert (lo - hi).norm() / hi.norm() < 0.05
+
+
+def test_device_side_skip_and_clip(monkeypatch):
+    """``step(ctl=...)``: gradients are scaled by ctl[0]; with ctl[1] = 0 nothing moves, even when the
+    gradient is not finite."""
+    torch.manual_seed(0)
+    w, v = nn.Parameter(torch.randn(8, 16)), nn.Parameter(torch.randn(16))
+    opt = fm.Muon([w, v], lr=0.05, ns_dtype=torch.float32)
+    w.grad, v.grad = torch.randn(8, 16), torch.randn(16)
+    opt.step(ctl=torch.tensor([1.0, 1.0]))
+    snap = [t.clone() for t in (w, v, opt.state[w]["momentum_buffer"], opt.state[v]["exp_avg"])]
+    w.grad, v.grad = torch.full((8, 16), float("nan")), torch.full((16,), float("inf"))
+    opt.step(ctl=torch.tensor([1.0, 0.0]))
+    now = (w, v, opt.state[w]["momentum_buffer"], opt.state[v]["exp_avg"])
+    assert all(torch.equal(a, b.detach()) for a, b in zip(snap, now))
+    # a clip coefficient scales what the AdamW group sees exactly like scaling its gradient would
+    a, b = nn.Parameter(torch.ones(16)), nn.Parameter(torch.ones(16))
+    oa, ob = fm.Muon([a], lr=0.05), fm.Muon([b], lr=0.05)
+    g = torch.randn(16)
+    a.grad, b.grad = g.clone(), g * 0.25
+    oa.step(ctl=torch.tensor([0.25, 1.0]))
+    ob.step()
+    assert torch.allclose(a, b, atol=1e-7) and torch.allclose(oa.state[a]["exp_avg"], ob.state[b]["exp_avg"])
+
+
+def test_two_ranks_share_the_newton_schulz_work():
+    """2 Gloo ranks under torchrun: see tests/muon_mp_check.py."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29644", os.path.join(here, "muon_mp_check.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert out.returncode == 0 and "MUON_MP_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-4000:]

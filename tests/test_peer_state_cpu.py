@@ -116,7 +116,8 @@ def test_chunk_tables_cover_the_shard_once_with_the_right_decay(two_ranks, monke
     monkeypatch.setattr(P.ops, "require", lambda: FakeC)
     for r, o in enumerate(opts):
         o._build_tables(0.1)
-        off, soff, ln, wd = (t.tolist() for t in o._tables)
+        assert o._tables[1][0].numel() == 0          # no rank-local buckets in a dense model
+        off, soff, ln, wd = (t.tolist() for t in o._tables[0])
         seen = torch.zeros(o.store.total, dtype=torch.int32)
         for a, s, n, w in zip(off, soff, ln, wd):
             assert n % 8 == 0 and 0 < n <= 4096
