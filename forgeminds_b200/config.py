@@ -35,7 +35,8 @@ class ParallelConfig:
     ds_extra: dict = field(default_factory=dict)
     # ---- additions of this library
     fused_comm: bool = True            # use the peer-memory kernels (falls back to torch.distributed when unavailable)
-    fsdp_resident_bytes: int = 64 << 30  # keep gathered bf16 weights resident when the model is smaller than this
+    fsdp_resident_bytes: int = 0       # memory the flat-store engine may use for parameters, gradients and optimizer
+                                       # state on one GPU (0: 80 % of the device); bigger models go to FSDP2
     comm_timeout_ms: int = 10000       # bound of every device-side wait on a peer flag
 
 

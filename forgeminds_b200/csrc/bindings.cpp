@@ -431,11 +431,17 @@ unsigned long long to_ns(double ms) { return static_cast<unsigned long long>(ms 
 
 void comm_rs_reduce(const std::vector<int64_t>& grad_ptrs, int64_t lo, int64_t n, double scale, Tensor& partial,
                     const std::vector<int64_t>& flag_ptrs, int64_t slot, int64_t epoch, int64_t rank, double timeout_ms,
-                    Tensor& status) {
+                    Tensor& status, const c10::optional<Tensor>& dst) {
   PtrTable g(grad_ptrs), f(flag_ptrs);
   TORCH_CHECK(g.world == f.world && partial.is_cuda() && partial.scalar_type() == at::kFloat);
+  float* out = nullptr;
+  if (dst.has_value() && dst->defined()) {
+    TORCH_CHECK(dst->is_cuda() && dst->scalar_type() == at::kFloat && dst->is_contiguous() && dst->numel() >= n,
+                "rs_reduce: dst must be a contiguous fp32 CUDA tensor of at least n elements");
+    out = dst->data_ptr<float>();
+  }
   c10::cuda::CUDAGuard guard(partial.device());
-  ok(fmb_comm_rs_reduce(g.p, lo, n, static_cast<float>(scale), partial.data_ptr<float>(),
+  ok(fmb_comm_rs_reduce(g.p, lo, n, static_cast<float>(scale), out, partial.data_ptr<float>(),
                         static_cast<int>(partial.numel()), f.p, static_cast<int>(slot), static_cast<unsigned>(epoch),
                         static_cast<int>(rank), g.world, to_ns(timeout_ms), status.data_ptr<int>(), cur_stream()),
      "comm_rs_reduce");
@@ -461,7 +467,8 @@ void comm_step_reduce(const Tensor& partial, const c10::optional<Tensor>& extra_
 
 void comm_adamw_push(Tensor& master, const Tensor& grad, Tensor& m, Tensor& v, const std::vector<int64_t>& shadow_ptrs,
                      const Tensor& off, const Tensor& soff, const Tensor& len, const Tensor& wd, double lr,
-                     double beta1, double beta2, double eps, double bc1, double bc2, const Tensor& ctl) {
+                     double beta1, double beta2, double eps, double bc1, double bc2, const Tensor& ctl,
+                     bool grad_compact) {
   PtrTable s(shadow_ptrs);
   TORCH_CHECK(master.scalar_type() == at::kFloat && grad.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat &&
               v.scalar_type() == at::kFloat, "adamw_push: fp32 state required");
@@ -474,7 +481,8 @@ void comm_adamw_push(Tensor& master, const Tensor& grad, Tensor& m, Tensor& v, c
                          reinterpret_cast<const long long*>(soff.data_ptr<int64_t>()), len.data_ptr<int>(),
                          wd.data_ptr<float>(), static_cast<int>(off.numel()), static_cast<float>(lr),
                          static_cast<float>(beta1), static_cast<float>(beta2), static_cast<float>(eps),
-                         static_cast<float>(bc1), static_cast<float>(bc2), ctl.data_ptr<float>(), cur_stream()),
+                         static_cast<float>(bc1), static_cast<float>(bc2), ctl.data_ptr<float>(),
+                         grad_compact ? 1 : 0, cur_stream()),
      "comm_adamw_push");
 }
 
@@ -827,11 +835,23 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sum_f32", &sum_f32);
   m.def("adamw_flat", &adamw_flat);
   m.def("sqnorm", &sqnorm);
-  m.def("comm_rs_reduce", &comm_rs_reduce);
+  m.def("comm_rs_reduce", &comm_rs_reduce, py::arg("grad_ptrs"), py::arg("lo"), py::arg("n"), py::arg("scale"),
+        py::arg("partial"), py::arg("flag_ptrs"), py::arg("slot"), py::arg("epoch"), py::arg("rank"),
+        py::arg("timeout_ms"), py::arg("status"), py::arg("dst") = c10::optional<Tensor>());
   m.def("comm_step_reduce", &comm_step_reduce);
-  m.def("comm_adamw_push", &comm_adamw_push);
+  m.def("comm_adamw_push", &comm_adamw_push, py::arg("master"), py::arg("grad"), py::arg("m"), py::arg("v"),
+        py::arg("shadow_ptrs"), py::arg("off"), py::arg("soff"), py::arg("len"), py::arg("wd"), py::arg("lr"),
+        py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("bc1"), py::arg("bc2"), py::arg("ctl"),
+        py::arg("grad_compact") = false);
   m.def("comm_barrier", &comm_barrier);
   m.def("comm_push_cast", &comm_push_cast);
+  m.def("debug_bounds", []() { return fmb_debug_bounds_enabled() != 0; });
+  m.def("debug_register", [](int64_t base, int64_t bytes, Tensor& status) {
+    c10::cuda::CUDAGuard guard(status.device());
+    const int rc = fmb_debug_register_extent(reinterpret_cast<const void*>(base), static_cast<unsigned long long>(bytes),
+                                             status.data_ptr<int>());
+    TORCH_CHECK(rc == 0, "forgeminds_b200: debug_register failed with code ", rc);
+  });
   m.def("gemm_swiglu_fwd", &gemm_swiglu_fwd);
   m.def("gemm_swiglu_bwd", &gemm_swiglu_bwd);
   m.def("gemm_rowdot", &gemm_rowdot);

@@ -54,57 +54,74 @@ def _run(cmd, log_path=None):
     return proc.stdout
 
 
-def build(verbose: bool = False, force: bool = False) -> Path:
+DEBUG_TARGET = PKG / "_C_debug.so"
+DEBUG_SOURCES = ("comm", "moe_ep", "gemm_sm100")       # the translation units with peer-memory accesses
+
+
+def build(verbose: bool = False, force: bool = False, debug_bounds: bool = False) -> Path:
+    """``debug_bounds=True`` builds ``_C_debug.so`` instead: the same library with ``-DFMB_DEBUG_BOUNDS`` in the
+    translation units that touch peer memory (every such access is checked against the registered buffers and
+    skipped, with an error code in the status word, when it lies outside). ``FORGEMINDS_DEBUG_SO=1`` makes the
+    package load that library."""
     import torch
     from torch.utils import cpp_extension as ce
 
     OBJ.mkdir(exist_ok=True)
+    target = DEBUG_TARGET if debug_bounds else TARGET
+    module = "_C_debug" if debug_bounds else "_C"
     headers = sorted(HERE.glob("*.cuh")) + sorted(HERE.glob("*.h"))
     hdr_sig = _digest(headers, " ".join(NVCC_FLAGS) + torch.__version__)
     cuda_inc = str(_cuda_home() / "include")
     jobs = []
     objects = []
     for src in sorted(HERE.glob("*.cu")):
+        checked = debug_bounds and src.stem in DEBUG_SOURCES
+        stem = src.stem + (".dbg" if checked else "")
         sig = _digest([src], hdr_sig)
-        obj = OBJ / f"{src.stem}.{sig}.o"
+        obj = OBJ / f"{stem}.{sig}.o"
         objects.append(obj)
         if obj.exists() and not force:
             continue
-        for stale in OBJ.glob(f"{src.stem}.*.o"):
-            stale.unlink()
-        jobs.append(([_nvcc(), *NVCC_FLAGS, "-I", str(HERE), "-c", str(src), "-o", str(obj)],
-                     OBJ / f"{src.stem}.log"))
+        for stale in OBJ.glob(f"{stem}.*.o"):
+            if checked or ".dbg." not in stale.name:
+                stale.unlink()
+        extra = ["-DFMB_DEBUG_BOUNDS"] if checked else []
+        jobs.append(([_nvcc(), *NVCC_FLAGS, *extra, "-I", str(HERE), "-c", str(src), "-o", str(obj)],
+                     OBJ / f"{stem}.log"))
     torch_inc = [f"-I{p}" for p in ce.include_paths()]
     py_inc = f"-I{sysconfig.get_paths()['include']}"
     for src in sorted(HERE.glob("*.cpp")):
+        named = src.stem == "bindings" and debug_bounds          # the module's init symbol carries its name
+        stem = src.stem + (".dbg" if named else "")
         sig = _digest([src], hdr_sig)
-        obj = OBJ / f"{src.stem}.{sig}.o"
+        obj = OBJ / f"{stem}.{sig}.o"
         objects.append(obj)
         if obj.exists() and not force:
             continue
-        for stale in OBJ.glob(f"{src.stem}.*.o"):
-            stale.unlink()
+        for stale in OBJ.glob(f"{stem}.*.o"):
+            if named or ".dbg." not in stale.name:
+                stale.unlink()
         abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
-        jobs.append((["g++", *CXX_FLAGS, f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-DTORCH_EXTENSION_NAME=_C",
+        jobs.append((["g++", *CXX_FLAGS, f"-D_GLIBCXX_USE_CXX11_ABI={abi}", f"-DTORCH_EXTENSION_NAME={module}",
                       "-DTORCH_API_INCLUDE_EXTENSION_H", f"-I{HERE}", f"-I{cuda_inc}", py_inc, *torch_inc,
-                      "-c", str(src), "-o", str(obj)], OBJ / f"{src.stem}.log"))
+                      "-c", str(src), "-o", str(obj)], OBJ / f"{stem}.log"))
     if jobs:
         with cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
             for out in pool.map(lambda j: _run(*j), jobs):
                 if verbose:
                     print(out)
-    stamp = OBJ / "link.sig"
+    stamp = OBJ / ("link.dbg.sig" if debug_bounds else "link.sig")
     link_sig = _digest(objects)
-    if force or jobs or not TARGET.exists() or not stamp.exists() or stamp.read_text() != link_sig:
+    if force or jobs or not target.exists() or not stamp.exists() or stamp.read_text() != link_sig:
         lib_dirs = ce.library_paths()
         cuda_lib = str(_cuda_home() / "lib64")
-        cmd = ["g++", "-shared", "-o", str(TARGET), *map(str, objects)]
+        cmd = ["g++", "-shared", "-o", str(target), *map(str, objects)]
         for d in [*lib_dirs, cuda_lib]:
             cmd += [f"-L{d}", f"-Wl,-rpath,{d}"]
         cmd += ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python", "-lcudart"]
-        _run(cmd, OBJ / "link.log")
+        _run(cmd, OBJ / ("link.dbg.log" if debug_bounds else "link.log"))
         stamp.write_text(link_sig)
-    return TARGET
+    return target
 
 
 def ptxas_report() -> str:
@@ -116,5 +133,5 @@ def ptxas_report() -> str:
 
 
 if __name__ == "__main__":
-    path = build(verbose="-v" in sys.argv, force="--force" in sys.argv)
+    path = build(verbose="-v" in sys.argv, force="--force" in sys.argv, debug_bounds="--debug-bounds" in sys.argv)
     print(path)

@@ -32,8 +32,9 @@ namespace fmb {
 
 // ------------------------------------------------------------------ reduce-scatter (pull) + sum of squares
 __global__ void __launch_bounds__(256)
-rs_reduce_kernel(Peers grads, long long lo, long long n, float scale, float* __restrict__ partial, Peers flags,
-                 int slot, uint32_t epoch, int rank, int world, unsigned long long timeout_ns, int* status) {
+rs_reduce_kernel(Peers grads, long long lo, long long n, float scale, float* __restrict__ dst,
+                 float* __restrict__ partial, Peers flags, int slot, uint32_t epoch, int rank, int world,
+                 unsigned long long timeout_ns, int* status) {
   __shared__ float red[8];
   if (blockIdx.x == 0) signal_all(flags, slot, rank, world, epoch);     // my bucket is complete (stream order)
   if (!wait_all(flags, slot, rank, world, epoch, timeout_ns, status)) {
@@ -43,8 +44,10 @@ rs_reduce_kernel(Peers grads, long long lo, long long n, float scale, float* __r
   float s = 0.f;
   const long long nvec = n >> 2;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  float* mine = static_cast<float*>(grads.p[rank]) + lo;
-  const bool store = world > 1 || scale != 1.f;
+  // `dst` (a compact buffer of n floats) takes the result when several ranks reduce the SAME range (the replicas
+  // of a hybrid-sharded group): storing in place would change what the other replica is still reading
+  float* mine = dst != nullptr ? dst : static_cast<float*>(grads.p[rank]) + lo;
+  const bool store = dst != nullptr || world > 1 || scale != 1.f;
   long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (world <= 2) {
     // few sources: four vectors per source in flight per thread, or the loads cannot cover the latency
@@ -60,7 +63,7 @@ rs_reduce_kernel(Peers grads, long long lo, long long n, float scale, float* __r
         float4 a = v[u][0];
         if (world > 1) { a.x += v[u][1].x; a.y += v[u][1].y; a.z += v[u][1].z; a.w += v[u][1].w; }
         a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
-        if (store) reinterpret_cast<float4*>(mine)[i + u * stride] = a;
+        if (store && addr_ok(reinterpret_cast<float4*>(mine) + i + u * stride, 16)) reinterpret_cast<float4*>(mine)[i + u * stride] = a;
         s += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
       }
     }
@@ -75,7 +78,7 @@ rs_reduce_kernel(Peers grads, long long lo, long long n, float scale, float* __r
     for (int r = 1; r < MAX_PEERS; ++r)
       if (r < world) { a.x += v[r].x; a.y += v[r].y; a.z += v[r].z; a.w += v[r].w; }
     a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
-    if (store) reinterpret_cast<float4*>(mine)[i] = a;
+    if (store && addr_ok(reinterpret_cast<float4*>(mine) + i, 16)) reinterpret_cast<float4*>(mine)[i] = a;
     s += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
   }
 #pragma unroll
@@ -145,11 +148,12 @@ adamw_push_kernel(float* __restrict__ master, const float* __restrict__ grad, fl
                   float* __restrict__ v, Peers shadows, int world, const long long* __restrict__ off,
                   const long long* __restrict__ soff, const int* __restrict__ len, const float* __restrict__ wd,
                   float lr, float beta1, float beta2, float eps, float bc1, float bc2,
-                  const float* __restrict__ ctl) {
+                  const float* __restrict__ ctl, int grad_compact) {
   const float clip = ctl[0];
   if (!(ctl[1] > 0.5f)) return;
   const int c = blockIdx.x;
   const long long o = off[c], so = soff[c];
+  const long long go = grad_compact ? so : o;      // reduced gradients laid out like the moments (see rs_reduce dst)
   const int n = len[c];
   const float step = lr / bc1;
   const float inv_sqrt_bc2 = rsqrtf(bc2);
@@ -159,7 +163,7 @@ adamw_push_kernel(float* __restrict__ master, const float* __restrict__ grad, fl
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const float4 pv = *reinterpret_cast<const float4*>(master + o + i + h * 4);
-      const float4 gv = *reinterpret_cast<const float4*>(grad + o + i + h * 4);
+      const float4 gv = *reinterpret_cast<const float4*>(grad + go + i + h * 4);
       const float4 mv = *reinterpret_cast<const float4*>(m + so + i + h * 4);
       const float4 vv = *reinterpret_cast<const float4*>(v + so + i + h * 4);
       pe[h * 4 + 0] = pv.x; pe[h * 4 + 1] = pv.y; pe[h * 4 + 2] = pv.z; pe[h * 4 + 3] = pv.w;
@@ -185,7 +189,8 @@ adamw_push_kernel(float* __restrict__ master, const float* __restrict__ grad, fl
     w.z = pack_bf16(pe[4], pe[5]); w.w = pack_bf16(pe[6], pe[7]);
 #pragma unroll
     for (int r = 0; r < MAX_PEERS; ++r)
-      if (r < world) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(shadows.p[r]) + o + i) = w;
+      if (r < world && addr_ok(static_cast<__nv_bfloat16*>(shadows.p[r]) + o + i, 16))
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(shadows.p[r]) + o + i) = w;
   }
 }
 
@@ -206,7 +211,8 @@ push_cast_kernel(const float* __restrict__ master, Peers shadows, int world, con
     w.z = pack_bf16(b.x, b.y); w.w = pack_bf16(b.z, b.w);
 #pragma unroll
     for (int r = 0; r < MAX_PEERS; ++r)
-      if (r < world) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(shadows.p[r]) + o + i) = w;
+      if (r < world && addr_ok(static_cast<__nv_bfloat16*>(shadows.p[r]) + o + i, 16))
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(shadows.p[r]) + o + i) = w;
   }
 }
 
@@ -256,14 +262,15 @@ static bool fill(Peers& t, const void* const* ptrs, int world) {
 
 using namespace fmb;
 
-extern "C" int fmb_comm_rs_reduce(const void* const* grad_ptrs, long long lo, long long n, float scale, float* partial,
-                                  int n_partial, const void* const* flag_ptrs, int slot, unsigned epoch, int rank,
-                                  int world, unsigned long long timeout_ns, int* status, cudaStream_t stream) {
+extern "C" int fmb_comm_rs_reduce(const void* const* grad_ptrs, long long lo, long long n, float scale, float* dst,
+                                  float* partial, int n_partial, const void* const* flag_ptrs, int slot,
+                                  unsigned epoch, int rank, int world, unsigned long long timeout_ns, int* status,
+                                  cudaStream_t stream) {
   Peers g, f;
   if (!fill(g, grad_ptrs, world) || !fill(f, flag_ptrs, world) || rank < 0 || rank >= world) return -2;
-  if ((lo & 3) || (n & 3) || n_partial < 1 || slot < 0) return -2;
-  rs_reduce_kernel<<<n_partial, 256, 0, stream>>>(g, lo, n, scale, partial, f, slot, epoch, rank, world, timeout_ns,
-                                                  status);
+  if ((lo & 3) || (n & 3) || n_partial < 1 || slot < 0 || (reinterpret_cast<uintptr_t>(dst) & 15)) return -2;
+  rs_reduce_kernel<<<n_partial, 256, 0, stream>>>(g, lo, n, scale, dst, partial, f, slot, epoch, rank, world,
+                                                  timeout_ns, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -283,7 +290,7 @@ extern "C" int fmb_comm_adamw_push(float* master, const float* grad, float* m, f
                                    const void* const* shadow_ptrs, int world, const long long* off,
                                    const long long* soff, const int* len, const float* wd, int n_chunks, float lr,
                                    float beta1, float beta2, float eps, float bc1, float bc2, const float* ctl,
-                                   cudaStream_t stream) {
+                                   int grad_compact, cudaStream_t stream) {
   Peers s;
   if (!fill(s, shadow_ptrs, world) || ctl == nullptr) return -2;
   if (n_chunks <= 0) return 0;
@@ -291,7 +298,7 @@ extern "C" int fmb_comm_adamw_push(float* master, const float* grad, float* m, f
        reinterpret_cast<uintptr_t>(v)) & 15)
     return -2;
   adamw_push_kernel<<<n_chunks, 256, 0, stream>>>(master, grad, m, v, s, world, off, soff, len, wd, lr, beta1, beta2,
-                                                  eps, bc1, bc2, ctl);
+                                                  eps, bc1, bc2, ctl, grad_compact);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -306,6 +313,47 @@ extern "C" int fmb_comm_push_cast(const float* master, const void* const* shadow
 }
 
 extern "C" int fmb_comm_adam_chunk(void) { return ADAM_CHUNK; }
+
+// ------------------------------------------------------------------ debug build: the table of registered buffers
+FMB_DEBUG_BIND(comm)
+extern "C" int fmb_debug_bind_moe_ep(const void* tab, int n, int* status);
+extern "C" int fmb_debug_bind_gemm(const void* tab, int n, int* status);
+
+extern "C" int fmb_debug_bounds_enabled(void) {
+#ifdef FMB_DEBUG_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// Adds [base, base + bytes) to the buffers that the checked accesses accept on the current device and points
+// the kernels' status reports at `status` (an int in device memory). Synchronises the device. No-op (returns 0)
+// in the normal build. At most 1024 buffers per process.
+extern "C" int fmb_debug_register_extent(const void* base, unsigned long long bytes, int* status) {
+#ifdef FMB_DEBUG_BOUNDS
+  constexpr int CAP = 1024;
+  static FmbExtent host_tab[CAP];
+  static int n = 0;
+  static FmbExtent* dev_tab = nullptr;
+  if (base == nullptr || bytes == 0) return -2;
+  if (n >= CAP) return -5;
+  if (dev_tab == nullptr && cudaMalloc(reinterpret_cast<void**>(&dev_tab), sizeof(FmbExtent) * CAP) != cudaSuccess) return -3;
+  const unsigned long long lo = reinterpret_cast<unsigned long long>(base);
+  host_tab[n].lo = lo;
+  host_tab[n].hi = lo + bytes;
+  ++n;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -3;
+  if (cudaMemcpy(dev_tab, host_tab, sizeof(FmbExtent) * n, cudaMemcpyHostToDevice) != cudaSuccess) return -3;
+  int rc = fmb_debug_bind_comm(dev_tab, n, status);
+  if (rc == 0) rc = fmb_debug_bind_moe_ep(dev_tab, n, status);
+  if (rc == 0) rc = fmb_debug_bind_gemm(dev_tab, n, status);
+  return rc;
+#else
+  (void)base; (void)bytes; (void)status;
+  return 0;
+#endif
+}
 
 extern "C" int fmb_comm_barrier(const void* const* flag_ptrs, int slot, unsigned epoch, int rank, int world,
                                 unsigned long long timeout_ns, int* status, cudaStream_t stream) {

@@ -1003,14 +1003,21 @@ extern "C" int fmb_topk(const void* x, void* values, long long* indices, long lo
 // itself to a kernel: in host code the name is only a handle. Its device address is fetched once per
 // device with cudaGetSymbolAddress and that pointer is what the launcher receives.
 #include "fmb_noalloc.h"
+#include <atomic>
 #include <cstdio>
 
 static __device__ __align__(256) float g_noalloc_scratch[FMB_NOALLOC_MAX_D * FMB_NOALLOC_MAX_BLOCKS];
 
 extern "C" int fmb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
                                        float* dw, long long rows, int d, int dtype, int w_dtype, cudaStream_t stream) {
-  static float* scratch_of_device[64] = {nullptr};
+  // one slot per device; atomic because two host threads may make their first call at the same time
+  // (both then look the address up and store the same value)
+  static std::atomic<float*> scratch_of_device[64];
   if (rows <= 0) return 0;
+  if (d <= 0 || d % 8) {
+    std::fprintf(stderr, "fmb_rmsnorm_bwd_noalloc: row width %d is not a positive multiple of 8\n", d);
+    return FMB_NOALLOC_BAD_WIDTH;
+  }
   int nblocks = fmb_rmsnorm_bwd_blocks(rows, d);
   if (nblocks > FMB_NOALLOC_MAX_BLOCKS) nblocks = FMB_NOALLOC_MAX_BLOCKS;   // the kernel strides over the rows
   if (d > FMB_NOALLOC_MAX_D ||
@@ -1021,7 +1028,8 @@ extern "C" int fmb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
   }
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FMB_NOALLOC_SETUP_FAILED;
-  if (scratch_of_device[dev] == nullptr) {
+  float* scratch = scratch_of_device[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
     // first call on this device (it is the current one): resolve the array's device address
     float* ptr = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
@@ -1029,9 +1037,9 @@ extern "C" int fmb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
       std::fprintf(stderr, "fmb_rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
       return FMB_NOALLOC_SETUP_FAILED;
     }
-    scratch_of_device[dev] = ptr;
+    scratch_of_device[dev].store(ptr, std::memory_order_release);
+    scratch = ptr;
   }
   // every block writes its whole row of partial sums before the column sum reads it: nothing to clear
-  return fmb_rmsnorm_bwd(dy, x, w, rstd, nullptr, dx, scratch_of_device[dev], dw, 0, rows, d, dtype, w_dtype, nblocks,
-                         stream);
+  return fmb_rmsnorm_bwd(dy, x, w, rstd, nullptr, dx, scratch, dw, 0, rows, d, dtype, w_dtype, nblocks, stream);
 }

@@ -142,7 +142,7 @@ int fmb_ep_combine_bwd(const void* const* dout_ptrs, const void* const* w_ptrs, 
 // `*_ptrs` are HOST arrays of `world` device pointers: the same symmetric buffer as mapped for each
 // rank. Flags are uint32 epochs, FMB_MAX_PEERS per slot, zero before first use; `epoch` must grow by
 // one per use of a slot on every rank. A wait that exceeds `timeout_ns` sets *status to ERR_WAIT_PEER.
-int fmb_comm_rs_reduce(const void* const* grad_ptrs, long long lo, long long n, float scale, float* partial,
+int fmb_comm_rs_reduce(const void* const* grad_ptrs, long long lo, long long n, float scale, float* dst, float* partial,
                        int n_partial, const void* const* flag_ptrs, int slot, unsigned epoch, int rank, int world,
                        unsigned long long timeout_ns, int* status, cudaStream_t stream);
 int fmb_comm_step_reduce(const float* partial, int n_partial, const float* extra_sq, const float* loss,
@@ -152,12 +152,16 @@ int fmb_comm_step_reduce(const float* partial, int n_partial, const float* extra
 int fmb_comm_adamw_push(float* master, const float* grad, float* m, float* v, const void* const* shadow_ptrs,
                         int world, const long long* off, const long long* soff, const int* len, const float* wd,
                         int n_chunks, float lr, float beta1, float beta2, float eps, float bc1, float bc2,
-                        const float* ctl, cudaStream_t stream);
+                        const float* ctl, int grad_compact, cudaStream_t stream);
 // fp32 master ranges (chunk table off/len on the device, len a multiple of 8) -> bf16 at the same offsets of every
 // rank's working-weight buffer.
 int fmb_comm_push_cast(const float* master, const void* const* shadow_ptrs, int world, const long long* off,
                        const int* len, int n_chunks, cudaStream_t stream);
 int fmb_comm_adam_chunk(void);
+// Debug build (-DFMB_DEBUG_BOUNDS): 1, and fmb_debug_register_extent() adds a buffer to the table that every checked
+// peer access is validated against (outside it: access skipped, ERR_BOUNDS = 7 in *status). Normal build: 0 / no-op.
+int fmb_debug_bounds_enabled(void);
+int fmb_debug_register_extent(const void* base, unsigned long long bytes, int* status);
 int fmb_comm_signal(const void* const* flag_ptrs, int slot, unsigned epoch, int rank, int world, cudaStream_t stream);
 // Product whose operands / output are spread over the ranks (gemm_sm100.cu): see the comment at the definition.
 int fmb_gemm_bf16_peer(const void* A, const void* B, void* D, int M, int N, int K, int a_mn, int b_mn, long long lda,

@@ -11,6 +11,7 @@
 // Limits and rules
 //   * d (row width) times the number of thread blocks used must fit the built-in scratch:
 //     d <= FMB_NOALLOC_MAX_D. Wider rows are refused with FMB_NOALLOC_TOO_LARGE and a message on stderr.
+//   * d must be a positive multiple of 8 (the kernels move 16-byte vectors): FMB_NOALLOC_BAD_WIDTH otherwise.
 //   * The array costs FMB_NOALLOC_SCRATCH_BYTES of device memory on every GPU that loads the library,
 //     until the process exits.
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress with that
@@ -30,9 +31,12 @@ extern "C" {
 #define FMB_NOALLOC_SCRATCH_BYTES (FMB_NOALLOC_MAX_D * FMB_NOALLOC_MAX_BLOCKS * 4)
 #define FMB_NOALLOC_TOO_LARGE (-20)
 #define FMB_NOALLOC_SETUP_FAILED (-21)
+#define FMB_NOALLOC_BAD_WIDTH (-22)
 
 // dx[rows, d] = RMSNorm backward of dy through y = x * rstd * w;  dw[d] (fp32) = sum over rows.
-// dtype / w_dtype: 0 = bf16, 1 = fp32 (as in fmb_api.h). Returns 0 or a negative code.
+// dtype / w_dtype: 0 = bf16, 1 = fp32 (as in fmb_api.h). Returns 0, one of the FMB_NOALLOC_* codes above, or the
+// regular entry point's codes (-2: an argument it refuses, e.g. a misaligned pointer; -3: the launch failed).
+// Safe to call from several host threads; see the ordering rule above for what runs on the GPU.
 int fmb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
                             long long rows, int d, int dtype, int w_dtype, cudaStream_t stream);
 

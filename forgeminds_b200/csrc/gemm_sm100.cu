@@ -243,8 +243,8 @@ __device__ __forceinline__ void gather_rows(const GemmParams& p, int tid) {
 #pragma unroll
       for (int u = 0; u < HALF; ++u)
         if (v0 + u * GATHER_THREADS < vec_per_row) {
-          dp0[v0 + u * GATHER_THREADS] = a[u];
-          if (two) dp1[v0 + u * GATHER_THREADS] = b[u];
+          if (addr_ok(dp0 + v0 + u * GATHER_THREADS, 16)) dp0[v0 + u * GATHER_THREADS] = a[u];
+          if (two && addr_ok(dp1 + v0 + u * GATHER_THREADS, 16)) dp1[v0 + u * GATHER_THREADS] = b[u];
         }
     }
     __threadfence();
@@ -1117,6 +1117,8 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
   }
   return e == cudaSuccess ? 0 : -10 - static_cast<int>(e);
 }
+
+FMB_DEBUG_BIND(gemm)
 
 extern "C" int fmb_gemm_bf16(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int a_mn,
                              int b_mn, long long lda, long long ldb, long long ldd, long long ldc, int d_f32,

@@ -138,7 +138,7 @@ ep_combine_bwd_kernel(Peers dout, Peers w, Peers drw, const uint4* __restrict__ 
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    if (lane == 0) static_cast<float*>(drw.p[r])[el] = dot;
+    if (lane == 0 && addr_ok(static_cast<float*>(drw.p[r]) + el, 4)) static_cast<float*>(drw.p[r])[el] = dot;
   }
 }
 
@@ -159,6 +159,8 @@ static int ep_grid(long long work) {
 }  // namespace fmb
 
 using namespace fmb;
+
+FMB_DEBUG_BIND(moe_ep)
 
 extern "C" int fmb_ep_collect_idx(const void* const* idx_ptrs, int* out, long long n, int world, int rank, int e_local,
                                   const unsigned* flags, int slot, unsigned epoch, unsigned long long timeout_ns,

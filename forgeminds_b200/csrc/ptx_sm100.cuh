@@ -20,6 +20,7 @@ enum : int {
   ERR_WAIT_TMEM_EMPTY = 4, // MMA warp timed out waiting for the epilogue
   ERR_WAIT_PEER = 5,       // a flag owned by another GPU never arrived
   ERR_WAIT_MISC = 6,
+  ERR_BOUNDS = 7,          // debug build (FMB_DEBUG_BOUNDS): an address outside every registered buffer; access skipped
 };
 
 #ifndef FMB_WAIT_LIMIT_NS

@@ -36,6 +36,16 @@ def flat_store_blockers(cfg, model, kernels: bool = True) -> list:
     return why
 
 
+def resident_bytes(model, cfg, ctx) -> int:
+    """Device memory the flat-store engine needs for this rank's slice of the model: bf16 working weights
+    (2 bytes per parameter), fp32 gradients (4) and fp32 masters (4) whole, AdamW moments (8) divided by
+    the number of ranks that share the optimizer state."""
+    n = sum(p.numel() for p in model.parameters() if p.requires_grad)
+    pc = cfg.parallel
+    share = max(1, ctx.dp_world if pc.dp_shard <= 1 else pc.dp_shard) if pc.fused_comm else 1
+    return int(n * (10 + 8 / share))
+
+
 def choose(owner, model):
     """``FORGEMINDS_FLAT_ENGINE=1`` selects the flat-store engine even where the sm_100a kernels cannot
     run (CPU, Gloo): the blocks then run PyTorch operators, gradients are reduced with ``all_reduce``
@@ -49,6 +59,14 @@ def choose(owner, model):
     forced = switch == "1" and hasattr(model, "layers")
     if (owner.native or forced) and not owner.use_ds and switch != "0":
         blockers = flat_store_blockers(owner.cfg, model, kernels=bool(owner.native))
+        if owner.native and owner.ctx.device.type == "cuda" and owner.ctx.dp_world > 1 and not blockers:
+            import torch
+            budget = int(owner.cfg.parallel.fsdp_resident_bytes) or \
+                int(0.8 * torch.cuda.get_device_properties(owner.ctx.device).total_memory)
+            need = resident_bytes(model, owner.cfg, owner.ctx)
+            if need > budget:
+                blockers.append(f"the flat store would need {need / 2 ** 30:.0f} GiB per GPU for weights, gradients and "
+                                f"optimizer state (budget {budget / 2 ** 30:.0f} GiB): parameters must be sharded")
         if not blockers:
             from .native import NativeEngine
             return NativeEngine(owner, model)

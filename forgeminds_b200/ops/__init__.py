@@ -8,6 +8,7 @@ paths in :mod:`forgeminds_b200.kernels.reference` are used instead.
 from __future__ import annotations
 
 import importlib
+import os
 import threading
 
 import torch
@@ -25,7 +26,10 @@ def native():
     with _lock:
         if _mod is None and _err is None:
             try:
-                _mod = importlib.import_module("forgeminds_b200._C")
+                # FORGEMINDS_DEBUG_SO=1: the build with bounds checks on every peer-memory access
+                # (python -m forgeminds_b200.csrc.build --debug-bounds)
+                name = "_C_debug" if os.environ.get("FORGEMINDS_DEBUG_SO") == "1" else "_C"
+                _mod = importlib.import_module(f"forgeminds_b200.{name}")
             except Exception as exc:  # missing file, wrong ABI, no libcudart ...
                 _err = exc
     return _mod
@@ -68,10 +72,32 @@ class CommTimeout(RuntimeError):
     """A device-side wait gave up; the status word holds the error code."""
 
 
+class BoundsError(RuntimeError):
+    """Debug build only: a kernel was about to touch memory outside every registered buffer (code 7);
+    the access was skipped."""
+
+
+def register_buffer(t_or_ptr, nbytes: int | None = None, device=None) -> None:
+    """Debug build: add a buffer (a tensor, or an address and a length) to the table that the checked
+    peer-memory accesses are validated against. No-op in the normal build."""
+    mod = native()
+    if mod is None or not hasattr(mod, "debug_bounds") or not mod.debug_bounds():
+        return
+    if torch.is_tensor(t_or_ptr):
+        base, nbytes, device = t_or_ptr.data_ptr(), t_or_ptr.numel() * t_or_ptr.element_size(), t_or_ptr.device
+    else:
+        base = int(t_or_ptr)
+    if nbytes:
+        mod.debug_register(base, int(nbytes), status_word(device))
+
+
 def check_status(device, sync_value: int | None = None) -> None:
     """Raise :class:`CommTimeout` if a kernel reported a timed-out wait. ``sync_value`` lets a
     caller pass a value it already brought to the host so that no extra sync is paid."""
     code = int(status_word(device).item()) if sync_value is None else int(sync_value)
     if code:
         status_word(device).zero_()
+        if code == 7:
+            raise BoundsError("forgeminds_b200: a kernel of the bounds-checked build skipped an access outside "
+                              "every registered buffer (code 7)")
         raise CommTimeout(f"forgeminds_b200: a kernel wait timed out (code {code})")

@@ -147,6 +147,7 @@ class FlatParamStore:
             self.buckets.append(b)
         self.total = cursor
         self.moment_total = mcursor
+        self.reduced = None          # compact buffer of reduced gradient shards (hybrid sharding only, see peer.py)
         self.master = torch.zeros(self.total, dtype=torch.float32, device=self.device)
         if symm is not None:
             self.grad_symm = symm.alloc(self.total, torch.float32)
@@ -212,6 +213,14 @@ class FlatParamStore:
                 whole.zero_()
                 self.master[lo:lo + n].copy_(mine)
                 dist.all_reduce(whole, group=lay.shard_group)
+
+    def reduced_shard(self, b: Bucket, rank: int) -> torch.Tensor:
+        """This rank's reduced gradients of bucket ``b`` after the reduce-scatter: a slice of the gradient
+        buffer itself, or of the compact buffer when replicas share shards (hybrid sharding)."""
+        lo, n = self.shard_range(b, rank)
+        if self.reduced is not None and not b.local:
+            return self.reduced[b.moff:b.moff + n]
+        return self.grad[lo:lo + n]
 
     def rebind(self) -> None:
         """Re-attach ``.grad`` views (something set them to ``None``)."""

@@ -58,6 +58,11 @@ class PeerReducer:
         self._launched: list = []
         self.enabled = True
         self.local_only = False      # timing diagnostics: same kernels, this rank's memory only (see detach)
+        # Hybrid sharding: the replicas of a shard all read that shard from every rank, so none of them may
+        # overwrite it. Their sums go to a compact buffer laid out like the optimizer moments instead.
+        if self.layout.replicas > 1 and getattr(store, "reduced", None) is None:
+            store.reduced = torch.zeros(store.moment_total, dtype=torch.float32, device=store.device)
+            ops.register_buffer(store.reduced)
 
     def _reduce(self, b: Bucket) -> None:
         C = ops.require()
@@ -74,8 +79,11 @@ class PeerReducer:
             C.comm_rs_reduce([st.grad_symm.ptrs[sg.rank]], lo, n, 1.0 / self.world, part, [sg.flags.ptrs[sg.rank]], slot,
                              sg.next_epoch(slot), 0, sg.timeout_ms, sg.status)
             return
+        dst = None
+        if getattr(st, "reduced", None) is not None:
+            dst = st.reduced[b.moff:b.moff + n]
         C.comm_rs_reduce(st.grad_symm.ptrs, lo, n, 1.0 / self.world, part, sg.flags.ptrs, slot, sg.next_epoch(slot),
-                         sg.rank, sg.timeout_ms, sg.status)
+                         sg.rank, sg.timeout_ms, sg.status, dst)
 
     def launch(self, b: Bucket) -> None:
         if not self.enabled:
@@ -207,10 +215,13 @@ class PeerAdamW(FlatAdamW):
             everyone = me
         elif self.layout.replicas > 1:           # hybrid sharding: the other replicas compute the same shard themselves
             everyone = [everyone[r] for r in self.layout.replica_peers()]
-        for (off, soff, ln, wds), ptrs in zip(self._tables, (everyone, me)):
+        compact = getattr(st, "reduced", None)      # hybrid sharding: reduced gradients live in their own buffer
+        for (off, soff, ln, wds), ptrs, shared in zip(self._tables, (everyone, me), (True, False)):
             if off.numel():
-                ops.require().comm_adamw_push(st.master, st.grad, self.exp_avg, self.exp_avg_sq, ptrs, off, soff,
-                                              ln, wds, lr, b1, b2, self.defaults["eps"], bc1, bc2, self.ctl)
+                from_compact = shared and compact is not None
+                ops.require().comm_adamw_push(st.master, compact if from_compact else st.grad, self.exp_avg,
+                                              self.exp_avg_sq, ptrs, off, soff, ln, wds, lr, b1, b2,
+                                              self.defaults["eps"], bc1, bc2, self.ctl, from_compact)
         if not self.local_only:
             sg.barrier(self.slot_done)
         return None

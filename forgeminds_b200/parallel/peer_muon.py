@@ -128,7 +128,8 @@ class PeerMuon(PeerAdamW):
             stack = []
             for p, off, moff in items:
                 n = p.numel()
-                g = st.grad[off:off + n] * clip
+                src = st.reduced[moff:moff + n] if st.reduced is not None else st.grad[off:off + n]
+                g = src * clip
                 buf = self.exp_avg[moff:moff + n]
                 buf.copy_(torch.where(go, buf.lerp(g, 1 - self.mu), buf))
                 stack.append(g.lerp(buf, self.mu).view(rows, cols))

@@ -70,7 +70,13 @@ class SymmGroup:
 
     # ------------------------------------------------------------------ allocation
     def alloc(self, numel: int, dtype) -> SymmTensor:
-        numel = int(numel)
+        st = self._alloc(int(numel), dtype)
+        nbytes = st.local.numel() * st.local.element_size()
+        for ptr in st.ptrs:                       # bounds-checked build: these are the buffers kernels may touch
+            ops.register_buffer(ptr, nbytes, self.device)
+        return st
+
+    def _alloc(self, numel: int, dtype) -> SymmTensor:
         if self.world == 1:
             t = torch.zeros(numel, dtype=dtype, device=self.device)
             return SymmTensor(t, [t.data_ptr()])

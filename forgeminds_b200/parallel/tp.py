@@ -308,7 +308,8 @@ def shard_model(model, ctx, plan=None):
         blk.attn_norm.weight._tp_partial = True
         blk.ffn_norm.weight._tp_partial = True
         blk._fm_tp = state
-    model.tok_emb.weight._tp_partial = True
+    if getattr(model, "tok_emb", None) is not None:           # absent on all but the first pipeline stage
+        model.tok_emb.weight._tp_partial = True
     model._fm_tp = state
     return model
 

@@ -440,7 +440,7 @@ def _mesh_equiv(world, rank, dev, label, check_ckpt=False, **par):
     worst = 0.0
     for b in st.buckets:
         lo, n = st.shard_range(b, st.layout.shard_rank)
-        got, want = st.grad[lo:lo + n], expected[lo:lo + n]
+        got, want = st.reduced_shard(b, st.layout.shard_rank), expected[lo:lo + n]
         if want.norm() == 0:
             continue
         rel = ((got - want).norm() / want.norm()).item()

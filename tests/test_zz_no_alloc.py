@@ -29,7 +29,9 @@ def test_matches_regular_entry_point_twice():
     C = ops.require()
     fn = _lib()
     stream = torch.cuda.current_stream().cuda_stream
-    for seed, (rows, d) in enumerate([(777, 1024), (300, 4096)]):
+    # the third case needs more thread blocks than the built-in scratch has rows for (320): the grid is
+    # clamped there and every block walks several row groups
+    for seed, (rows, d) in enumerate([(777, 1024), (300, 4096), (16384, 512)]):
         g = torch.Generator(device="cuda").manual_seed(seed)
         x = torch.randn(rows, d, device="cuda", generator=g).to(torch.bfloat16)
         dy = torch.randn(rows, d, device="cuda", generator=g).to(torch.bfloat16)
@@ -58,3 +60,13 @@ def test_refuses_rows_wider_than_the_scratch():
     rc = fn(t.data_ptr(), t.data_ptr(), w.data_ptr(), r.data_ptr(), out.data_ptr(), dw.data_ptr(), 8, 8192, 0, 1,
             torch.cuda.current_stream().cuda_stream)
     assert rc == -20
+
+
+def test_refuses_a_width_the_kernels_cannot_vectorise():
+    fn = _lib()
+    t = torch.zeros(8, 36, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(36, device="cuda")
+    r = torch.ones(8, device="cuda")
+    rc = fn(t.data_ptr(), t.data_ptr(), w.data_ptr(), r.data_ptr(), t.data_ptr(), w.data_ptr(), 8, 36, 0, 1,
+            torch.cuda.current_stream().cuda_stream)
+    assert rc == -22
