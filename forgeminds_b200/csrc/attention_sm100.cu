@@ -1,15 +1,17 @@
 // Causal / full flash attention with grouped-query heads for sm_100a, forward and backward.
 //
 // Forward: one CTA per (batch, query head, 128-row query tile). Warp 0 streams K/V tiles with TMA,
-// warp 1 issues tcgen05.mma (S = Q K^T into TMEM, then O += P V), warps 2-5 own one query row per
-// thread: they read S from TMEM, keep the running max / sum, write P (bf16) into a swizzled smem
-// tile for the second MMA and rescale the O accumulator in TMEM only when the row max moved.
-// Two CTAs fit on an SM for head_dim <= 64 (256 TMEM columns each), so one CTA's softmax overlaps
-// the other's MMAs.
+// warp 1 issues tcgen05.mma (S = Q K^T into TMEM, then O += P V with P as a TMEM operand), eight row
+// warps own half a query row per thread: they read S from TMEM, keep the running max / sum, write P
+// (bf16) into its own TMEM columns and rescale the O accumulator in TMEM only when the row max moved.
+// S and P have separate TMEM columns, so the CTA is software-pipelined: S(j+1) is issued as soon as the
+// row warps have read S(j) and runs while they compute the exponentials of tile j; they only wait for
+// P(j-1) V(j-1) before they overwrite P or touch O. Two CTAs fit on an SM for head_dim <= 64 (256 TMEM
+// columns each), which hides the rest.
 //
 // Backward: one CTA per (batch, kv head, 128-row kv tile); it walks the query tiles of every query
 // head of the group, keeps dK/dV in TMEM for the whole walk and hands each dQ tile to four
-// writer warps that add it to an fp32 buffer. P and dS are written once to smem and serve both as
+// writer warps that add it to an fp32 buffer with TMA reduce-add boxes. P and dS are written once to smem and serve both as
 // the K-major operand of dQ = dS K and as the MN-major operand of dV = P^T dO, dK = dS^T Q.
 //
 // Head dims that are not a multiple of 64 are padded by TMA out-of-bounds fill (zeros).
@@ -92,7 +94,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bars = sbase + L::BAR_OFF;
   const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = bars + 24, s_full = bars + 40, p_ready = bars + 48,
-                 o_full = bars + 56;
+                 o_full = bars + 56, s_free = bars + 64, pv_done = bars + 72;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::BAR_OFF + 16 * 8);
   AbortState* ab = reinterpret_cast<AbortState*>(tmem_slot + 1);
 
@@ -111,6 +113,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(s_full, 1);
     mbar_init(p_ready, ATT_ROW_WARPS);
     mbar_init(o_full, 1);
+    mbar_init(s_free, ATT_ROW_WARPS);
+    mbar_init(pv_done, 1);
     ab->flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -172,8 +176,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         issue_s(0);
         umma_commit(s_full);
       }
+      // Software pipeline inside the CTA: the scores of tile j+1 are issued as soon as the row warps have
+      // READ the scores of tile j (s_free), i.e. before P(j) exists, so S(j+1) runs on the tensor pipe while
+      // the row warps are still busy with the exponentials of tile j, and their work on tile j+1 can start
+      // the moment they have handed over P(j). P and the output accumulator are only touched by the row
+      // warps again after P(j) V(j) has completed (pv_done).
       for (int j = 0; ok && j < n_kv; ++j) {
         const int st = j & 1;
+        if (j + 1 < n_kv) {
+          const int nst = (j + 1) & 1;
+          if (!mbar_wait_bounded(s_free, j & 1, ab, p.status, ERR_WAIT_MISC)) break;
+          // stage nst holds tile j+1: it is the (j+1)/2-th use of that stage
+          if (!mbar_wait_bounded(kv_full0 + 8 * nst, ((j + 1) >> 1) & 1, ab, p.status, ERR_WAIT_FULL)) break;
+          tc_fence_after();
+          issue_s(nst);
+          umma_commit(s_full);
+        }
         if (!mbar_wait_bounded(p_ready, j & 1, ab, p.status, ERR_WAIT_MISC)) break;
         tc_fence_after();
 #pragma unroll
@@ -182,16 +200,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           umma_f16_ts(tmem + O_COL, tmem + P_COL + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);   // 16 kv = 8 columns
         }
         umma_commit(kv_empty0 + 8 * st);
-        if (j + 1 < n_kv) {
-          const int nst = (j + 1) & 1;
-          // stage nst holds tile j+1: it is the (j+1)/2-th use of that stage
-          if (!mbar_wait_bounded(kv_full0 + 8 * nst, ((j + 1) >> 1) & 1, ab, p.status, ERR_WAIT_FULL)) break;
-          tc_fence_after();
-          issue_s(nst);
-          umma_commit(s_full);
-        } else {
-          umma_commit(o_full);
-        }
+        umma_commit(pv_done);
+        if (j + 1 == n_kv) umma_commit(o_full);
       }
     }
   } else {
@@ -227,6 +237,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld_32x32(t_lane + S_COL + c_lo + 32, r1);
         tmem_ld_fence(r0);
         tmem_ld_fence(r1);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);            // the scores are in registers: the next tile's may be written
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) { r0[i] = 0u; r1[i] = 0u; }
@@ -249,9 +262,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float m_new = fmaxf(m_run, fmaxf(mx, *get_slot) * p.scale_log2);
       const float alpha = exp2f(m_run - m_new);          // 0 on the first tile (m_run = -inf)
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      // 32 columns at a time: exponentials, row sum, bf16 pairs into this thread's P columns in TMEM
-      auto p_half = [&](const uint32_t (&r)[32], int c_first, int word0) {
-        uint32_t packed[16];
+      // 32 columns at a time: exponentials, row sum, bf16 pairs (kept in registers until P(j-1) V(j-1) is done)
+      uint32_t packed0[16], packed1[16];
+      auto p_half = [&](const uint32_t (&r)[32], int c_first, uint32_t (&packed)[16]) {
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float a0 = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_new));
@@ -263,12 +276,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           sum4[(i >> 1) & 3] += a0 + a1;
           packed[i >> 1] = pack_bf16(a0, a1);
         }
-        tmem_st_32x16(t_lane + P_COL + half * 32 + word0, packed);
       };
-      p_half(r0, c_lo, 0);
-      p_half(r1, c_lo + 32, 16);
+      p_half(r0, c_lo, packed0);
+      p_half(r1, c_lo + 32, packed1);
       l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       m_run = m_new;
+      if (j > 0) {          // P columns and the accumulator belong to the tensor pipe until the previous product is done
+        bool done = mbar_wait_bounded(pv_done, (j - 1) & 1, ab, p.status, ERR_WAIT_TMEM_FULL);
+        done = __all_sync(0xffffffffu, done);
+        if (!done) { alive = false; break; }
+        tc_fence_after();
+      }
+      tmem_st_32x16(t_lane + P_COL + half * 32, packed0);
+      tmem_st_32x16(t_lane + P_COL + half * 32 + 16, packed1);
       // rescale this half's output columns only if some row of the warp moved its maximum
       if (j > 0 && !__all_sync(0xffffffffu, alpha == 1.f)) {
 #pragma unroll 1
@@ -352,18 +372,18 @@ struct BwdSmem {
   static constexpr uint32_t DO_OFF = Q_OFF + STAGES * TILE;        // STAGES tiles
   static constexpr uint32_t P_OFF = DO_OFF + STAGES * TILE;
   static constexpr uint32_t DS_OFF = P_OFF + 2 * PANEL_BYTES;
-  static constexpr uint32_t BAR_OFF = DS_OFF + 2 * PANEL_BYTES;
+  // dQ staging: each of the four writer warps sends 32 x 32 fp32 boxes (4 KB, 128B-swizzled) with TMA reduce-add
+  static constexpr int DQ_BUFS = HD_PAD == 64 ? 2 : 1;
+  static constexpr uint32_t DQ_STG_OFF = DS_OFF + 2 * PANEL_BYTES;
+  static constexpr uint32_t BAR_OFF = DQ_STG_OFF + 4 * DQ_BUFS * 4096;
   static constexpr uint32_t TOTAL = BAR_OFF + 16 * 8 + 16;
 };
-
-__device__ __forceinline__ void red_add4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
 
 template <int HD_PAD>
 __global__ void __launch_bounds__(ATT_BWD_THREADS)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, AttnBwdParams p) {
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                const __grid_constant__ CUtensorMap tmDQ, AttnBwdParams p) {
   using L = BwdSmem<HD_PAD>;
   constexpr int PANELS = L::PANELS;
   constexpr int STAGES = L::STAGES;
@@ -404,6 +424,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     ab->flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
+    tma_prefetch_desc(&tmDQ);
   }
   if (warp == 1) { tmem_alloc<512>(smem_u32(tmem_slot)); tmem_relinquish(); }
   tc_fence_before();
@@ -623,39 +644,50 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ---------------------------------------------------------------- dQ writer warps
+    // Every kv tile contributes to the dQ rows of the query tiles it sees, so dQ is summed in an fp32 buffer.
+    // The sum goes through TMA: a warp stages its 32 rows x 32 columns in 128B-swizzled shared memory and one
+    // lane sends the box as a reduce-add ([B, T, Hq * hd] map: rows past T are clipped by the copy engine).
+    // That is one instruction per 4 KB instead of 256 vector atomics per warp and chunk.
     const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
+    const uint32_t stg_base = sbase + L::DQ_STG_OFF + static_cast<uint32_t>(quarter) * (L::DQ_BUFS * 4096u);
     const uint32_t t_lane = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    uint32_t stg_i = 0;
     for (int it = 0; it < n_it; ++it) {
       const int g = it / n_i, i = i0 + it % n_i;
       const int h = hk * G + g;
-      const int q_idx = i * ATT_BM + row;
       bool ok = mbar_wait_bounded(dq_full, it & 1, ab, p.status, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, ok)) break;
       tc_fence_after();
-      float* dst = p.dq_acc + ((static_cast<long long>(b) * p.T + q_idx) * p.Hq + h) * p.hd;
 #pragma unroll 1
       for (int c = 0; c < HD_PAD / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(t_lane + DQ_COL + c * 32, r);
         tmem_ld_fence(r);
         if (c == HD_PAD / 32 - 1) {
-          // the accumulator is in registers now: let the MMA warp reuse it while the adds drain
+          // the accumulator is in registers now: let the MMA warp reuse it while the boxes drain
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(dq_free);
         }
-        if (q_idx < p.T) {
+        if (c * 32 >= p.hd) continue;                 // padding columns of a head dim below the tile width
+        const uint32_t buf = stg_base + (stg_i % L::DQ_BUFS) * 4096u;
+        ++stg_i;
+        if (lane == 0) tma_store_wait_read<L::DQ_BUFS - 1>();     // the box sent from this buffer earlier has been read
+        __syncwarp();
+        const uint32_t row_addr = buf + static_cast<uint32_t>(lane) * 128u;
 #pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4) {
-            const int col = c * 32 + q4 * 4;
-            if (col < p.hd)
-              red_add4(dst + col, __uint_as_float(r[q4 * 4]), __uint_as_float(r[q4 * 4 + 1]), __uint_as_float(r[q4 * 4 + 2]),
-                       __uint_as_float(r[q4 * 4 + 3]));
-          }
+        for (int q = 0; q < 8; ++q)                   // 16-byte piece q of row r sits at q ^ (r % 8)
+          st_shared_v4(row_addr + (static_cast<uint32_t>(q ^ (lane & 7)) << 4), r[4 * q], r[4 * q + 1], r[4 * q + 2],
+                       r[4 * q + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_3d(&tmDQ, buf, h * p.hd + c * 32, i * ATT_BM + quarter * 32, b);
+          tma_store_commit();
         }
       }
     }
+    if (lane == 0) tma_store_wait_all<0>();           // shared memory must outlive the copies that read it
   }
   tc_fence_before();
   __syncthreads();
@@ -776,10 +808,20 @@ extern "C" int fmb_attn_bwd(const void* q, const void* k, const void* v, const v
   if (hd % 8 || hd > 128 || Hq % Hkv || (q_stride_t % 8) || (kv_stride_t % 8) || (o_stride_t % 8) ||
       (dq_stride_t % 8) || (dkv_stride_t % 8))
     return -2;
-  CUtensorMap tq, tk, tv, tdo;
+  CUtensorMap tq, tk, tv, tdo, tdq;
   if (!make_head_tmap(&tq, q, B, T, Hq, hd, q_stride_t) || !make_head_tmap(&tk, k, B, T, Hkv, hd, kv_stride_t) ||
       !make_head_tmap(&tv, v, B, T, Hkv, hd, kv_stride_t) || !make_head_tmap(&tdo, d_o, B, T, Hq, hd, o_stride_t))
     return -5;
+  {
+    // dq_acc [B, T, Hq * hd] fp32, reduce-added in boxes of 32 rows x 32 columns (x = h * hd + c * 32 is a
+    // multiple of 4 elements because hd % 8 == 0)
+    const uint64_t width = static_cast<uint64_t>(Hq) * hd;
+    const uint64_t dims[3] = {width, static_cast<uint64_t>(T), static_cast<uint64_t>(B)};
+    const uint64_t strides[3] = {4, width * 4, width * 4 * static_cast<uint64_t>(T)};
+    const uint32_t box[3] = {32, 32, 1};
+    if ((reinterpret_cast<uintptr_t>(dq_acc) & 15) || !make_tmap_nd(&tdq, dq_acc, 3, dims, strides, box, 4, TmapSwizzle::B128))
+      return -5;
+  }
   if (!delta_ready) {     // else the caller computed delta[b, h, t] already (fused into the producer of dO)
     const long long items = static_cast<long long>(B) * T * Hq;
     int lpr = 1;
@@ -802,13 +844,13 @@ extern "C" int fmb_attn_bwd(const void* q, const void* k, const void* v, const v
     constexpr int sm = BwdSmem<64>::TOTAL;
     static bool done = false;
     if (!done) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sm) != cudaSuccess) return -6; done = true; }
-    if (launch_pdl(kern, dim3(grid), dim3(ATT_BWD_THREADS), sm, stream, tq, tk, tv, tdo, p) != cudaSuccess) return -7;
+    if (launch_pdl(kern, dim3(grid), dim3(ATT_BWD_THREADS), sm, stream, tq, tk, tv, tdo, tdq, p) != cudaSuccess) return -7;
   } else {
     auto kern = attn_bwd_kernel<128>;
     constexpr int sm = BwdSmem<128>::TOTAL;
     static bool done = false;
     if (!done) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, sm) != cudaSuccess) return -6; done = true; }
-    if (launch_pdl(kern, dim3(grid), dim3(ATT_BWD_THREADS), sm, stream, tq, tk, tv, tdo, p) != cudaSuccess) return -7;
+    if (launch_pdl(kern, dim3(grid), dim3(ATT_BWD_THREADS), sm, stream, tq, tk, tv, tdo, tdq, p) != cudaSuccess) return -7;
   }
   if (cudaGetLastError() != cudaSuccess) return -7;
   {

@@ -62,6 +62,28 @@ def as_sharded(model, msd: dict, osd, tp_mesh):
     return msd, osd
 
 
+def _each_optimizer(osd, fn):
+    """Apply ``fn`` to the state dict of every optimizer in ``osd`` (one, or several side by side)."""
+    if isinstance(osd, dict) and "state" not in osd and "param_groups" not in osd:
+        return {k: _each_optimizer(v, fn) for k, v in osd.items()}
+    return fn(osd) if isinstance(osd, dict) else osd
+
+
+def stage_groups(osd, stage: str, restore: bool = False):
+    """Pipeline stages hold different parameters, so their ``param_groups`` differ, but a checkpoint
+    stores one object per key. Keep each stage's groups under a key of its own (``param_groups@<stage>``)
+    while saving / loading and put them back afterwards (``restore=True``)."""
+    key = f"param_groups@{stage}"
+
+    def move(d):
+        src, dst = (key, "param_groups") if restore else ("param_groups", key)
+        if src in d:
+            d = dict(d)
+            d[dst] = d.pop(src)
+        return d
+    return _each_optimizer(osd, move)
+
+
 def as_local(obj):
     """Local tensors of every DTensor in a nested state."""
     if hasattr(obj, "to_local"):

@@ -410,6 +410,8 @@ class Trainer:
 
     def _dcp_state(self):
         msd, osd = self.eng.state_for_dcp()
+        if self.cfg.parallel.pp > 1:
+            osd = ckpt.stage_groups(osd, f"pp{self.ctx.pp_rank}")
         return ckpt.as_sharded(self.raw, msd, osd, self._tp_mesh())
 
     def save(self, keep_last: int = 3) -> None:
@@ -448,7 +450,10 @@ class Trainer:
             msd, osd = self._dcp_state()
             state = {"model": msd} if self.off_opt is not None else {"model": msd, "optim": osd}
             dcp.load(state, checkpoint_id=os.path.join(path, "dcp"))
-            self.eng.load_from_dcp(ckpt.as_local(state["model"]), ckpt.as_local(state.get("optim", {})))
+            loaded_opt = ckpt.as_local(state.get("optim", {}))
+            if self.cfg.parallel.pp > 1:
+                loaded_opt = ckpt.stage_groups(loaded_opt, f"pp{self.ctx.pp_rank}", restore=True)
+            self.eng.load_from_dcp(ckpt.as_local(state["model"]), loaded_opt)
             if self.off_opt is not None:
                 self.off_opt.load_state_dict(torch.load(os.path.join(path, f"offopt_rank{self.ctx.rank}.pt"),
                                                         map_location="cpu", weights_only=False))

@@ -296,6 +296,38 @@ def sc_flat_ep(world):
     assert max(abs(a - b) / b for a, b in zip(norms[True], norms[False])) < 1e-4, norms
 
 
+def sc_pp_ckpt(world):
+    """A pipeline-parallel run resumes from its checkpoint on both engines: every stage gets its own
+    parameters, optimizer moments and param groups back and continues on the same trajectory."""
+    import tempfile
+    for flat in (True, False):
+        os.environ["FORGEMINDS_FLAT_ENGINE"] = "1" if flat else "0"
+        box = [tempfile.mkdtemp() if dist.is_initialized() and dist.get_rank() == 0 else None]
+        if not dist.is_initialized():
+            fm.init_distributed(fm.ParallelConfig(pp=world))
+            box = [tempfile.mkdtemp() if dist.get_rank() == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+
+        def build(resume):
+            cfg = _cfg(pp=world)
+            cfg.parallel.pp_microbatches = 2
+            cfg.train.__dict__.update(max_steps=8, ckpt_dir=box[0], resume=resume, ckpt_every=0)
+            mc = _mc()
+            return fm.Trainer(lambda ctx: fm.GPT(mc), cfg, fm.SyntheticLM(mc.vocab_size, mc.max_seq, n=1024), micro_batch=8)
+        tr = build(False)
+        for _ in range(3):
+            tr.train_step()
+        tr.save()
+        again = build(True)
+        assert again.step == 3
+        assert all("weight_decay" in g for g in again.opt.param_groups)
+        for _ in range(3):
+            a, b = tr.train_step(), again.train_step()
+            assert abs(a["loss"] - b["loss"]) < 1e-5 and abs(a["grad_norm"] - b["grad_norm"]) < 1e-4, (flat, a, b)
+        tr.close()
+        again.close()
+
+
 def sc_tp_ckpt(world):
     """Plain tensors that hold one tensor-parallel slice per rank are stored as one sharded tensor and
     come back slice by slice (what the fused tensor-parallel blocks rely on for their checkpoints)."""

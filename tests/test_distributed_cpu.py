@@ -21,7 +21,7 @@ def _run(name, nproc, timeout=420):
 @pytest.mark.slow
 @pytest.mark.parametrize("name,nproc", [
     ("collectives", 2), ("ddp", 2), ("ddp_accum_offload", 2), ("fsdp", 2), ("fsdp_accum", 2), ("ep_ddp", 2),
-    ("pp", 2), ("tp", 2), ("ep_equiv", 2), ("tp_equiv", 2), ("pp_equiv", 2), ("prefetch", 2), ("tp_ckpt", 2), ("flat_ep", 2),
+    ("pp", 2), ("tp", 2), ("ep_equiv", 2), ("tp_equiv", 2), ("pp_equiv", 2), ("prefetch", 2), ("tp_ckpt", 2), ("flat_ep", 2), ("pp_ckpt", 2),
 ])
 def test_two_ranks(name, nproc):
     _run(name, nproc)

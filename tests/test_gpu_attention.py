@@ -8,7 +8,11 @@ pytestmark = pytest.mark.gpu
 
 
 def _ref(q, k, v, causal):
-    # q [B,T,Hq,hd], k/v [B,T,Hkv,hd] -> fp32 attention with grouped heads
+    # q [B,T,Hq,hd], k/v [B,T,Hkv,hd] -> fp32 attention with grouped heads (one batch entry at a time: the
+    # score matrix of the long cases is large)
+    if q.shape[0] > 1:
+        parts = [_ref(q[i:i + 1], k[i:i + 1], v[i:i + 1], causal) for i in range(q.shape[0])]
+        return torch.cat([p[0] for p in parts]), torch.cat([p[1] for p in parts])
     B, T, Hq, hd = q.shape
     G = Hq // k.shape[2]
     qf = q.float().permute(0, 2, 1, 3)
@@ -35,6 +39,9 @@ CASES = [
     (1, 256, 2, 2, 32, True),
     (2, 256, 4, 2, 64, False),
     (1, 200, 4, 2, 64, True),      # sequence not a multiple of the tile
+    (4, 2048, 16, 4, 64, True),    # the benchmark shape: 16 kv tiles, groups of four query heads
+    (1, 2048, 8, 2, 128, True),
+    (1, 1100, 8, 2, 80, True),     # head dim 80, ragged last tile (the dQ boxes are clipped at T)
 ]
 
 
