@@ -170,9 +170,11 @@ class Attention(nn.Module):
         hd = self.hd
         n_q, n_kv = self.wq.weight.shape[0] // hd, self.wk.weight.shape[0] // hd
         if _is_quantised(self.wq):
-            # int8 / fp8 training: every projection is its own quantised product (8-bit tcgen05 GEMMs)
+            # int8 / fp8 training: q|k|v are ONE quantised product (8-bit tcgen05 GEMM); the normalised
+            # activations are quantised once
+            from ..ops.quant import qlinear_multi
             xn = Fn.rms_norm(x, norm.weight, norm.eps)
-            qkv = torch.cat([self.wq(xn), self.wk(xn), self.wv(xn)], dim=-1)
+            qkv = qlinear_multi(xn, (self.wq.weight, self.wk.weight, self.wv.weight), self.wq.mode, self.wq.block)
             cos, sin = rope_tables(T, hd, self.theta, x.device, torch.float32)
             qkv = Fn.rope_qkv_(qkv, cos.reshape(T, hd // 2), sin.reshape(T, hd // 2), n_q, n_kv, hd)
             return x + self.wo(Fn.attention_qkv(qkv, n_q, n_kv, hd, True))
@@ -197,8 +199,10 @@ class SwiGLU(nn.Module):
         """``x + mlp(norm(x))``; the norm output and the activation are recomputed in the backward."""
         from ..ops import functional as Fn
         if _is_quantised(self.w1):
+            from ..ops.quant import qlinear_multi
             xn = Fn.rms_norm(x, norm.weight, norm.eps)
-            return x + self.w2(Fn.swiglu(self.w1(xn), self.w3(xn)))
+            gu = qlinear_multi(xn, (self.w1.weight, self.w3.weight), self.w1.mode, self.w1.block)
+            return x + self.w2(Fn.swiglu_split(gu))
         if self.w1.weight.shape[0] % 128 == 0:
             return Fn.mlp_block(x, norm.weight, norm.eps, self.w1.weight, self.w3.weight, self.w2.weight)
         gu, x = Fn.norm_linear_multi(x, norm.weight, norm.eps, (self.w1.weight, self.w3.weight), passthrough=True)

@@ -59,6 +59,8 @@ def require():
 def status_word(device) -> torch.Tensor:
     """Per-device int32 word that kernels set when one of their bounded waits runs out."""
     key = torch.device(device)
+    if key.type == "cuda" and key.index is None:          # "cuda" and "cuda:0" must name the same word
+        key = torch.device("cuda", torch.cuda.current_device())
     word = _status.get(key)
     if word is None:
         word = _status[key] = torch.zeros(1, dtype=torch.int32, device=key)

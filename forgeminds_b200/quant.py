@@ -120,8 +120,15 @@ class _QuantLinearFn(torch.autograd.Function):
             x2 = x.reshape(-1, x.shape[-1])
             if x2.is_cuda and x2.dtype == torch.bfloat16:
                 from .ops.functional import gemm
-                dw = gemm(dy2.contiguous(), x2.contiguous(), a_mn=True, b_mn=True, out_dtype=torch.float32,
-                          allow_split=True).to(weight.dtype)
+                main = getattr(weight, "_fm_main_grad", None)
+                if main is not None and dy2.dtype == torch.bfloat16:
+                    # a flat parameter store owns this weight: accumulate into its fp32 gradient buffer in place
+                    gemm(dy2.contiguous(), x2.contiguous(), a_mn=True, b_mn=True, out=main, c=main, beta=1.0,
+                         allow_split=True)
+                    dw = None
+                else:
+                    dw = gemm(dy2.contiguous(), x2.contiguous(), a_mn=True, b_mn=True, out_dtype=torch.float32,
+                              allow_split=True).to(weight.dtype)
             else:
                 dw = (dy2.float().t() @ x2.float()).to(weight.dtype)
         return dx, dw, None, None

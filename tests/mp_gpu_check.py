@@ -566,9 +566,10 @@ def ep_trainer():
         out[flat] = ([h["loss"] for h in hist], [h["grad_norm"] for h in hist])
     os.environ.pop("FORGEMINDS_FLAT_ENGINE", None)
     (la, na), (lb, nb) = out[True], out[False]
-    assert la[-1] < 0.9 * la[0], la
+    assert la[-1] < 0.6 * la[0] and lb[-1] < 0.6 * lb[0], (la, lb)
     assert abs(na[0] - nb[0]) < 2e-2 * nb[0], (na, nb)                       # same gradient before the first update
-    assert max(abs(x - y) for x, y in zip(la, lb)) < 0.03, (la, lb)
+    # the same trajectory while the routing agrees; a top-k choice that flips in one run sends the two apart
+    assert max(abs(x - y) for x, y in zip(la[:3], lb[:3])) < 0.03, (la, lb)
     if rank == 0:
         print("OK ep_trainer", flush=True)
 
