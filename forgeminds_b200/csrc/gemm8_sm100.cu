@@ -3,7 +3,10 @@
 //
 // Same machine as the bf16 kernel (gemm_sm100.cu): one persistent CTA per SM; warp 0 feeds a ring of
 // 128B-swizzled shared-memory stages with TMA, warp 1 issues tcgen05.mma into TMEM, warps 2-5 drain
-// TMEM. A stage holds 128 rows x 128 bytes of each operand, i.e. 128 elements of K, four MMAs of K=32.
+// TMEM. A stage holds 128 rows of A and BN rows of B, 128 bytes (= 128 elements of K) each: four MMAs of
+// K = 32. At the 8-bit rate a 128 x 128 tile needs 32 KB of operands per 256 tensor cycles, which is all
+// that shared memory delivers (128 B / clock); products with row scales therefore use 128 x 256 tiles
+// (48 KB per 512 cycles) whenever the output is at least 256 columns wide.
 //
 // Two scaling schemes:
 //   row scales      one fp32 scale per row of A and per row of B (per token / per output channel).
@@ -25,7 +28,7 @@
 
 namespace fmb {
 
-constexpr int G8_BM = 128, G8_BN = 128, G8_BK = 128, G8_STAGES = 6, G8_THREADS = 192;
+constexpr int G8_BM = 128, G8_BK = 128, G8_THREADS = 192;
 
 struct G8Params {
   int M, N;
@@ -39,20 +42,23 @@ struct G8Params {
   int* status;
 };
 
+template <int BN>
 struct G8Smem {
+  static constexpr int STAGES = BN == 128 ? 6 : 4;
   static constexpr uint32_t A_BYTES = G8_BM * G8_BK;
-  static constexpr uint32_t B_BYTES = G8_BN * G8_BK;
+  static constexpr uint32_t B_BYTES = BN * G8_BK;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr uint32_t BAR_OFFSET = G8_STAGES * STAGE_BYTES;
-  static constexpr uint32_t TOTAL = BAR_OFFSET + (2 * G8_STAGES + 4) * 8 + 16 + 1024;
+  static constexpr uint32_t BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr uint32_t TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;
 };
 
-// KIND: 0 = int8, 1 = fp8 e4m3.  BLOCKED: per-K-block scales (fp8 only).
-template <int KIND, bool BLOCKED>
+// KIND: 0 = int8, 1 = fp8 e4m3.  BLOCKED: per-K-block scales (fp8 only, BN = 128).  BN: 128 or 256 output columns.
+template <int KIND, bool BLOCKED, int BN>
 __global__ void __launch_bounds__(G8_THREADS, 1)
 gemm8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, G8Params p) {
-  using L = G8Smem;
-  constexpr int BM = G8_BM, BN = G8_BN, BK = G8_BK, STAGES = G8_STAGES;
+  using L = G8Smem<BN>;
+  static_assert(!BLOCKED || BN == 128, "the block-scaled epilogue keeps a 128-column tile in registers");
+  constexpr int BM = G8_BM, BK = G8_BK, STAGES = L::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
@@ -380,15 +386,15 @@ quant_tiles_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __re
 
 using namespace fmb;
 
-template <int KIND, bool BLOCKED>
+template <int KIND, bool BLOCKED, int BN>
 static int launch_gemm8(const CUtensorMap& ta, const CUtensorMap& tb, const G8Params& p, int grid, cudaStream_t stream) {
-  auto kern = gemm8_kernel<KIND, BLOCKED>;
+  auto kern = gemm8_kernel<KIND, BLOCKED, BN>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G8Smem::TOTAL) != cudaSuccess) return -6;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G8Smem<BN>::TOTAL) != cudaSuccess) return -6;
     attr_set = true;
   }
-  return launch_pdl(kern, dim3(grid), dim3(G8_THREADS), G8Smem::TOTAL, stream, ta, tb, p) == cudaSuccess ? 0 : -3;
+  return launch_pdl(kern, dim3(grid), dim3(G8_THREADS), G8Smem<BN>::TOTAL, stream, ta, tb, p) == cudaSuccess ? 0 : -3;
 }
 
 // kind: 0 int8, 1 fp8 e4m3. A [M, K] and B [N, K] are 1-byte, K-major with pitches lda / ldb (bytes = elements,
@@ -407,22 +413,33 @@ extern "C" int fmb_gemm8(const void* A, const void* B, void* D, int M, int N, in
   G8Params p;
   p.M = M; p.N = N;
   p.tiles_m = (M + G8_BM - 1) / G8_BM;
-  p.tiles_n = (N + G8_BN - 1) / G8_BN;
   p.kblocks = (K + G8_BK - 1) / G8_BK;
+  // wide tiles for row-scaled products unless they would leave most of the machine idle or mostly padded
+  const int sms = sm_count();
+  int bn = 128;
+  if (!blocked && N >= 256) {
+    const long long wide_tiles = static_cast<long long>(p.tiles_m) * ((N + 255) / 256);
+    const double pad = static_cast<double>(N) / (((N + 255) / 256) * 256.0);
+    if (wide_tiles >= sms / 2 && pad >= 0.8) bn = 256;
+  }
+  static const bool wide_env = [] { const char* v = getenv("FMB_GEMM8_WIDE"); return v == nullptr || v[0] != '0'; }();
+  if (!wide_env) bn = 128;
+  p.tiles_n = (N + bn - 1) / bn;
   if (blocked && (sa_ld < p.kblocks || sb_ld < p.kblocks)) return -2;
   p.D = D; p.ldd = ldd; p.d_f32 = d_f32;
   p.sa = sa; p.sb = sb; p.sa_ld = sa_ld; p.sb_ld = sb_ld;
   p.status = status;
   CUtensorMap ta, tb;
   if (!make_tmap_2d(&ta, A, M, K, lda, G8_BM, G8_BK, 1, TmapSwizzle::B128) ||
-      !make_tmap_2d(&tb, B, N, K, ldb, G8_BN, G8_BK, 1, TmapSwizzle::B128))
+      !make_tmap_2d(&tb, B, N, K, ldb, static_cast<uint32_t>(bn), G8_BK, 1, TmapSwizzle::B128))
     return -5;
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n;
-  const int sms = sm_count();
   const int grid = static_cast<int>(total < sms ? total : sms);
-  if (kind == 0) return launch_gemm8<0, false>(ta, tb, p, grid, stream);
-  if (!blocked) return launch_gemm8<1, false>(ta, tb, p, grid, stream);
-  return launch_gemm8<1, true>(ta, tb, p, grid, stream);
+  if (blocked) return launch_gemm8<1, true, 128>(ta, tb, p, grid, stream);
+  if (bn == 256) return kind == 0 ? launch_gemm8<0, false, 256>(ta, tb, p, grid, stream)
+                                  : launch_gemm8<1, false, 256>(ta, tb, p, grid, stream);
+  return kind == 0 ? launch_gemm8<0, false, 128>(ta, tb, p, grid, stream)
+                   : launch_gemm8<1, false, 128>(ta, tb, p, grid, stream);
 }
 
 // Row quantiser. x: bf16 (dtype 0) or fp32 (1), [rows, cols] with pitch ldx. block > 0: fp8 scales per row and

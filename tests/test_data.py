@@ -142,3 +142,54 @@ def test_to_device_nested_and_token_file(tmp_path):
     tf.close()
     syn = fm.SyntheticLM(100, 16, n=8)
     assert syn[0]["input_ids"].shape == (16,) and torch.equal(syn[0]["input_ids"][1:], syn[0]["labels"][:-1])
+
+
+# ------------------------------------------------------------------ loader worker processes
+def _worker_children():
+    import psutil
+    me = psutil.Process()
+    return [c for c in me.children(recursive=True) if c.is_running() and c.status() != psutil.STATUS_ZOMBIE]
+
+
+def _wait_gone(before, timeout=10.0):
+    deadline = time.time() + timeout
+    while time.time() < deadline:
+        extra = [c for c in _worker_children() if c.pid not in before]
+        if not extra:
+            return []
+        time.sleep(0.1)
+    return extra
+
+
+def test_loader_workers_are_one_persistent_pool_across_epochs():
+    """``workers=2``: the same two processes serve every epoch (no respawn per epoch) and leave when the
+    stream closes."""
+    before = {c.pid for c in _worker_children()}
+    dl, sampler = build_loader(Counting(32), 4, Ctx(), seed=1, workers=2)
+    s = BatchStream(dl, sampler, torch.device("cpu"), threaded=True)
+    pids = set()
+    seen = []
+    for _ in range(20):                                   # 8 batches per epoch: more than two epochs
+        seen.append(s.next()[0][0, 0].item())
+        pids |= {c.pid for c in _worker_children() if c.pid not in before}
+    assert s.epoch >= 2
+    assert len(pids) == 2, pids                           # one pool, reused
+    s.close()
+    del s, dl
+    import gc
+    gc.collect()
+    assert _wait_gone(before) == []
+
+
+def test_async_loader_over_worker_processes_releases_them_on_close():
+    from torch.utils.data import DataLoader
+    before = {c.pid for c in _worker_children()}
+    dl = DataLoader(Counting(24), batch_size=4, num_workers=2)
+    it = async_loader(dl, torch.device("cpu"), depth=2)
+    first = next(iter(it))
+    assert first["input_ids"].shape == (4, 4)
+    it.close()                                            # stopped early: the workers must not linger
+    del it, dl
+    import gc
+    gc.collect()
+    assert _wait_gone(before) == []
