@@ -91,7 +91,8 @@ class _QLinearMulti(torch.autograd.Function):
         y = C.gemm8(aq, wq, a_s, ws, KINDS[mode], False, status_word(x.device))
         ctx.save_for_backward(x2)
         ctx.weights, ctx.mode, ctx.block, ctx.x_shape = weights, mode, block, x.shape
-        return y.view(*x.shape[:-1], y.shape[-1])
+        # reshape the fresh tensor itself: a view returned from a Function could not be updated in place (RoPE does)
+        return y.resize_(*x.shape[:-1], y.shape[-1])
 
     @staticmethod
     @torch.autograd.function.once_differentiable

@@ -105,7 +105,9 @@ def test_fused_quantised_projection_equals_separate_ones(mode, cuda_status):
     xr = x.detach().clone().requires_grad_()
     y = qlinear_multi(x, tuple(l.weight for l in lins), mode, 128)
     want = torch.cat([cls.from_linear(l)(xr) for l in lins], dim=-1)
-    assert (y.float() - want.float()).norm() / want.float().norm() < 5e-3
+    # int8: identical integer products. fp8: the fused form quantises the bf16 copy of the weights, the modules
+    # the fp32 weights; a handful of e4m3 codes (3 mantissa bits) round the other way
+    assert (y.float() - want.float()).norm() / want.float().norm() < (5e-3 if mode == "int8" else 2e-2)
     g = _rand(y.shape, 4)
     y.backward(g)
     fused_grads = [l.weight.grad.clone() for l in lins]
@@ -114,7 +116,7 @@ def test_fused_quantised_projection_equals_separate_ones(mode, cuda_status):
     want.backward(g)
     assert (x.grad.float() - xr.grad.float()).norm() / xr.grad.float().norm() < 2e-2
     for a, l in zip(fused_grads, lins):
-        assert (a.float() - l.weight.grad.float()).norm() / l.weight.grad.float().norm() < 5e-3
+        assert (a.float() - l.weight.grad.float()).norm() / l.weight.grad.float().norm() < 5e-3      # bf16 products both
 
 
 @pytest.mark.parametrize("mode", ["int8", "fp8"])
