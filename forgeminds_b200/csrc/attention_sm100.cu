@@ -853,7 +853,7 @@ extern "C" int fmb_attn_bwd(const void* q, const void* k, const void* v, const v
     if (launch_pdl(kern, dim3(grid), dim3(ATT_BWD_THREADS), sm, stream, tq, tk, tv, tdo, tdq, p) != cudaSuccess) return -7;
   }
   if (cudaGetLastError() != cudaSuccess) return -7;
-  {
+  if (dq != nullptr) {   // a caller that consumes the fp32 sum itself (the RoPE backward) passes no dq
     const long long rows = static_cast<long long>(B) * T;
     const int width = Hq * hd;
     long long blocks = (rows * (width / 8) + 255) / 256;

@@ -192,17 +192,27 @@ void swiglu_bwd(const Tensor& gate, const Tensor& up, const Tensor& dy, Tensor& 
      "swiglu_bwd");
 }
 
+// q32 (optional, fp32 [rows, n_q, hd] packed): source of the first n_q heads instead of x
 void rope(const Tensor& x, Tensor& out, const Tensor& cos, const Tensor& sin, int64_t T, int64_t n_rot,
-          int64_t heads_total, int64_t hd, double sign) {
+          int64_t heads_total, int64_t hd, double sign, const c10::optional<Tensor>& q32) {
   cuda_contig(x, "x"); cuda_contig(out, "out"); cuda_contig(cos, "cos"); cuda_contig(sin, "sin");
   TORCH_CHECK(out.numel() == x.numel() && out.scalar_type() == x.scalar_type(), "rope: out must match x");
   TORCH_CHECK(cos.scalar_type() == at::kFloat && sin.scalar_type() == at::kFloat, "rope tables must be fp32");
   TORCH_CHECK(cos.numel() >= T * hd / 2, "rope table shorter than the sequence");
   const int64_t rows = x.numel() / (heads_total * hd);
+  const float* q32_ptr = nullptr;
+  int n_q32 = 0;
+  if (q32.has_value() && q32->defined()) {
+    cuda_contig(*q32, "q32");
+    TORCH_CHECK(q32->scalar_type() == at::kFloat && q32->numel() % (rows * hd) == 0, "rope: q32 must be fp32 [rows, n_q, hd]");
+    n_q32 = static_cast<int>(q32->numel() / (rows * hd));
+    TORCH_CHECK(n_q32 >= 1 && n_q32 <= n_rot, "rope: q32 holds more heads than are rotated");
+    q32_ptr = q32->data_ptr<float>();
+  }
   c10::cuda::CUDAGuard guard(x.device());
   ok(fmb_rope(x.data_ptr(), out.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), rows, static_cast<int>(T),
               static_cast<int>(n_rot), static_cast<int>(heads_total), static_cast<int>(hd), static_cast<float>(sign),
-              dt(x), cur_stream()), "rope");
+              dt(x), q32_ptr, n_q32, cur_stream()), "rope");
 }
 
 std::vector<Tensor> qk_norm_rope_fwd(const Tensor& x, const Tensor& w, const Tensor& cos, const Tensor& sin, double eps) {
@@ -791,10 +801,12 @@ std::vector<Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, 
   return {o, lse};
 }
 
-// writes dq/dk/dv into the given (possibly strided) views
-void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o, const Tensor& lse,
-              Tensor& dq, Tensor& dk, Tensor& dv, double scale, bool causal, const c10::optional<Tensor>& status,
-              const c10::optional<Tensor>& delta_in) {
+// writes dq/dk/dv into the given (possibly strided) views. Without dq the query gradient is only returned as
+// the fp32 sum [B, T, Hq, hd] the kernel accumulates (the caller's next pass converts it).
+Tensor attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o, const Tensor& lse,
+                const c10::optional<Tensor>& dq_out, Tensor& dk, Tensor& dv, double scale, bool causal,
+                const c10::optional<Tensor>& status, const c10::optional<Tensor>& delta_in) {
+  const bool have_dq = dq_out.has_value() && dq_out->defined();
   const int64_t B = q.size(0), T = q.size(1), Hq = q.size(2), hd = q.size(3), Hkv = k.size(2);
   TORCH_CHECK(d_o.is_contiguous() && o.is_contiguous(), "attention backward: o and d_o must be contiguous");
   TORCH_CHECK(dk.stride(1) == dv.stride(1), "attention backward: dk and dv must share a token pitch");
@@ -805,10 +817,13 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   Tensor dq_acc = torch::zeros({B, T, Hq, hd}, q.options().dtype(at::kFloat));
   int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
   ok(fmb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr<float>(),
-                  dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr<float>(), dq_acc.data_ptr<float>(),
+                  have_dq ? dq_out->data_ptr() : nullptr, dk.data_ptr(), dv.data_ptr(), delta.data_ptr<float>(),
+                  dq_acc.data_ptr<float>(),
                   static_cast<int>(B), static_cast<int>(T), static_cast<int>(Hq), static_cast<int>(Hkv),
-                  static_cast<int>(hd), q.stride(1), k.stride(1), o.stride(1), dq.stride(1), dk.stride(1),
-                  static_cast<float>(scale), causal, have_delta ? 1 : 0, st, cur_stream()), "attn_bwd", have_delta ? 2 : 3);
+                  static_cast<int>(hd), q.stride(1), k.stride(1), o.stride(1), have_dq ? dq_out->stride(1) : Hq * hd,
+                  dk.stride(1), static_cast<float>(scale), causal, have_delta ? 1 : 0, st, cur_stream()), "attn_bwd",
+     (have_delta ? 2 : 3) - (have_dq ? 0 : 1));
+  return dq_acc;
 }
 #endif
 
@@ -824,7 +839,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_fwd", &swiglu_fwd, pybind11::arg("gate"), pybind11::arg("up"), pybind11::arg("row_limit") = pybind11::none());
   m.def("swiglu_bwd", &swiglu_bwd, pybind11::arg("gate"), pybind11::arg("up"), pybind11::arg("dy"), pybind11::arg("dgate"),
         pybind11::arg("dup"), pybind11::arg("row_limit") = pybind11::none());
-  m.def("rope", &rope);
+  m.def("rope", &rope, pybind11::arg("x"), pybind11::arg("out"), pybind11::arg("cos"), pybind11::arg("sin"), pybind11::arg("T"),
+        pybind11::arg("n_rot"), pybind11::arg("heads_total"), pybind11::arg("hd"), pybind11::arg("sign"),
+        pybind11::arg("q32") = pybind11::none());
   m.def("qk_norm_rope_fwd", &qk_norm_rope_fwd);
   m.def("qk_norm_rope_bwd", &qk_norm_rope_bwd);
   m.def("softmax_fwd", &softmax_fwd);

@@ -284,10 +284,12 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ gate, const T* __restric
 
 // ------------------------------------------------------------------ RoPE (half-split)
 // Rotates the first n_rot heads of every row; the remaining heads are copied when dst != src.
+// With q32 given, the first n_q32 heads are read from that packed fp32 tensor [rows, n_q32, hd] instead of
+// src (the attention backward leaves dQ there as an fp32 sum; this pass is then also its conversion).
 template <typename T>
 __global__ void rope_kernel(const T* __restrict__ src, T* __restrict__ dst, const float* __restrict__ cs,
                             const float* __restrict__ sn, long long rows, int T_len, int n_rot, int heads_total, int hd,
-                            float sign) {
+                            float sign, const float* __restrict__ q32, int n_q32) {
   pdl_wait();
   pdl_launch_dependents();
   const int half = hd >> 1;
@@ -303,8 +305,14 @@ __global__ void rope_kernel(const T* __restrict__ src, T* __restrict__ dst, cons
     const long long row = rh / heads;
     const long long off = (row * heads_total + head) * hd + c;
     float a[8], b[8], oa[8], ob[8];
-    V8<T>::load(src + off, a);
-    V8<T>::load(src + off + half, b);
+    if (q32 != nullptr && head < n_q32) {
+      const long long off32 = (row * n_q32 + head) * hd + c;
+      V8<float>::load(q32 + off32, a);
+      V8<float>::load(q32 + off32 + half, b);
+    } else {
+      V8<T>::load(src + off, a);
+      V8<T>::load(src + off + half, b);
+    }
     if (head < n_rot) {
       const int pos = static_cast<int>(row % T_len);
       float co[8], si[8];
@@ -870,15 +878,17 @@ extern "C" int fmb_swiglu_bwd(const void* gate, const void* up, const void* dy, 
 }
 
 extern "C" int fmb_rope(const void* src, void* dst, const float* cos, const float* sin, long long rows, int T,
-                        int n_rot_heads, int heads_total, int hd, float sign, int dtype, cudaStream_t stream) {
+                        int n_rot_heads, int heads_total, int hd, float sign, int dtype, const float* q32, int n_q32,
+                        cudaStream_t stream) {
   if (rows <= 0 || n_rot_heads <= 0) return 0;
   if (hd % 16) return -2;
+  if (q32 != nullptr && (n_q32 <= 0 || n_q32 > n_rot_heads || (reinterpret_cast<uintptr_t>(q32) & 15))) return -2;
   const int heads = src == dst ? n_rot_heads : heads_total;
   return by_dtype(dtype, [&](auto* tp) {
     using Tt = std::remove_pointer_t<decltype(tp)>;
     return launch_pdl(rope_kernel<Tt>, dim3(grid_for(rows * heads * (hd / 16), 256)), dim3(256), 0, stream,
                       static_cast<const Tt*>(src), static_cast<Tt*>(dst), cos, sin, rows, T, n_rot_heads, heads_total,
-                      hd, sign) == cudaSuccess ? 0 : -3;
+                      hd, sign, q32, q32 ? n_q32 : 0) == cudaSuccess ? 0 : -3;
   });
 }
 

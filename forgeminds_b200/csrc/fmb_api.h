@@ -42,7 +42,7 @@ int fmb_swiglu_bwd(const void* gate, const void* up, const void* dy, void* dgate
 // src[rows, n_heads_total * hd] into dst (dst may be src; otherwise the other heads are copied);
 // position = row % T; sign = +1 forward, -1 backward.
 int fmb_rope(const void* src, void* dst, const float* cos, const float* sin, long long rows, int T, int n_rot_heads,
-             int heads_total, int hd, float sign, int dtype, cudaStream_t stream);
+             int heads_total, int hd, float sign, int dtype, const float* q32, int n_q32, cudaStream_t stream);
 int fmb_qk_norm_rope_fwd(const void* x, const void* w, const float* cos, const float* sin, void* y, float* rstd,
                          long long rows, int T, int H, int hd, float eps, int dtype, int w_dtype, cudaStream_t stream);
 int fmb_qk_norm_rope_bwd(const void* dy, const void* x, const void* w, const float* cos, const float* sin,

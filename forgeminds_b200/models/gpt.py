@@ -176,13 +176,13 @@ class Attention(nn.Module):
             xn = Fn.rms_norm(x, norm.weight, norm.eps)
             qkv = qlinear_multi(xn, (self.wq.weight, self.wk.weight, self.wv.weight), self.wq.mode, self.wq.block)
             cos, sin = rope_tables(T, hd, self.theta, x.device, torch.float32)
-            qkv = Fn.rope_qkv_(qkv, cos.reshape(T, hd // 2), sin.reshape(T, hd // 2), n_q, n_kv, hd)
-            return x + self.wo(Fn.attention_qkv(qkv, n_q, n_kv, hd, True))
+            rope = (cos.reshape(T, hd // 2), sin.reshape(T, hd // 2))
+            return x + self.wo(Fn.attention_qkv(qkv, n_q, n_kv, hd, True, rope=rope))
         qkv, x = Fn.norm_linear_multi(x, norm.weight, norm.eps, (self.wq.weight, self.wk.weight, self.wv.weight),
                                       passthrough=True)
         cos, sin = rope_tables(T, hd, self.theta, x.device, torch.float32)
-        qkv = Fn.rope_qkv_(qkv, cos.reshape(T, hd // 2), sin.reshape(T, hd // 2), n_q, n_kv, hd)
-        return Fn.attention_proj(qkv, self.wo.weight, x, n_q, n_kv, hd, True)
+        rope = (cos.reshape(T, hd // 2), sin.reshape(T, hd // 2))
+        return Fn.attention_proj(qkv, self.wo.weight, x, n_q, n_kv, hd, True, rope=rope)
 
 
 class SwiGLU(nn.Module):

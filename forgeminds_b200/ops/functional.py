@@ -547,23 +547,44 @@ def rope_qkv_(qkv, cos, sin, n_q, n_kv, hd):
 
 # ------------------------------------------------------------------------------ attention
 class _Attention(torch.autograd.Function):
+    """Causal GQA attention on a fused q|k|v buffer. With ``cos`` / ``sin`` the q and k heads are rotated in
+    place first (the buffer comes back as a second, dirty output) and the backward rotates the gradient
+    back in the pass that converts the kernel's fp32 dQ sum to bf16."""
+
     @staticmethod
-    def forward(ctx, qkv, n_q, n_kv, hd, causal):
+    def forward(ctx, qkv, n_q, n_kv, hd, causal, cos=None, sin=None):
         C = require()
         B, T, _ = qkv.shape
+        ctx.rope = cos is not None
+        if ctx.rope:
+            C.rope(qkv, qkv, cos, sin, T, n_q + n_kv, n_q + 2 * n_kv, hd, 1.0)
+            ctx.mark_dirty(qkv)
+            ctx.set_materialize_grads(False)
         q = qkv[..., : n_q * hd].unflatten(-1, (n_q, hd))
         k = qkv[..., n_q * hd: (n_q + n_kv) * hd].unflatten(-1, (n_kv, hd))
         v = qkv[..., (n_q + n_kv) * hd:].unflatten(-1, (n_kv, hd))
         o, lse = C.attn_fwd(q, k, v, 1.0 / math.sqrt(hd), causal, status_word(qkv.device))
-        ctx.save_for_backward(qkv, o, lse)
+        if ctx.rope:
+            ctx.save_for_backward(qkv, o, lse, cos, sin)
+        else:
+            ctx.save_for_backward(qkv, o, lse)
         ctx.dims = (n_q, n_kv, hd, causal)
-        return o.view(B, T, n_q * hd)
+        out = o.view(B, T, n_q * hd)
+        return (out, qkv) if ctx.rope else out
 
     @staticmethod
     @once_differentiable
-    def backward(ctx, d_o):
+    def backward(ctx, d_o, g_qkv=None):
         C = require()
-        qkv, o, lse = ctx.saved_tensors
+        cos = sin = None
+        if ctx.rope:
+            qkv, o, lse, cos, sin = ctx.saved_tensors
+            if g_qkv is not None:
+                raise RuntimeError("the rotated qkv buffer returned by attention_qkv is not differentiable")
+            if d_o is None:
+                return (None,) * 7
+        else:
+            qkv, o, lse = ctx.saved_tensors
         n_q, n_kv, hd, causal = ctx.dims
         B, T, _ = qkv.shape
         dqkv = torch.empty_like(qkv)
@@ -573,20 +594,35 @@ class _Attention(torch.autograd.Function):
         dq = dqkv[..., : n_q * hd].unflatten(-1, (n_q, hd))
         dk = dqkv[..., n_q * hd: (n_q + n_kv) * hd].unflatten(-1, (n_kv, hd))
         dv = dqkv[..., (n_q + n_kv) * hd:].unflatten(-1, (n_kv, hd))
-        C.attn_bwd(q, k, v, o, d_o.contiguous().view(B, T, n_q, hd), lse, dq, dk, dv, 1.0 / math.sqrt(hd), causal,
-                   status_word(qkv.device), None)
-        return dqkv, None, None, None, None
+        d_o4 = d_o.contiguous().view(B, T, n_q, hd)
+        scale, st = 1.0 / math.sqrt(hd), status_word(qkv.device)
+        if ctx.rope:
+            dq32 = C.attn_bwd(q, k, v, o, d_o4, lse, None, dk, dv, scale, causal, st, None)
+            C.rope(dqkv, dqkv, cos, sin, T, n_q + n_kv, n_q + 2 * n_kv, hd, -1.0, dq32)
+        else:
+            C.attn_bwd(q, k, v, o, d_o4, lse, dq, dk, dv, scale, causal, st, None)
+        return dqkv, None, None, None, None, None, None
 
 
 class _AttentionProj(torch.autograd.Function):
     """``attention(qkv) @ Wo.T + residual`` as one autograd node. In the backward, the product that
     yields ``dO = dY @ Wo`` also emits ``delta = rowsum(dO * O)`` per head from its epilogue, so the
-    attention backward needs no separate pass over ``O`` and ``dO``."""
+    attention backward needs no separate pass over ``O`` and ``dO``.
+
+    With ``cos`` / ``sin`` the q and k heads of ``qkv`` are first rotated in place (RoPE), and the backward
+    rotates the gradient back in the same pass that converts the fp32 dQ sum of the attention kernel to
+    bf16, so that sum is read once and no separate conversion kernel runs. ``qkv`` then comes back as a
+    second (dirty) output."""
 
     @staticmethod
-    def forward(ctx, qkv, weight, residual, n_q, n_kv, hd, causal):
+    def forward(ctx, qkv, weight, residual, n_q, n_kv, hd, causal, cos=None, sin=None):
         C = require()
         B, T, _ = qkv.shape
+        ctx.rope = cos is not None
+        if ctx.rope:
+            C.rope(qkv, qkv, cos, sin, T, n_q + n_kv, n_q + 2 * n_kv, hd, 1.0)
+            ctx.mark_dirty(qkv)
+            ctx.set_materialize_grads(False)
         q = qkv[..., : n_q * hd].unflatten(-1, (n_q, hd))
         k = qkv[..., n_q * hd: (n_q + n_kv) * hd].unflatten(-1, (n_kv, hd))
         v = qkv[..., (n_q + n_kv) * hd:].unflatten(-1, (n_kv, hd))
@@ -600,16 +636,27 @@ class _AttentionProj(torch.autograd.Function):
                 res2 = res2.contiguous()
         y = torch.empty((B, T, w.shape[0]), dtype=BF16, device=qkv.device)
         gemm(o2, w, out=y.view(B * T, w.shape[0]), c=res2, beta=1.0 if res2 is not None else 0.0)
-        ctx.save_for_backward(qkv, o, lse, w)
+        if ctx.rope:
+            ctx.save_for_backward(qkv, o, lse, w, cos, sin)
+        else:
+            ctx.save_for_backward(qkv, o, lse, w)
         ctx.weight = weight
         ctx.dims = (n_q, n_kv, hd, causal, residual is not None)
-        return y
+        return (y, qkv) if ctx.rope else y
 
     @staticmethod
     @once_differentiable
-    def backward(ctx, dy):
+    def backward(ctx, dy, g_qkv=None):
         C = require()
-        qkv, o, lse, w = ctx.saved_tensors
+        cos = sin = None
+        if ctx.rope:
+            qkv, o, lse, w, cos, sin = ctx.saved_tensors
+            if g_qkv is not None:
+                raise RuntimeError("the rotated qkv buffer returned by attention_proj is not differentiable")
+            if dy is None:
+                return (None,) * 9
+        else:
+            qkv, o, lse, w = ctx.saved_tensors
         weight = ctx.weight
         n_q, n_kv, hd, causal, has_res = ctx.dims
         B, T, _ = qkv.shape
@@ -643,13 +690,21 @@ class _AttentionProj(torch.autograd.Function):
             dq = dqkv[..., : n_q * hd].unflatten(-1, (n_q, hd))
             dk = dqkv[..., n_q * hd: (n_q + n_kv) * hd].unflatten(-1, (n_kv, hd))
             dv = dqkv[..., (n_q + n_kv) * hd:].unflatten(-1, (n_kv, hd))
-            C.attn_bwd(q, k, v, o, d_o.view(B, T, n_q, hd), lse, dq, dk, dv, 1.0 / math.sqrt(hd), causal, st, delta)
-        return dqkv, dw, (dy if has_res else None), None, None, None, None
+            if ctx.rope:
+                dq32 = C.attn_bwd(q, k, v, o, d_o.view(B, T, n_q, hd), lse, None, dk, dv, 1.0 / math.sqrt(hd), causal,
+                                  st, delta)
+                C.rope(dqkv, dqkv, cos, sin, T, n_q + n_kv, n_q + 2 * n_kv, hd, -1.0, dq32)
+            else:
+                C.attn_bwd(q, k, v, o, d_o.view(B, T, n_q, hd), lse, dq, dk, dv, 1.0 / math.sqrt(hd), causal, st, delta)
+        return dqkv, dw, (dy if has_res else None), None, None, None, None, None, None
 
 
-def attention_proj(qkv, weight, residual, n_q, n_kv, hd, causal=True):
-    """Causal GQA attention on a fused q|k|v buffer followed by the output projection (+ residual)."""
-    return _AttentionProj.apply(qkv, weight, residual, n_q, n_kv, hd, causal)
+def attention_proj(qkv, weight, residual, n_q, n_kv, hd, causal=True, rope=None):
+    """Causal GQA attention on a fused q|k|v buffer followed by the output projection (+ residual).
+    ``rope=(cos, sin)`` rotates the q and k heads of ``qkv`` in place first."""
+    if rope is None:
+        return _AttentionProj.apply(qkv, weight, residual, n_q, n_kv, hd, causal)
+    return _AttentionProj.apply(qkv, weight, residual, n_q, n_kv, hd, causal, rope[0], rope[1])[0]
 
 
 # Whether the SwiGLU runs in the epilogue of the neighbouring product (forward: gate|up product; backward:
@@ -732,9 +787,12 @@ def mlp_block(x, norm_w, eps, w1, w3, w2):
     return _MLPBlock.apply(x, norm_w, eps, w1, w3, w2)
 
 
-def attention_qkv(qkv, n_q, n_kv, hd, causal=True):
-    """Causal GQA flash attention reading q, k, v as slices of one fused projection output."""
-    return _Attention.apply(qkv, n_q, n_kv, hd, causal)
+def attention_qkv(qkv, n_q, n_kv, hd, causal=True, rope=None):
+    """Causal GQA flash attention reading q, k, v as slices of one fused projection output.
+    ``rope=(cos, sin)`` rotates the q and k heads of ``qkv`` in place first."""
+    if rope is None:
+        return _Attention.apply(qkv, n_q, n_kv, hd, causal)
+    return _Attention.apply(qkv, n_q, n_kv, hd, causal, rope[0], rope[1])[0]
 
 
 # ------------------------------------------------------------------------------ fused lm_head + cross-entropy

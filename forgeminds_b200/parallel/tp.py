@@ -334,8 +334,8 @@ def block_forward(blk, x_shard, state: TPState):
     B, T = blk._fm_bt
     qkv = qkv.view(B, T, -1)
     cos, sin = rope_tables(T, hd, at.theta, qkv.device, torch.float32)
-    qkv = Fn.rope_qkv_(qkv, cos.reshape(T, hd // 2), sin.reshape(T, hd // 2), nq, nkv, hd)
-    o = Fn.attention_qkv(qkv, nq, nkv, hd, True)               # [B, T, nq * hd]
+    o = Fn.attention_qkv(qkv, nq, nkv, hd, True,                # [B, T, nq * hd]
+                         rope=(cos.reshape(T, hd // 2), sin.reshape(T, hd // 2)))
     h = linear_scatter(o.reshape(B * T, nq * hd), at.wo.weight, x_shard, state)
     hn = Fn.rms_norm(h, blk.ffn_norm.weight, blk.ffn_norm.eps)
     gu = gather_linear(hn, (ff.w1.weight, ff.w3.weight), state)                   # [M, 2 * hidden_local]

@@ -77,3 +77,41 @@ def test_backward(B, T, Hq, Hkv, hd, causal, cuda_status):
         a, b = got[..., lo:hi], want[..., lo:hi]
         rel = (a - b).norm() / b.norm().clamp(min=1e-6)
         assert rel < 2.5e-2, f"{name}: relative error {rel}"
+
+
+@pytest.mark.parametrize("B,T,Hq,Hkv,hd", [(2, 256, 4, 2, 64), (1, 1100, 8, 2, 80), (1, 512, 8, 2, 128)])
+def test_rope_folded_into_attention(B, T, Hq, Hkv, hd, cuda_status):
+    """RoPE applied inside the attention node (backward rotation reads the fp32 dQ sum) against the
+    separate rotate-then-attend nodes and against fp32 autograd."""
+    from forgeminds_b200.models.gpt import rope_tables
+    from forgeminds_b200.ops import functional as Fn
+    cos, sin = rope_tables(T, hd, 10000.0, "cuda", torch.float32)
+    cos, sin = cos.reshape(T, hd // 2).contiguous(), sin.reshape(T, hd // 2).contiguous()
+    raw = _qkv(B, T, Hq, Hkv, hd, 3)
+    g = torch.randn(B, T, Hq * hd, device="cuda", dtype=torch.bfloat16)
+    grads = []
+    for folded in (True, False):
+        leaf = raw.clone().requires_grad_()
+        x = leaf * 1.0                                  # a non-leaf buffer the node may rotate in place
+        if folded:
+            out = Fn.attention_qkv(x, Hq, Hkv, hd, True, rope=(cos, sin))
+        else:
+            out = Fn.attention_qkv(Fn.rope_qkv_(x, cos, sin, Hq, Hkv, hd), Hq, Hkv, hd, True)
+        out.backward(g)
+        grads.append((out.detach().float(), leaf.grad.float()))
+    assert torch.equal(grads[0][0], grads[1][0])
+    rel = (grads[0][1] - grads[1][1]).norm() / grads[1][1].norm()
+    assert rel < 1e-2, rel
+
+    # fp32 reference of rotate + attend
+    ref_in = raw.float().requires_grad_()
+    n_rot = Hq + Hkv
+    heads = ref_in.unflatten(-1, (Hq + 2 * Hkv, hd))
+    a, b = heads[..., : hd // 2], heads[..., hd // 2:]
+    c, s = cos[None, :, None, :], sin[None, :, None, :]
+    rot = torch.cat([a * c - b * s, a * s + b * c], -1)
+    heads = torch.cat([rot[:, :, :n_rot], heads[:, :, n_rot:]], 2)
+    ro, _ = _ref(heads[:, :, :Hq], heads[:, :, Hq:n_rot], heads[:, :, n_rot:], True)
+    ro.reshape(B, T, Hq * hd).backward(g.float())
+    rel = (grads[0][1] - ref_in.grad).norm() / ref_in.grad.norm()
+    assert rel < 2.5e-2, rel
