@@ -152,3 +152,37 @@ def test_gemmbench_is_registered_and_refuses_to_run_without_a_gpu(capsys):
     if not torch.cuda.is_available():
         assert gemmbench.main([]) == 1
         assert "needs a GPU" in capsys.readouterr().out
+
+
+# ------------------------------------------------------------------ compile check and probe
+PTXAS_SAMPLE = """
+ptxas info    : Compiling entry function '_ZN3fmb6kern_aEv' for 'sm_100a'
+ptxas info    : Function properties for _ZN3fmb6kern_aEv
+    0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads
+ptxas info    : Used 40 registers, used 1 barriers, 1024 bytes smem
+ptxas info    : Compiling entry function '_ZN3fmb6kern_bEv' for 'sm_100a'
+ptxas info    : Function properties for _ZN3fmb6kern_bEv
+    800 bytes stack frame, 640 bytes spill stores, 700 bytes spill loads
+ptxas info    : Used 255 registers, used 0 barriers
+"""
+
+
+def test_compilecheck_reads_the_assembler_report_and_flags_spills():
+    from forgeminds_b200.cli import compilecheck as cc
+    rows = cc.parse_ptxas(PTXAS_SAMPLE)
+    assert [r["registers"] for r in rows] == [40, 255]
+    assert rows[0]["smem"] == 1024 and rows[0]["barriers"] == 1 and rows[0]["spill_stores"] == 0
+    assert rows[1]["stack"] == 800 and rows[1]["spill_stores"] == 640 and rows[1]["spill_loads"] == 700
+    for r, name in zip(rows, cc.demangle([r["name"] for r in rows])):
+        r["pretty"] = name
+    assert "kern_a" in rows[0]["pretty"]
+    bad = cc.problems(rows, max_spill=512)
+    assert len(bad) == 1 and "kern_b" in bad[0]
+    assert cc.problems(rows, max_spill=2000) == [] and len(cc.warnings(rows, max_spill=2000)) == 1
+
+
+def test_probe_runs_every_case_on_cpu():
+    from forgeminds_b200.cli import probe
+    rows = probe.run(torch.device("cpu"), torch.float32)
+    assert len(rows) >= 10 and all(r["ok"] for r in rows), [r for r in rows if not r["ok"]]
+    assert probe.main(["--device", "cpu", "--json"]) == 0
