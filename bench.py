@@ -236,9 +236,23 @@ def build_reference(args, world):
     ds = Tokens(spec["model"]["vocab_size"], spec["seq"], n=max(256, spec["micro_batch"] * spec["grad_accum"] * world * 8))
 
     def make(ctx):
-        return _on_device(ctx, lambda: fm.GPT(mc, fm.moe_kwargs(ctx, cfg) if args.config == "moe" else None))
+        build = lambda: fm.GPT(mc, fm.moe_kwargs(ctx, cfg) if args.config == "moe" else None)   # noqa: E731
+        # the reference builds on the host and moves the model (its expert re-initialisation draws from a host
+        # generator); only the multi-billion-parameter configurations are built on the GPU, for host memory
+        return _on_device(ctx, build) if args.config in ("llama8b", "gpt2p7b") else build()
     trainer = fm.Trainer(make, cfg, ds, micro_batch=spec["micro_batch"])
     return trainer, fm
+
+
+def reference_failed(rank, exc):
+    """The unmodified reference raised on its own stock path (for example its fused AdamW over a mix of plain
+    and distributed tensors when a tensor-parallel mesh has no sharded data-parallel axis): say so in the
+    contract's ``unavailable`` form and leave without waiting for the other ranks' teardown."""
+    if rank == 0:
+        why = f"the reference raised {type(exc).__name__}: {str(exc).splitlines()[0][:300] if str(exc) else ''}"
+        print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+    sys.stdout.flush()
+    os._exit(0)
 
 
 def full_model_flops_per_token(spec, moe: bool) -> int:
@@ -293,7 +307,10 @@ def main() -> int:
     args.warmup = max(3, args.warmup)
 
     if args.impl == "reference":
-        trainer, fm = build_reference(args, world)
+        try:
+            trainer, fm = build_reference(args, world)
+        except Exception as e:                      # noqa: BLE001 - any failure of the stock path is reported, not hidden
+            reference_failed(rank, e)
         if trainer is None:
             if rank == 0:
                 print(json.dumps({"impl": "reference", "unavailable": fm}))
@@ -317,8 +334,13 @@ def main() -> int:
     # ---- device-timed: batches resident on the GPU
     host_feed = trainer.feed
     trainer.feed = DeviceFeed(vocab, device, micro_batch, seq)
-    for _ in range(args.warmup):
-        trainer.train_step()
+    try:
+        for _ in range(args.warmup):
+            trainer.train_step()
+    except Exception as e:                          # noqa: BLE001
+        if args.impl != "reference":
+            raise
+        reference_failed(rank, e)
     launches0 = ops.require().launch_count() if ours else 0
     torch.cuda.reset_peak_memory_stats(device)
     with ClockSampler(device.index or 0) as clocks:

@@ -397,7 +397,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t bars = sbase + L::BAR_OFF;
   const uint32_t kv_full = bars, qdo_full0 = bars + 8, qdo_empty0 = bars + 24, sdp_full = bars + 40,
                  pds_ready = bars + 48, pds_free = bars + 56, dq_full = bars + 64, dq_free = bars + 72,
-                 dkv_full = bars + 80;
+                 dkv_full = bars + 80, sdp_read = bars + 88;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::BAR_OFF + 16 * 8);
   AbortState* ab = reinterpret_cast<AbortState*>(tmem_slot + 1);
 
@@ -421,6 +421,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(dq_full, 1);
     mbar_init(dq_free, 4);
     mbar_init(dkv_full, 1);
+    mbar_init(sdp_read, ATT_ROW_WARPS);
     ab->flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
@@ -498,15 +499,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           issue_sdp(st);
           umma_commit(sdp_full);
         }
-        if (!mbar_wait_bounded(pds_ready, it & 1, ab, p.status, ERR_WAIT_MISC)) break;
-        tc_fence_after();
         if (!ALIAS && it + 1 < n_it) {
+          // S and dP of the next query tile are issued as soon as the P / dS warps hold this tile's in
+          // registers (sdp_read), so they run under those warps' exponentials and stores
           const int nst = (it + 1) % STAGES;
+          if (!mbar_wait_bounded(sdp_read, it & 1, ab, p.status, ERR_WAIT_TMEM_EMPTY)) break;
           if (!mbar_wait_bounded(qdo_full0 + 8 * nst, ((it + 1) / STAGES) & 1, ab, p.status, ERR_WAIT_FULL)) break;
           tc_fence_after();
           issue_sdp(nst);
           umma_commit(sdp_full);
         }
+        if (!mbar_wait_bounded(pds_ready, it & 1, ab, p.status, ERR_WAIT_MISC)) break;
         if (!ALIAS && it > 0 && !mbar_wait_bounded(dq_free, (it - 1) & 1, ab, p.status, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         // dV += P^T dO ; dK += dS^T Q ; dQ = dS K      (reduction over 128 rows in 8 slices of 16)
@@ -544,14 +547,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t t_lane = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
     const float LOG2E = 1.4426950408889634f;
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
+    // row statistics of query tile `it`: fetched one iteration ahead, their latency would otherwise sit
+    // between the arrival of S / dP and the first exponential
+    auto row_stats = [&](int it, float& lse_v, float& dlt_v) {
       const int g = it / n_i, i = i0 + it % n_i;
-      const int h = hk * G + g;
+      const int q_idx = i * ATT_BM + row;
+      const long long stat = (static_cast<long long>(b) * p.Hq + (hk * G + g)) * p.T + q_idx;
+      const bool live = it < n_it && q_idx < p.T;
+      lse_v = live ? p.lse[stat] : 0.f;
+      dlt_v = live ? p.delta[stat] : 0.f;
+    };
+    float lse_nxt, dlt_nxt;
+    row_stats(0, lse_nxt, dlt_nxt);
+    for (int it = 0; it < n_it; ++it) {
+      const int i = i0 + it % n_i;
       const int q_idx = i * ATT_BM + row;
       const bool q_live = q_idx < p.T;
-      const long long stat = (static_cast<long long>(b) * p.Hq + h) * p.T + q_idx;
-      const float lse_l2 = q_live ? p.lse[stat] * LOG2E : 0.f;
-      const float dlt_s = q_live ? p.delta[stat] * p.scale : 0.f;
+      const float lse_l2 = lse_nxt * LOG2E;
+      const float dlt_s = dlt_nxt * p.scale;
+      row_stats(it + 1, lse_nxt, dlt_nxt);
       ok = mbar_wait_bounded(sdp_full, it & 1, ab, p.status, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       tc_fence_after();
@@ -563,15 +577,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!q_live) limit = 0;
       const int c_lo = half * 64;
       const bool masked = __any_sync(0xffffffffu, limit < c_lo + 64);
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c0 = c_lo + cc * 32;
-        uint32_t rs[32], rd[32];
-        tmem_ld_32x32(t_lane + S_COL + c0, rs);
-        tmem_ld_32x32(t_lane + DP_COL + c0, rd);
-        tmem_ld_fence(rs);
-        tmem_ld_fence(rd);
-        uint32_t pp[16], dd[16];
+      // 32 columns of S and dP -> bf16 pairs of P and dS
+      auto p_ds = [&](const uint32_t (&rs)[32], const uint32_t (&rd)[32], int c0, uint32_t (&pp)[16], uint32_t (&dd)[16]) {
         if (!masked) {
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
@@ -596,18 +603,39 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             dd[e >> 1] = pack_bf16(d0, d1);
           }
         }
-        if (cc == 0 && it > 0) {
-          // P / dS of the previous iteration must have been consumed before they are overwritten
-          ok = mbar_wait_bounded(pds_free, (it - 1) & 1, ab, p.status, ERR_WAIT_MISC);
-          if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-        }
+      };
+      auto put = [&](int cc, const uint32_t (&pp)[16], const uint32_t (&dd)[16]) {
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const uint32_t off = swz_tile_offset(row, half * 8 + cc * 4 + q4);
           *reinterpret_cast<uint4*>(smem + L::P_OFF + off) = make_uint4(pp[4 * q4], pp[4 * q4 + 1], pp[4 * q4 + 2], pp[4 * q4 + 3]);
           *reinterpret_cast<uint4*>(smem + L::DS_OFF + off) = make_uint4(dd[4 * q4], dd[4 * q4 + 1], dd[4 * q4 + 2], dd[4 * q4 + 3]);
         }
+      };
+      uint32_t pp0[16], dd0[16];
+      uint32_t rs[32], rd[32];
+      tmem_ld_32x32(t_lane + S_COL + c_lo, rs);
+      tmem_ld_32x32(t_lane + DP_COL + c_lo, rd);
+      tmem_ld_fence(rs);
+      tmem_ld_fence(rd);
+      p_ds(rs, rd, c_lo, pp0, dd0);
+      if (it > 0) {
+        // P / dS of the previous iteration must have been consumed before they are overwritten
+        ok = mbar_wait_bounded(pds_free, (it - 1) & 1, ab, p.status, ERR_WAIT_MISC);
+        if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       }
+      put(0, pp0, dd0);
+      tmem_ld_32x32(t_lane + S_COL + c_lo + 32, rs);
+      tmem_ld_32x32(t_lane + DP_COL + c_lo + 32, rd);
+      tmem_ld_fence(rs);
+      tmem_ld_fence(rd);
+      // S and dP of this tile are in registers: the tensor pipe may overwrite them with the next tile's
+      // while this warp is still busy with the second half's exponentials and stores
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sdp_read);
+      p_ds(rs, rd, c_lo + 32, pp0, dd0);
+      put(1, pp0, dd0);
       if (!ok) break;
       fence_proxy_async_smem();
       tc_fence_before();
