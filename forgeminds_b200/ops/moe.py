@@ -60,26 +60,33 @@ class _Route(torch.autograd.Function):
 
 
 class _Experts(torch.autograd.Function):
-    """Gather, SwiGLU experts, weighted combine for an already planned routing."""
+    """Gather, SwiGLU experts, weighted combine for an already planned routing.
+
+    ``limit`` (device int, first row past the last expert's region) is given for dropless plans: every row
+    tile below it belongs to an expert and is written whole by the grouped products (padding rows of the
+    gathered input are zero, so theirs are too), and nothing below reads a row at or past it, so the
+    buffers need no clearing. With a capacity an unused tile inside a region would feed stale values into
+    the expert weight gradients: those (bounded) buffers are cleared."""
 
     @staticmethod
-    def forward(ctx, x, route_w, w1, w3, w2, slot_of, token_of, region, tile_group, k):
+    def forward(ctx, x, route_w, w1, w3, w2, slot_of, token_of, region, tile_group, k, limit=None):
         C = require()
         st = status_word(x.device)
         n, d = x.shape
         S = token_of.numel()
         h = w1.shape[2]
+        alloc = torch.empty if limit is not None else torch.zeros
         b1, b3, b2 = bf16_of(w1), bf16_of(w3), bf16_of(w2)
         xs = C.moe_gather(x, token_of)
-        gu = torch.zeros((S, 2 * h), dtype=BF16, device=x.device)
+        gu = alloc((S, 2 * h), dtype=BF16, device=x.device)
         C.gemm_grouped_rows(xs, b1, gu[:, :h], tile_group, True, False, st)
         C.gemm_grouped_rows(xs, b3, gu[:, h:], tile_group, True, False, st)
-        act = C.swiglu_fwd(gu[:, :h], gu[:, h:])
-        ys = torch.zeros((S, d), dtype=BF16, device=x.device)
+        act = C.swiglu_fwd(gu[:, :h], gu[:, h:], limit)
+        ys = alloc((S, d), dtype=BF16, device=x.device)
         C.gemm_grouped_rows(act, b2, ys, tile_group, True, False, st)
         rw = route_w.detach().to(torch.float32).contiguous()
         out = C.moe_combine(ys, slot_of, rw, n, k)
-        ctx.save_for_backward(xs, gu, ys, rw, slot_of, region, tile_group, b1, b3, b2)
+        ctx.save_for_backward(xs, gu, ys, rw, slot_of, region, tile_group, b1, b3, b2, limit)
         ctx.params = (w1, w3, w2)
         ctx.dims = (n, d, h, k, route_w.dtype)
         return out
@@ -88,14 +95,15 @@ class _Experts(torch.autograd.Function):
     @once_differentiable
     def backward(ctx, dout):
         C = require()
-        xs, gu, ys, rw, slot_of, region, tile_group, b1, b3, b2 = ctx.saved_tensors
+        xs, gu, ys, rw, slot_of, region, tile_group, b1, b3, b2, limit = ctx.saved_tensors
         w1, w3, w2 = ctx.params
         n, d, h, k, rw_dtype = ctx.dims
         st = status_word(dout.device)
         S = xs.shape[0]
+        alloc = torch.empty if limit is not None else torch.zeros
         dout = dout.contiguous()
-        dys, drw = C.moe_combine_bwd(dout, ys, slot_of, rw, k)
-        act = C.swiglu_fwd(gu[:, :h], gu[:, h:])                              # recomputed
+        dys, drw = C.moe_combine_bwd(dout, ys, slot_of, rw, k)                # zero in rows that hold no entry
+        act = C.swiglu_fwd(gu[:, :h], gu[:, h:], limit)                       # recomputed
         grads = {}
 
         def wgrad(name, param, a, b):
@@ -109,33 +117,37 @@ class _Experts(torch.autograd.Function):
                 grads[name] = g if g.dtype == param.dtype else g.to(param.dtype)
 
         wgrad("w2", w2, act, dys)
-        dact = torch.zeros((S, h), dtype=BF16, device=dout.device)
+        dact = alloc((S, h), dtype=BF16, device=dout.device)
         C.gemm_grouped_rows(dys, b2, dact, tile_group, False, False, st)      # dys @ w2[e]^T
-        dgu = torch.zeros_like(gu)
-        C.swiglu_bwd(gu[:, :h], gu[:, h:], dact, dgu[:, :h], dgu[:, h:])
+        dgu = alloc(gu.shape, dtype=BF16, device=dout.device)
+        C.swiglu_bwd(gu[:, :h], gu[:, h:], dact, dgu[:, :h], dgu[:, h:], limit)
         wgrad("w1", w1, xs, dgu[:, :h])
         wgrad("w3", w3, xs, dgu[:, h:])
-        dxs = torch.zeros((S, d), dtype=BF16, device=dout.device)
+        dxs = alloc((S, d), dtype=BF16, device=dout.device)
         C.gemm_grouped_rows(dgu[:, :h], b1, dxs, tile_group, False, False, st)
         C.gemm_grouped_rows(dgu[:, h:], b3, dxs, tile_group, False, True, st)
         dx = C.moe_combine(dxs, slot_of, None, n, k)
-        return dx, drw.view(n, k).to(rw_dtype), grads["w1"], grads["w3"], grads["w2"], None, None, None, None, None
+        return dx, drw.view(n, k).to(rw_dtype), grads["w1"], grads["w3"], grads["w2"], None, None, None, None, None, None
 
 
 def plan(idx, n_experts: int, capacity: int = 0):
-    """Slot plan for ``idx [N, k]`` (int32): ``(slot_of_entry, token_of_slot, region, tile_group)``.
-    ``capacity > 0`` gives every expert a fixed region of ``ceil128(capacity)`` rows."""
+    """Slot plan for ``idx [N, k]`` (int32): ``(slot_of_entry, token_of_slot, region, tile_group, limit)``.
+    ``capacity > 0`` gives every expert a fixed region of ``ceil128(capacity)`` rows (``limit`` is None);
+    a dropless plan also returns ``limit``, a device int holding the first row past the last region."""
     C = require()
     n, k = idx.shape
     if capacity > 0:
         cap = (capacity + 127) // 128 * 128
         slots = n_experts * cap
         slot_of, token_of, region, _ = C.moe_plan(idx, n_experts, 128, cap, 1, slots)
+        limit = None
     else:
-        slots = (n * k + 127) // 128 * 128 + n_experts * 128
-        slot_of, token_of, region, _ = C.moe_plan(idx, n_experts, 128, 0, 0, slots)
+        # one more (always empty) expert: its region starts where the live rows end
+        slots = (n * k + 127) // 128 * 128 + (n_experts + 1) * 128
+        slot_of, token_of, region, _ = C.moe_plan(idx, n_experts + 1, 128, 0, 0, slots)
+        limit, region = region[n_experts], region[:n_experts]
     tile_group = C.moe_tile_groups(region, slots // 128)
-    return slot_of, token_of, region, tile_group
+    return slot_of, token_of, region, tile_group, limit
 
 
 def moe_forward_native(moe, x):
@@ -152,9 +164,9 @@ def moe_forward_native(moe, x):
         logits = torch.nn.functional.linear(x, gate.to(x.dtype))
     route_w, idx, aux, _counts = _Route.apply(logits, moe.top_k, moe.aux_coef, moe.z_coef)
     moe.last_aux = aux
-    slot_of, token_of, region, tile_group = plan(idx, moe.n_experts, moe.capacity(x.shape[0]))
+    slot_of, token_of, region, tile_group, limit = plan(idx, moe.n_experts, moe.capacity(x.shape[0]))
     ex = moe.experts
-    out = _Experts.apply(x, route_w, ex.w1, ex.w3, ex.w2, slot_of, token_of, region, tile_group, moe.top_k)
+    out = _Experts.apply(x, route_w, ex.w1, ex.w3, ex.w2, slot_of, token_of, region, tile_group, moe.top_k, limit)
     if moe.shared is not None:
         from .functional import linear_multi, swiglu_linear
         gu = linear_multi(x, (moe.shared.w1.weight, moe.shared.w3.weight))

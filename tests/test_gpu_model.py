@@ -84,6 +84,9 @@ def test_moe_native_matches_torch_path(cuda_status):
     ref = copy.deepcopy(moe)
     x = (torch.randn(1000, 256, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
     xr = x.detach().clone().requires_grad_()
+    # the dropless path takes its row buffers uncleared: hand the allocator blocks full of NaN to reuse
+    junk = [torch.full((8 << 20,), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(4)]
+    del junk
     out = moe(x)                               # bf16 CUDA input -> kernels
     assert moe.last_aux is not None
     with torch.autocast("cuda", dtype=torch.bfloat16):
@@ -92,11 +95,15 @@ def test_moe_native_matches_torch_path(cuda_status):
     assert (out.float() - want.float()).abs().max() < 0.05
     assert abs(moe.last_aux.item() - (ref.aux_coef * aux_r + ref.z_coef * z_r).item()) < 2e-3
     g = torch.randn_like(out)
+    junk = [torch.full((8 << 20,), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(4)]
+    del junk
     (out.float() * g.float()).sum().backward()
     (want.float() * g.float()).sum().backward()
+    assert torch.isfinite(x.grad).all()
     assert (x.grad.float() - xr.grad.float()).norm() / xr.grad.float().norm() < 0.08
     for name in ("w1", "w3", "w2"):
         a, b = getattr(moe.experts, name).grad.float(), getattr(ref.experts, name).grad.float()
+        assert torch.isfinite(a).all(), name
         assert (a - b).norm() / b.norm() < 0.08, name
 
 
