@@ -707,21 +707,24 @@ std::vector<Tensor> moe_combine_bwd(const Tensor& dout, const Tensor& ys, const 
 
 // Row-grouped product: out[rows, N] = a[rows, K] @ B[group(row)]^T where `b` is [G, N, K] (b_mn=false)
 // or [G, K, N] (b_mn=true) and `tile_group[rows / 128]` names the group of each 128-row tile (-1: skip).
+// pair_aligned: every group starts on a multiple of 256 rows (and the row count is one), so 256-row tiles on CTA
+// pairs may serve the product
 void gemm_grouped_rows(const Tensor& a, const Tensor& b, Tensor& out, const Tensor& tile_group, bool b_mn,
-                       bool accumulate, const c10::optional<Tensor>& status) {
+                       bool accumulate, const c10::optional<Tensor>& status, bool pair_aligned) {
   TORCH_CHECK(a.is_cuda() && a.dim() == 2 && b.dim() == 3 && out.dim() == 2 && a.stride(1) == 1 && b.is_contiguous() &&
               out.stride(1) == 1 && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16);
   const int64_t M = a.size(0), K = a.size(1), G = b.size(0);
   const int64_t N = b_mn ? b.size(2) : b.size(1);
   TORCH_CHECK((b_mn ? b.size(1) : b.size(2)) == K && out.size(0) == M && out.size(1) == N && M % 128 == 0);
   TORCH_CHECK(tile_group.numel() >= M / 128 && tile_group.scalar_type() == at::kInt);
+  TORCH_CHECK(!pair_aligned || M % 256 == 0, "pair-aligned groups need a row count that is a multiple of 256");
   c10::cuda::CUDAGuard guard(a.device());
   int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
   const bool f32 = out.scalar_type() == at::kFloat;
   ok(fmb_gemm_bf16_grouped(a.data_ptr(), b.data_ptr(), out.data_ptr(), accumulate ? out.data_ptr() : nullptr,
                            static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), 0, b_mn, a.stride(0),
-                           b.stride(1), out.stride(0), out.stride(0), f32, f32, 1.f, accumulate ? 1.f : 0.f, 1,
-                           static_cast<int>(G),
+                           b.stride(1), out.stride(0), out.stride(0), f32, f32, 1.f, accumulate ? 1.f : 0.f,
+                           pair_aligned ? 3 : 1, static_cast<int>(G),
                            tile_group.data_ptr<int>(), nullptr, b.stride(0), 0, st, cur_stream()), "gemm_grouped_rows");
 }
 
@@ -748,7 +751,8 @@ void gemm_batched(const Tensor& a, const Tensor& b, Tensor& out, const c10::opti
   int* st = status.has_value() && status->defined() ? status->data_ptr<int>() : nullptr;
   ok(fmb_gemm_bf16_grouped(a.data_ptr(), b.data_ptr(), out.data_ptr(), cp, static_cast<int>(G * M), static_cast<int>(N),
                            static_cast<int>(K), 0, b_mn, K, b.stride(1), N, N, f32, c_f32, static_cast<float>(alpha),
-                           static_cast<float>(beta), 1, static_cast<int>(G), tile_group.data_ptr<int>(), nullptr,
+                           static_cast<float>(beta), M % 256 == 0 ? 3 : 1,      // entries start on multiples of 256 rows
+                           static_cast<int>(G), tile_group.data_ptr<int>(), nullptr,
                            b.stride(0), 0, st, cur_stream()), "gemm_batched");
 }
 
@@ -889,7 +893,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("router_fwd", &router_fwd);
   m.def("router_bwd", &router_bwd);
   m.def("moe_plan", &moe_plan);
-  m.def("gemm_grouped_rows", &gemm_grouped_rows);
+  m.def("gemm_grouped_rows", &gemm_grouped_rows, pybind11::arg("a"), pybind11::arg("b"), pybind11::arg("out"),
+        pybind11::arg("tile_group"), pybind11::arg("b_mn"), pybind11::arg("accumulate"), pybind11::arg("status"),
+        pybind11::arg("pair_aligned") = false);
   m.def("gemm_grouped_wgrad", &gemm_grouped_wgrad);
   m.def("gemm_batched", &gemm_batched);
   m.def("moe_tile_groups", &moe_tile_groups);

@@ -46,6 +46,7 @@ struct GemmParams {
   //      padded rows}` gives the K range, `group_stride_d` the distance between output matrices.
   int mode;
   int n_groups;
+  int tg_step;              // 128-row entries of tile_group per row tile of this launch (2 on CTA pairs)
   const int* tile_group;
   const int* region;
   long long group_stride_d;
@@ -148,7 +149,9 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
   t.k0 = ks * p.kblocks_per_split;
   t.k1 = min(p.kblocks_total, t.k0 + p.kblocks_per_split);
   if (p.mode == 1) {
-    t.zb = __ldg(p.tile_group + t.m_blk);
+    // on CTA pairs a 256-row tile starts a group or continues one (groups are 256-aligned then): its first
+    // 128 rows name the group; a second half that holds only padding is computed and never read
+    t.zb = __ldg(p.tile_group + t.m_blk * p.tg_step);
     t.valid = t.zb >= 0;
   }
   return t;
@@ -851,6 +854,7 @@ struct GroupSpec {
   int n_groups = 1;
   const int* tile_group = nullptr;
   const int* region = nullptr;
+  int row_align = 128;           // mode 1: every group starts on a multiple of this many rows (256: CTA pairs may serve it)
   long long group_stride_b = 0;  // elements between the B matrices of consecutive groups (mode 1)
   long long group_stride_d = 0;  // elements between the D (and C) matrices of consecutive groups (mode 2)
 };
@@ -923,7 +927,11 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
   const bool can_split = allow_split && d_f32 && (C == nullptr || C == D);
   // CTA pairs (256-row tiles over two SMs) serve plain products; FMB_GEMM_PAIR=0 turns them off.
   static const bool pair_env = [] { const char* v = getenv("FMB_GEMM_PAIR"); return v == nullptr || v[0] != '0'; }();
-  const bool pair_ok = pair_env && (ps == nullptr || ps->gather == 0) && gs.mode == 0 && sms % 2 == 0;
+  static const bool gpair_env = [] { const char* v = getenv("FMB_GEMM_GROUP_PAIR"); return v == nullptr || v[0] != '0'; }();
+  const bool rows_pair = gs.mode == 1 && gpair_env && gs.row_align % 256 == 0 && M % 256 == 0;
+  const bool out_pair = gs.mode == 2 && gpair_env;          // one output per group: tiles are ordinary M x N tiles
+  const bool pair_ok = pair_env && (ps == nullptr || ps->gather == 0) && (gs.mode == 0 || rows_pair || out_pair) &&
+                       sms % 2 == 0;
 
   // Pick the N tile, the split count and the CTAs per tile that fill the machine best.
   int best_bn = 256, best_split = 1, best_ctas = 1;
@@ -969,6 +977,7 @@ static int run_gemm(const void* A, const void* B, void* D, const void* C, int M,
   p.status = status;
   p.mode = gs.mode;
   p.n_groups = gs.n_groups;
+  p.tg_step = best_ctas;
   p.tile_group = gs.tile_group;
   p.region = gs.region;
   p.group_stride_d = gs.group_stride_d;
@@ -1138,6 +1147,7 @@ extern "C" int fmb_gemm_bf16_grouped(const void* A, const void* B, void* D, cons
                                      const int* tile_group, const int* region, long long group_stride_b,
                                      long long group_stride_d, int* status, cudaStream_t stream) {
   fmb::GroupSpec gs;
+  if (mode == 3) { mode = 1; gs.row_align = 256; }      // mode 1 whose groups all start on multiples of 256 rows
   gs.mode = mode;
   gs.n_groups = n_groups;
   gs.tile_group = tile_group;

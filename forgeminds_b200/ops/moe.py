@@ -5,11 +5,13 @@ Pipeline for tokens ``x [N, d]`` (bf16):
 1. gate logits on the tcgen05 GEMM, then one router kernel: fp32 softmax, top-k, renormalised
    weights, per-expert counts and the sums the auxiliary losses need;
 2. a device-side slot plan: every routed entry gets a row in an expert-major buffer whose expert
-   regions start on 128-row boundaries (dropless) or have a fixed capacity (overflow dropped);
+   regions start on 256-row boundaries (dropless) or have a fixed capacity (overflow dropped);
 3. gather -> grouped GEMMs (gate, up) -> SwiGLU -> grouped GEMM (down) -> weighted combine.
 
 The grouped GEMM is the dense tcgen05 kernel with a per-row-tile expert table: the B operand of
-each 128-row tile is picked by the z coordinate of a 3-D TMA map over the stacked expert weights.
+each row tile is picked by the z coordinate of a 3-D TMA map over the stacked expert weights. Regions
+are aligned to 256 rows so that the products run on CTA pairs (256-row tiles over two SMs, each SM
+loading half of the expert's weight tile).
 Weight gradients use the "one output per group" mode of the same kernel (reduction over the rows of
 each region). The reference does the same work with a sort, ``index_add`` and
 ``torch._grouped_mm`` / a per-expert loop (``forgemind/moe.py:227-251``).
@@ -25,6 +27,7 @@ from . import require, status_word
 from .functional import bf16_of, gemm
 
 BF16 = torch.bfloat16
+ALIGN = 256          # rows: expert regions start on multiples of it, so that 256-row tiles never mix experts
 
 
 class _Route(torch.autograd.Function):
@@ -79,11 +82,11 @@ class _Experts(torch.autograd.Function):
         b1, b3, b2 = bf16_of(w1), bf16_of(w3), bf16_of(w2)
         xs = C.moe_gather(x, token_of)
         gu = alloc((S, 2 * h), dtype=BF16, device=x.device)
-        C.gemm_grouped_rows(xs, b1, gu[:, :h], tile_group, True, False, st)
-        C.gemm_grouped_rows(xs, b3, gu[:, h:], tile_group, True, False, st)
+        C.gemm_grouped_rows(xs, b1, gu[:, :h], tile_group, True, False, st, True)
+        C.gemm_grouped_rows(xs, b3, gu[:, h:], tile_group, True, False, st, True)
         act = C.swiglu_fwd(gu[:, :h], gu[:, h:], limit)
         ys = alloc((S, d), dtype=BF16, device=x.device)
-        C.gemm_grouped_rows(act, b2, ys, tile_group, True, False, st)
+        C.gemm_grouped_rows(act, b2, ys, tile_group, True, False, st, True)
         rw = route_w.detach().to(torch.float32).contiguous()
         out = C.moe_combine(ys, slot_of, rw, n, k)
         ctx.save_for_backward(xs, gu, ys, rw, slot_of, region, tile_group, b1, b3, b2, limit)
@@ -118,33 +121,33 @@ class _Experts(torch.autograd.Function):
 
         wgrad("w2", w2, act, dys)
         dact = alloc((S, h), dtype=BF16, device=dout.device)
-        C.gemm_grouped_rows(dys, b2, dact, tile_group, False, False, st)      # dys @ w2[e]^T
+        C.gemm_grouped_rows(dys, b2, dact, tile_group, False, False, st, True)    # dys @ w2[e]^T
         dgu = alloc(gu.shape, dtype=BF16, device=dout.device)
         C.swiglu_bwd(gu[:, :h], gu[:, h:], dact, dgu[:, :h], dgu[:, h:], limit)
         wgrad("w1", w1, xs, dgu[:, :h])
         wgrad("w3", w3, xs, dgu[:, h:])
         dxs = alloc((S, d), dtype=BF16, device=dout.device)
-        C.gemm_grouped_rows(dgu[:, :h], b1, dxs, tile_group, False, False, st)
-        C.gemm_grouped_rows(dgu[:, h:], b3, dxs, tile_group, False, True, st)
+        C.gemm_grouped_rows(dgu[:, :h], b1, dxs, tile_group, False, False, st, True)
+        C.gemm_grouped_rows(dgu[:, h:], b3, dxs, tile_group, False, True, st, True)
         dx = C.moe_combine(dxs, slot_of, None, n, k)
         return dx, drw.view(n, k).to(rw_dtype), grads["w1"], grads["w3"], grads["w2"], None, None, None, None, None, None
 
 
 def plan(idx, n_experts: int, capacity: int = 0):
     """Slot plan for ``idx [N, k]`` (int32): ``(slot_of_entry, token_of_slot, region, tile_group, limit)``.
-    ``capacity > 0`` gives every expert a fixed region of ``ceil128(capacity)`` rows (``limit`` is None);
+    ``capacity > 0`` gives every expert a fixed region of ``ceil256(capacity)`` rows (``limit`` is None);
     a dropless plan also returns ``limit``, a device int holding the first row past the last region."""
     C = require()
     n, k = idx.shape
     if capacity > 0:
-        cap = (capacity + 127) // 128 * 128
+        cap = (capacity + ALIGN - 1) // ALIGN * ALIGN
         slots = n_experts * cap
-        slot_of, token_of, region, _ = C.moe_plan(idx, n_experts, 128, cap, 1, slots)
+        slot_of, token_of, region, _ = C.moe_plan(idx, n_experts, ALIGN, cap, 1, slots)
         limit = None
     else:
         # one more (always empty) expert: its region starts where the live rows end
-        slots = (n * k + 127) // 128 * 128 + (n_experts + 1) * 128
-        slot_of, token_of, region, _ = C.moe_plan(idx, n_experts + 1, 128, 0, 0, slots)
+        slots = (n * k + ALIGN - 1) // ALIGN * ALIGN + (n_experts + 1) * ALIGN
+        slot_of, token_of, region, _ = C.moe_plan(idx, n_experts + 1, ALIGN, 0, 0, slots)
         limit, region = region[n_experts], region[:n_experts]
     tile_group = C.moe_tile_groups(region, slots // 128)
     return slot_of, token_of, region, tile_group, limit

@@ -25,6 +25,7 @@ import torch
 from torch.autograd.function import once_differentiable
 
 from .. import ops
+from ..ops.moe import ALIGN          # rows: expert regions start on multiples of it (256-row tiles on CTA pairs)
 
 BF16 = torch.bfloat16
 
@@ -91,11 +92,11 @@ class _EPExperts(torch.autograd.Function):
         h = w1.shape[2]
         entries = W * n * k
         if capacity > 0:
-            cap = (capacity * W + 127) // 128 * 128              # capacity counts tokens of all ranks
+            cap = (capacity * W + ALIGN - 1) // ALIGN * ALIGN    # capacity counts tokens of all ranks
             slots = (e_local + 1) * cap
         else:
             cap = 0
-            slots = (entries + 127) // 128 * 128 + (e_local + 1) * 128
+            slots = (entries + ALIGN - 1) // ALIGN * ALIGN + (e_local + 1) * ALIGN
         eng._buffers(n, k, d, slots)
         # 1. publish
         eng.x_sym.local.view(n, d).copy_(x)
@@ -105,7 +106,7 @@ class _EPExperts(torch.autograd.Function):
         all_idx = torch.empty((W * n, k), dtype=torch.int32, device=x.device)
         C.ep_collect_idx(eng.idx_sym.ptrs, all_idx, n * k, rank, e_local, sg.flags.local, eng.s_pub, e_pub,
                          sg.timeout_ms, st)
-        slot_of, token_of, region, _meta = C.moe_plan(all_idx, e_local + 1, 128, cap, 1 if cap else 0, slots)
+        slot_of, token_of, region, _meta = C.moe_plan(all_idx, e_local + 1, ALIGN, cap, 1 if cap else 0, slots)
         limit = region[e_local]                                  # [start of the foreign region, ...]: live rows end here
         own = region[:e_local]
         slot_of = torch.where(slot_of >= limit[0], torch.full_like(slot_of, -1), slot_of)   # foreign entries have no slot here
@@ -124,13 +125,13 @@ class _EPExperts(torch.autograd.Function):
         C.ep_gather(eng.x_sym.ptrs, token_of, limit, xs, n, sg.flags.local, eng.s_pub, e_pub, sg.timeout_ms, st)
         b1, b3, b2 = bf16_of(w1), bf16_of(w3), bf16_of(w2)
         gu = alloc((slots, 2 * h), dtype=BF16, device=x.device)
-        C.gemm_grouped_rows(xs, b1, gu[:, :h], tile_group, True, False, st)
-        C.gemm_grouped_rows(xs, b3, gu[:, h:], tile_group, True, False, st)
+        C.gemm_grouped_rows(xs, b1, gu[:, :h], tile_group, True, False, st, True)
+        C.gemm_grouped_rows(xs, b3, gu[:, h:], tile_group, True, False, st, True)
         act = C.swiglu_fwd(gu[:, :h], gu[:, h:], limit)
         ys = eng.rows_sym.local.view(slots, d)
         if cap:
             ys.zero_()
-        C.gemm_grouped_rows(act, b2, ys, tile_group, True, False, st)
+        C.gemm_grouped_rows(act, b2, ys, tile_group, True, False, st, True)
         e_ys = eng.signal(eng.s_ys)
         # 4. combine: every token pulls from the owners
         rw = route_w.detach().to(torch.float32).contiguous()
@@ -181,7 +182,7 @@ class _EPExperts(torch.autograd.Function):
 
         wgrad("w2", w2, act, dys)
         dact = alloc((slots, h), dtype=BF16, device=dout.device)
-        C.gemm_grouped_rows(dys, b2, dact, tile_group, False, False, st)
+        C.gemm_grouped_rows(dys, b2, dact, tile_group, False, False, st, True)
         dgu = alloc(gu.shape, dtype=BF16, device=dout.device)
         C.swiglu_bwd(gu[:, :h], gu[:, h:], dact, dgu[:, :h], dgu[:, h:], limit)
         wgrad("w1", w1, xs, dgu[:, :h])
@@ -189,8 +190,8 @@ class _EPExperts(torch.autograd.Function):
         dxs = eng.rows_sym.local.view(slots, d)
         if clear:
             dxs.zero_()
-        C.gemm_grouped_rows(dgu[:, :h], b1, dxs, tile_group, False, False, st)
-        C.gemm_grouped_rows(dgu[:, h:], b3, dxs, tile_group, False, True, st)
+        C.gemm_grouped_rows(dgu[:, :h], b1, dxs, tile_group, False, False, st, True)
+        C.gemm_grouped_rows(dgu[:, h:], b3, dxs, tile_group, False, True, st, True)
         e_dx = eng.signal(eng.s_dxs)
         dx = torch.empty((n, d), dtype=BF16, device=dout.device)
         C.ep_combine(eng.rows_sym.ptrs, eng.slot_sym.ptrs, idx, None, dx, e_local, rank, sg.flags.local, eng.s_dxs,

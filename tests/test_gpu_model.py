@@ -112,7 +112,8 @@ def test_moe_capacity_drops_overflow(cuda_status):
     torch.manual_seed(1)
     moe = MoE(128, 256, 4, 2, grouped_mm=True, capacity_factor=1.0).cuda()
     ref = copy.deepcopy(moe)
-    ref.capacity = lambda n: (moe.capacity(n) + 127) // 128 * 128       # regions are whole 128-row tiles
+    from forgeminds_b200.ops.moe import ALIGN
+    ref.capacity = lambda n: (moe.capacity(n) + ALIGN - 1) // ALIGN * ALIGN       # regions are whole row tiles
     x = (torch.randn(2048, 128, device="cuda")).to(torch.bfloat16)
     out = moe(x)
     with torch.autocast("cuda", dtype=torch.bfloat16):
