@@ -549,28 +549,31 @@ def rope_qkv_(qkv, cos, sin, n_q, n_kv, hd):
 class _Attention(torch.autograd.Function):
     """Causal GQA attention on a fused q|k|v buffer. With ``cos`` / ``sin`` the q and k heads are rotated in
     place first (the buffer comes back as a second, dirty output) and the backward rotates the gradient
-    back in the pass that converts the kernel's fp32 dQ sum to bf16."""
+    back in the pass that converts the kernel's fp32 dQ sum to bf16. The buffer is ``[B, T, W]`` or, with
+    ``bt = (B, T)``, the ``[B * T, W]`` rows of a projection output (autograd lets a Function with two
+    outputs modify an input in place only if that input is not a view, so such rows are passed as they are)."""
 
     @staticmethod
-    def forward(ctx, qkv, n_q, n_kv, hd, causal, cos=None, sin=None):
+    def forward(ctx, given, n_q, n_kv, hd, causal, cos=None, sin=None, bt=None):
         C = require()
+        qkv = given.view(bt[0], bt[1], -1) if given.dim() == 2 else given
         B, T, _ = qkv.shape
         ctx.rope = cos is not None
         if ctx.rope:
             C.rope(qkv, qkv, cos, sin, T, n_q + n_kv, n_q + 2 * n_kv, hd, 1.0)
-            ctx.mark_dirty(qkv)
+            ctx.mark_dirty(given)
             ctx.set_materialize_grads(False)
         q = qkv[..., : n_q * hd].unflatten(-1, (n_q, hd))
         k = qkv[..., n_q * hd: (n_q + n_kv) * hd].unflatten(-1, (n_kv, hd))
         v = qkv[..., (n_q + n_kv) * hd:].unflatten(-1, (n_kv, hd))
         o, lse = C.attn_fwd(q, k, v, 1.0 / math.sqrt(hd), causal, status_word(qkv.device))
         if ctx.rope:
-            ctx.save_for_backward(qkv, o, lse, cos, sin)
+            ctx.save_for_backward(given, o, lse, cos, sin)
         else:
-            ctx.save_for_backward(qkv, o, lse)
-        ctx.dims = (n_q, n_kv, hd, causal)
+            ctx.save_for_backward(given, o, lse)
+        ctx.dims = (n_q, n_kv, hd, causal, B, T)
         out = o.view(B, T, n_q * hd)
-        return (out, qkv) if ctx.rope else out
+        return (out, given) if ctx.rope else out
 
     @staticmethod
     @once_differentiable
@@ -578,15 +581,15 @@ class _Attention(torch.autograd.Function):
         C = require()
         cos = sin = None
         if ctx.rope:
-            qkv, o, lse, cos, sin = ctx.saved_tensors
+            given, o, lse, cos, sin = ctx.saved_tensors
             if g_qkv is not None:
                 raise RuntimeError("the rotated qkv buffer returned by attention_qkv is not differentiable")
             if d_o is None:
-                return (None,) * 7
+                return (None,) * 8
         else:
-            qkv, o, lse = ctx.saved_tensors
-        n_q, n_kv, hd, causal = ctx.dims
-        B, T, _ = qkv.shape
+            given, o, lse = ctx.saved_tensors
+        n_q, n_kv, hd, causal, B, T = ctx.dims
+        qkv = given.view(B, T, -1)
         dqkv = torch.empty_like(qkv)
         q = qkv[..., : n_q * hd].unflatten(-1, (n_q, hd))
         k = qkv[..., n_q * hd: (n_q + n_kv) * hd].unflatten(-1, (n_kv, hd))
@@ -601,7 +604,7 @@ class _Attention(torch.autograd.Function):
             C.rope(dqkv, dqkv, cos, sin, T, n_q + n_kv, n_q + 2 * n_kv, hd, -1.0, dq32)
         else:
             C.attn_bwd(q, k, v, o, d_o4, lse, dq, dk, dv, scale, causal, st, None)
-        return dqkv, None, None, None, None, None, None
+        return dqkv.view(given.shape), None, None, None, None, None, None, None
 
 
 class _AttentionProj(torch.autograd.Function):
@@ -704,6 +707,9 @@ def attention_proj(qkv, weight, residual, n_q, n_kv, hd, causal=True, rope=None)
     ``rope=(cos, sin)`` rotates the q and k heads of ``qkv`` in place first."""
     if rope is None:
         return _AttentionProj.apply(qkv, weight, residual, n_q, n_kv, hd, causal)
+    if qkv._is_view():          # a view cannot be rotated in place by a node with two outputs: rotate it on its own
+        return _AttentionProj.apply(rope_qkv_(qkv, rope[0], rope[1], n_q, n_kv, hd), weight, residual, n_q, n_kv, hd,
+                                    causal)
     return _AttentionProj.apply(qkv, weight, residual, n_q, n_kv, hd, causal, rope[0], rope[1])[0]
 
 
@@ -787,12 +793,16 @@ def mlp_block(x, norm_w, eps, w1, w3, w2):
     return _MLPBlock.apply(x, norm_w, eps, w1, w3, w2)
 
 
-def attention_qkv(qkv, n_q, n_kv, hd, causal=True, rope=None):
-    """Causal GQA flash attention reading q, k, v as slices of one fused projection output.
+def attention_qkv(qkv, n_q, n_kv, hd, causal=True, rope=None, bt=None):
+    """Causal GQA flash attention reading q, k, v as slices of one fused projection output ``[B, T, W]`` (or
+    its rows ``[B * T, W]`` with ``bt = (B, T)``); the result is ``[B, T, n_q * hd]``.
     ``rope=(cos, sin)`` rotates the q and k heads of ``qkv`` in place first."""
     if rope is None:
+        return _Attention.apply(qkv, n_q, n_kv, hd, causal, None, None, bt)
+    if qkv._is_view():          # a view cannot be rotated in place by a node with two outputs: rotate it on its own
+        qkv = rope_qkv_(qkv.view(bt[0], bt[1], -1) if qkv.dim() == 2 else qkv, rope[0], rope[1], n_q, n_kv, hd)
         return _Attention.apply(qkv, n_q, n_kv, hd, causal)
-    return _Attention.apply(qkv, n_q, n_kv, hd, causal, rope[0], rope[1])[0]
+    return _Attention.apply(qkv, n_q, n_kv, hd, causal, rope[0], rope[1], bt)[0]
 
 
 # ------------------------------------------------------------------------------ fused lm_head + cross-entropy

@@ -332,10 +332,9 @@ def block_forward(blk, x_shard, state: TPState):
     xn = Fn.rms_norm(x_shard, blk.attn_norm.weight, blk.attn_norm.eps)
     qkv = gather_linear(xn, (at.wq.weight, at.wk.weight, at.wv.weight), state)     # [M, (nq + 2 nkv) * hd]
     B, T = blk._fm_bt
-    qkv = qkv.view(B, T, -1)
     cos, sin = rope_tables(T, hd, at.theta, qkv.device, torch.float32)
-    o = Fn.attention_qkv(qkv, nq, nkv, hd, True,                # [B, T, nq * hd]
-                         rope=(cos.reshape(T, hd // 2), sin.reshape(T, hd // 2)))
+    o = Fn.attention_qkv(qkv, nq, nkv, hd, True,                # rows in, [B, T, nq * hd] out
+                         rope=(cos.reshape(T, hd // 2), sin.reshape(T, hd // 2)), bt=(B, T))
     h = linear_scatter(o.reshape(B * T, nq * hd), at.wo.weight, x_shard, state)
     hn = Fn.rms_norm(h, blk.ffn_norm.weight, blk.ffn_norm.eps)
     gu = gather_linear(hn, (ff.w1.weight, ff.w3.weight), state)                   # [M, 2 * hidden_local]
