@@ -26,6 +26,10 @@ product that read the same slice by a full flag barrier (every reduce-scatter en
 peer can only reach its next reduce-scatter into a rank's staging buffer after waiting for that rank's
 next publish, which comes after the rank has summed the buffer.
 
+Blocks whose projections are int8 / fp8 layers run the same layout with the 8-bit tensor-core products of
+``csrc/gemm8_sm100.cu`` between NCCL all-gather / reduce-scatter calls (:func:`quant_gather_linear`,
+:func:`quant_linear_scatter`): the gather warps and the scattered-output epilogue exist in the bf16 kernel only.
+
 The reference expresses the same layout with DTensor ``ColwiseParallel`` / ``RowwiseParallel`` and
 NCCL all-reduces (``forgemind/parallel/native.py:21-49``); that path remains the fallback
 (:func:`usable` false: CPU, Gloo, ``fused_comm=False``, shapes that do not tile).
@@ -57,6 +61,7 @@ class TPState:
         self.rank, self.world = self.sg.rank, self.sg.world
         self.slot_act, self.slot_grad, self.slot_bar = (self.sg.reserve_slots(1) for _ in range(3))
         self._bufs: dict = {}
+        self.quant_calls = 0          # 8-bit column-parallel products issued so far (tests read it)
 
     def buffers(self, rows: int, width: int):
         """(gather buffer for activations, gather buffer for gradients, staging) for row shards ``[rows, width]``:
@@ -265,6 +270,58 @@ class _GatherRows(torch.autograd.Function):
         return dout[rank * ms:(rank + 1) * ms].contiguous(), None, None, None
 
 
+class _AllGatherRows(torch.autograd.Function):
+    """All-gather of row shards whose consumer is column-parallel (every rank multiplies ALL rows by its own
+    weight slice): the input gradient is the sum of the ranks' partial gradients, reduce-scattered back."""
+
+    @staticmethod
+    def forward(ctx, x_shard, group, world):
+        out = x_shard.new_empty((x_shard.shape[0] * world,) + tuple(x_shard.shape[1:]))
+        dist.all_gather_into_tensor(out, x_shard.contiguous(), group=group)
+        ctx.group, ctx.world = group, world
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        dx = dout.new_empty((dout.shape[0] // ctx.world,) + tuple(dout.shape[1:]))
+        dist.reduce_scatter_tensor(dx, dout.contiguous(), group=ctx.group)
+        return dx, None, None
+
+
+class _ReduceScatterRows(torch.autograd.Function):
+    """Sum of the ranks' partial outputs of a row-parallel layer, each rank keeping its rows."""
+
+    @staticmethod
+    def forward(ctx, y_partial, group, world):
+        out = y_partial.new_empty((y_partial.shape[0] // world,) + tuple(y_partial.shape[1:]))
+        dist.reduce_scatter_tensor(out, y_partial.contiguous(), group=group)
+        ctx.group, ctx.world = group, world
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        full = dout.new_empty((dout.shape[0] * ctx.world,) + tuple(dout.shape[1:]))
+        dist.all_gather_into_tensor(full, dout.contiguous(), group=ctx.group)
+        return full, None, None
+
+
+def quant_gather_linear(x_shard, linears, tp: TPState):
+    """Column-parallel projection(s) of int8 / fp8 layers: the row shards are all-gathered (NCCL) and multiplied
+    by this rank's weight slices as ONE product on the 8-bit tensor-core kernel. The bf16 kernels above fuse the
+    gather into the product; the 8-bit kernel has no gather warps, so here the collective is a call of its own."""
+    from ..ops.quant import qlinear_multi
+    tp.quant_calls += 1
+    x_full = _AllGatherRows.apply(x_shard, tp.group, tp.world)
+    head = linears[0]
+    return qlinear_multi(x_full, tuple(m.weight for m in linears), head.mode, head.block)
+
+
+def quant_linear_scatter(h, linear, residual, tp: TPState):
+    """Row-parallel int8 / fp8 projection: 8-bit product of this rank's columns, reduce-scatter of the bf16
+    partial outputs (NCCL), residual added to the rows this rank keeps."""
+    return _ReduceScatterRows.apply(linear(h), tp.group, tp.world) + residual
+
+
 # ---------------------------------------------------------------------------------------------- model surgery
 def _shard_rows(linear, lo, hi):
     w = linear.weight.data[lo:hi].clone()
@@ -326,20 +383,31 @@ def block_forward(blk, x_shard, state: TPState):
     """One transformer block on a row shard ``[Ms, d]`` of the residual stream."""
     from ..models.gpt import rope_tables
     from ..ops import functional as Fn
+    from ..models.gpt import _is_quantised
     at, ff = blk.attn, blk.ffn
     hd = at.hd
     nq, nkv = at.wq.weight.shape[0] // hd, at.wk.weight.shape[0] // hd
+    q_attn, q_ffn = _is_quantised(at.wq), _is_quantised(ff.w1)      # int8 / fp8 layers: 8-bit products, NCCL collectives
     xn = Fn.rms_norm(x_shard, blk.attn_norm.weight, blk.attn_norm.eps)
-    qkv = gather_linear(xn, (at.wq.weight, at.wk.weight, at.wv.weight), state)     # [M, (nq + 2 nkv) * hd]
+    if q_attn:
+        qkv = quant_gather_linear(xn, (at.wq, at.wk, at.wv), state)
+    else:
+        qkv = gather_linear(xn, (at.wq.weight, at.wk.weight, at.wv.weight), state)     # [M, (nq + 2 nkv) * hd]
     B, T = blk._fm_bt
     cos, sin = rope_tables(T, hd, at.theta, qkv.device, torch.float32)
     o = Fn.attention_qkv(qkv, nq, nkv, hd, True,                # rows in, [B, T, nq * hd] out
                          rope=(cos.reshape(T, hd // 2), sin.reshape(T, hd // 2)), bt=(B, T))
-    h = linear_scatter(o.reshape(B * T, nq * hd), at.wo.weight, x_shard, state)
+    o = o.reshape(B * T, nq * hd)
+    h = quant_linear_scatter(o, at.wo, x_shard, state) if _is_quantised(at.wo) else \
+        linear_scatter(o, at.wo.weight, x_shard, state)
     hn = Fn.rms_norm(h, blk.ffn_norm.weight, blk.ffn_norm.eps)
-    gu = gather_linear(hn, (ff.w1.weight, ff.w3.weight), state)                   # [M, 2 * hidden_local]
+    if q_ffn:
+        gu = quant_gather_linear(hn, (ff.w1, ff.w3), state)
+    else:
+        gu = gather_linear(hn, (ff.w1.weight, ff.w3.weight), state)               # [M, 2 * hidden_local]
     act = Fn.swiglu_split(gu)
-    return linear_scatter(act, ff.w2.weight, h, state)
+    return quant_linear_scatter(act, ff.w2, h, state) if _is_quantised(ff.w2) else \
+        linear_scatter(act, ff.w2.weight, h, state)
 
 
 def stack_forward(model, x):

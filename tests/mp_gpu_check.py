@@ -590,6 +590,7 @@ def _mesh_run(world, rank, label, steps=8, quant="none", optimizer="adamw", **pa
     if rank == 0:
         print(f"  {label}: engine={'native' if tr.store is not None else 'library'} "
               f"loss {losses[0]:.3f} -> {losses[-1]:.3f}", flush=True)
+    return tr
 
 
 def mesh_smoke():
@@ -601,6 +602,9 @@ def mesh_smoke():
     _mesh_run(world, rank, f"dp_shard={world} + int8 + muon", quant="int8", optimizer="muon", dp_shard=world)
     _mesh_run(world, rank, f"pp=2 x dp_shard={world // 2}", pp=2, dp_shard=world // 2, pp_microbatches=2)
     _mesh_run(world, rank, f"tp=2 x dp_shard={world // 2}", tp=2, dp_shard=world // 2)
+    for mode in ("int8", "fp8"):          # quantised layers under tensor parallelism run their 8-bit products
+        tr = _mesh_run(world, rank, f"tp=2 x dp_shard={world // 2} + {mode}", quant=mode, tp=2, dp_shard=world // 2)
+        assert tr.store is not None and tr.raw._fm_tp.quant_calls > 0, mode
     if world >= 4:
         _mesh_run(world, rank, "dp_replicate=2 x dp_shard=2 (HSDP)", dp_replicate=2, dp_shard=world // 2)
         _mesh_run(world, rank, f"tp=2 x pp=2 x dp_shard={world // 4}", tp=2, pp=2, dp_shard=world // 4, pp_microbatches=2)
