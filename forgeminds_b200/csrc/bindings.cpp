@@ -145,22 +145,28 @@ std::vector<Tensor> add_rmsnorm_fwd(const Tensor& x, const Tensor& delta, const 
 }
 
 // returns (dx, dw fp32)
+// dw_acc (optional, fp32 [d]): the weight gradient is ADDED to it by the column-sum kernel (a flat gradient store
+// owns the parameter) and the second result is undefined.
 std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd,
-                                const c10::optional<Tensor>& dres, bool need_dw) {
+                                const c10::optional<Tensor>& dres, bool need_dw, const c10::optional<Tensor>& dw_acc) {
   cuda_contig(dy, "dy"); cuda_contig(x, "x"); cuda_contig(w, "w");
   const int64_t d = x.size(-1);
   const int64_t rows = x.numel() / d;
   c10::cuda::CUDAGuard guard(x.device());
   Tensor dx = torch::empty_like(x);
   const int nb = fmb_rmsnorm_bwd_blocks(rows, static_cast<int>(d));
+  const bool into = need_dw && dw_acc.has_value() && dw_acc->defined();
+  if (into) TORCH_CHECK(dw_acc->is_cuda() && dw_acc->scalar_type() == at::kFloat && dw_acc->is_contiguous() &&
+                        dw_acc->numel() == d, "rmsnorm_bwd: dw_acc must be a contiguous fp32 vector of the row width");
   Tensor dwp, dw;
   if (need_dw) {
     dwp = torch::empty({nb, d}, x.options().dtype(at::kFloat));
-    dw = torch::empty({d}, x.options().dtype(at::kFloat));
+    if (!into) dw = torch::empty({d}, x.options().dtype(at::kFloat));
   }
   if (dres.has_value() && dres->defined()) cuda_contig(*dres, "dres");
+  float* dw_ptr = !need_dw ? nullptr : into ? dw_acc->data_ptr<float>() : dw.data_ptr<float>();
   ok(fmb_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), cptr(dres), dx.data_ptr(),
-                     need_dw ? dwp.data_ptr<float>() : nullptr, need_dw ? dw.data_ptr<float>() : nullptr, 0, rows,
+                     need_dw ? dwp.data_ptr<float>() : nullptr, dw_ptr, into ? 1 : 0, rows,
                      static_cast<int>(d), dt(x), dt(w), nb, cur_stream()), "rmsnorm_bwd", need_dw ? 2 : 1);
   return {dx, dw};
 }
@@ -839,7 +845,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
-  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd, pybind11::arg("dy"), pybind11::arg("x"), pybind11::arg("w"), pybind11::arg("rstd"),
+        pybind11::arg("dres"), pybind11::arg("need_dw"), pybind11::arg("dw_acc") = pybind11::none());
   m.def("swiglu_fwd", &swiglu_fwd, pybind11::arg("gate"), pybind11::arg("up"), pybind11::arg("row_limit") = pybind11::none());
   m.def("swiglu_bwd", &swiglu_bwd, pybind11::arg("gate"), pybind11::arg("up"), pybind11::arg("dy"), pybind11::arg("dgate"),
         pybind11::arg("dup"), pybind11::arg("row_limit") = pybind11::none());

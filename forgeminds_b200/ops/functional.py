@@ -266,6 +266,15 @@ def _weight_grads(ctx_needs, weights, dy2, x2):
     return grads
 
 
+def _norm_acc(ctx):
+    """fp32 gradient buffer of the norm weight when a flat store owns it and it wants a gradient: the column
+    sum of the RMSNorm backward then adds into it, and autograd gets no tensor to accumulate."""
+    main = getattr(ctx, "norm_main", None)
+    if main is None or not ctx.needs_input_grad[1] or main.dtype != torch.float32 or not main.is_contiguous():
+        return None
+    return main
+
+
 class _NormLinearMulti(torch.autograd.Function):
     """``rms_norm(x) @ cat(weights).T``. Only ``x`` and the per-row ``rstd`` are kept; the normalised
     activations are recomputed in the backward (one extra pass over ``x`` instead of a saved tensor).
@@ -289,6 +298,7 @@ class _NormLinearMulti(torch.autograd.Function):
         y = _gemm_like(x, h, w)
         ctx.save_for_backward(x2, nw, rstd, w)
         ctx.weights, ctx.eps, ctx.x_shape, ctx.nw_dtype = weights, eps, x.shape, norm_w.dtype
+        ctx.norm_main = getattr(norm_w, "_fm_main_grad", None)      # a flat gradient store owns the norm weight
         if passthrough:
             return y, x.view_as(x)
         return y
@@ -312,7 +322,7 @@ class _NormLinearMulti(torch.autograd.Function):
                     dres = dres.to(dh.dtype)
                 if not dres.is_contiguous():
                     dres = dres.contiguous()
-            dx, dnw = C.rmsnorm_bwd(dh, x2, nw, rstd, dres, ctx.needs_input_grad[1])
+            dx, dnw = C.rmsnorm_bwd(dh, x2, nw, rstd, dres, ctx.needs_input_grad[1], _norm_acc(ctx))
             dx = dx.view(ctx.x_shape)
             if dnw is not None and dnw.dtype != ctx.nw_dtype:
                 dnw = dnw.to(ctx.nw_dtype)
@@ -758,6 +768,7 @@ class _MLPBlock(torch.autograd.Function):
         ctx.save_for_backward(x2, nw, rstd, gu, w13, b2)
         ctx.params = (w1, w3, w2)
         ctx.meta = (eps, x.shape, norm_w.dtype)
+        ctx.norm_main = getattr(norm_w, "_fm_main_grad", None)
         return y
 
     @staticmethod
@@ -783,7 +794,7 @@ class _MLPBlock(torch.autograd.Function):
         xn, _ = C.rmsnorm_fwd(x2, nw, eps)                              # recomputed
         g13 = _weight_grads(ctx.needs_input_grad[3:5], (w1, w3), dgu, xn)
         dxn = gemm(dgu, w13, b_mn=True)
-        dx, dnw = C.rmsnorm_bwd(dxn, x2, nw, rstd, dy2, ctx.needs_input_grad[1])
+        dx, dnw = C.rmsnorm_bwd(dxn, x2, nw, rstd, dy2, ctx.needs_input_grad[1], _norm_acc(ctx))
         if dnw is not None and dnw.dtype != nw_dtype:
             dnw = dnw.to(nw_dtype)
         return dx.view(x_shape), dnw, None, g13[0], g13[1], g2[0]
