@@ -31,6 +31,20 @@ def test_rmsnorm(d, wdtype):
     assert (w.grad.float() - wr.grad).norm() / wr.grad.norm() < 1e-2
 
 
+def test_rmsnorm_bwd_adds_the_weight_gradient_into_a_given_buffer():
+    """The form the flat gradient store uses: no gradient tensor comes back, the column sum adds in place."""
+    from forgeminds_b200 import ops
+    C = ops.require()
+    x, dy = _bf(300, 256, seed=3), _bf(300, 256, seed=4)
+    w = 1 + 0.1 * torch.randn(256, device="cuda")
+    _, rstd = C.rmsnorm_fwd(x, w, 1e-6)
+    dx0, dw0 = C.rmsnorm_bwd(dy, x, w, rstd, None, True)
+    acc = torch.full((256,), 0.5, device="cuda")
+    dx1, dw1 = C.rmsnorm_bwd(dy, x, w, rstd, None, True, acc)
+    assert dw1 is None and torch.equal(dx0, dx1)
+    assert torch.allclose(acc, 0.5 + dw0, rtol=1e-6, atol=1e-6)
+
+
 def test_rmsnorm_fp32_input():
     from forgeminds_b200.ops import functional as Fn
     x = torch.randn(77, 512, device="cuda", requires_grad=True)
