@@ -388,8 +388,9 @@ def main() -> int:
                    "grad_accum": accum, "seq_len": seq, "parallelism": spec["label"](world),
                    "optimizer": optim, "ac": "selective",
                    "engine": (trainer.eng.name + ("+peer" if trainer.peer else "")) if ours else "reference Trainer",
-                   "memory_layout": ("bf16 weights and fp32 gradients whole on every GPU, fp32 master weights and AdamW "
-                                     "moments sharded 1/dp_shard" if ours and getattr(trainer, "store", None) is not None
+                   "memory_layout": ("bf16 weights, fp32 gradients and the fp32 master buffer whole on every GPU (only the "
+                                     "rank's own shard of the masters is updated between steps), optimizer moments "
+                                     "sharded 1/dp_shard" if ours and getattr(trainer, "store", None) is not None
                                      else "as the wrapped torch.distributed strategy shards it"),
                    "l2": "per-step working set (weights+activations, >10 GB) exceeds the 126 MB L2"},
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
