@@ -207,6 +207,7 @@ def build_ours(args, world):
         cfg.train.optimizer = args.optimizer
     if args.offload_activations:
         cfg.offload.activations = True
+    cfg.parallel.ep_slot_factor = args.ep_slot_factor
     # the MoE arm runs dropless, like the reference, which has no capacity factor: both arms do the same work
     extra = dict(MOE, capacity_factor=args.capacity_factor, z_coef=0.0) if args.config == "moe" else {}
     mc = fm.GPTConfig(ffn_hidden=spec["hidden"], **spec["model"], **extra)
@@ -284,6 +285,9 @@ def main() -> int:
     ap.add_argument("--offload-activations", action="store_true")
     ap.add_argument("--capacity-factor", type=float, default=0.0,
                     help="MoE arm: 0 = dropless like the reference; 1.25 = the capacity the config names")
+    ap.add_argument("--ep-slot-factor", type=float, default=0.0,
+                    help="MoE arm of this library: dispatch buffers sized to this multiple of a rank's average share "
+                         "of the routed rows (0 = the worst case; an overflow is raised, never dropped silently)")
     ap.add_argument("--no-exposed-comm", action="store_true", help="skip the extra timed phase with local-only comm")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))

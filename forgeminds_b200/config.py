@@ -38,6 +38,9 @@ class ParallelConfig:
     fsdp_resident_bytes: int = 0       # memory the flat-store engine may use for parameters, gradients and optimizer
                                        # state on one GPU (0: 80 % of the device); bigger models go to FSDP2
     comm_timeout_ms: int = 10000       # bound of every device-side wait on a peer flag
+    ep_slot_factor: float = 0.0        # dropless expert parallelism: row buffers of a rank hold this many times its
+                                       # average share of the routed rows (0: the worst case, every row); a layer
+                                       # that needs more raises fm.ops.EPOverflow at the step's host read
 
 
 @dataclass

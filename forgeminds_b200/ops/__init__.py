@@ -79,6 +79,14 @@ class BoundsError(RuntimeError):
     the access was skipped."""
 
 
+class EPOverflow(RuntimeError):
+    """An expert-parallel layer routed more rows to one rank than its dispatch buffers hold
+    (``parallel.ep_slot_factor``, code 8); the rows beyond were left out and the step must not be trusted."""
+
+
+ERR_EP_OVERFLOW = 8
+
+
 def register_buffer(t_or_ptr, nbytes: int | None = None, device=None) -> None:
     """Debug build: add a buffer (a tensor, or an address and a length) to the table that the checked
     peer-memory accesses are validated against. No-op in the normal build."""
@@ -102,4 +110,7 @@ def check_status(device, sync_value: int | None = None) -> None:
         if code == 7:
             raise BoundsError("forgeminds_b200: a kernel of the bounds-checked build skipped an access outside "
                               "every registered buffer (code 7)")
+        if code == ERR_EP_OVERFLOW:
+            raise EPOverflow("forgeminds_b200: an expert-parallel layer routed more rows to one rank than "
+                             "parallel.ep_slot_factor provides room for (code 8): raise the factor or set it to 0")
         raise CommTimeout(f"forgeminds_b200: a kernel wait timed out (code {code})")

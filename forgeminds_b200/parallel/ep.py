@@ -30,9 +30,35 @@ from ..ops.moe import ALIGN          # rows: expert regions start on multiples o
 BF16 = torch.bfloat16
 
 
+def bounded_rows(slots: int, entries: int, world: int, e_local: int, factor: float) -> int:
+    """Rows of a rank's dispatch buffers: the worst case ``slots`` (every routed row of every rank lands here),
+    or ``factor`` times the rank's average share plus the padding of its expert regions when that is less."""
+    if factor <= 0:
+        return slots
+    want = int(factor * entries / world) + e_local * ALIGN
+    return min(slots, (want + ALIGN - 1) // ALIGN * ALIGN)
+
+
+def clamp_plan(region, limit, rows: int):
+    """Cut a slot plan down to ``rows`` buffer rows (device tensors in, device tensors out, no host read):
+    expert regions ``[start, used, padded]`` end at ``rows``, and so does the first row past the live ones.
+    Returns ``(region, limit, overflowed)`` with ``overflowed`` a device bool."""
+    over = limit[0] > rows
+    limit = limit.clone()
+    limit[0] = torch.clamp(limit[0], max=rows)
+    r = region.view(-1, 3).clone()
+    end_pad = torch.clamp(r[:, 0] + r[:, 2], max=rows)
+    end_use = torch.clamp(r[:, 0] + r[:, 1], max=rows)
+    r[:, 0] = torch.clamp(r[:, 0], max=rows)
+    r[:, 2] = end_pad - r[:, 0]
+    r[:, 1] = end_use - r[:, 0]
+    return r.view(region.shape), limit, over
+
+
 class EPEngine:
-    def __init__(self, group, device, timeout_ms: float = 10000.0):
+    def __init__(self, group, device, timeout_ms: float = 10000.0, slot_factor: float = 0.0):
         from .symm import SymmGroup
+        self.slot_factor = float(slot_factor)
         self.sg = SymmGroup(group, device, timeout_ms=timeout_ms)
         self.rank, self.world = self.sg.rank, self.sg.world
         sg = self.sg
@@ -97,6 +123,9 @@ class _EPExperts(torch.autograd.Function):
         else:
             cap = 0
             slots = (entries + ALIGN - 1) // ALIGN * ALIGN + (e_local + 1) * ALIGN
+        plan_slots = slots
+        if not cap:        # dropless: the row buffers may be smaller than the plan's worst case
+            slots = bounded_rows(plan_slots, entries, W, e_local, eng.slot_factor)
         eng._buffers(n, k, d, slots)
         # 1. publish
         eng.x_sym.local.view(n, d).copy_(x)
@@ -106,9 +135,15 @@ class _EPExperts(torch.autograd.Function):
         all_idx = torch.empty((W * n, k), dtype=torch.int32, device=x.device)
         C.ep_collect_idx(eng.idx_sym.ptrs, all_idx, n * k, rank, e_local, sg.flags.local, eng.s_pub, e_pub,
                          sg.timeout_ms, st)
-        slot_of, token_of, region, _meta = C.moe_plan(all_idx, e_local + 1, ALIGN, cap, 1 if cap else 0, slots)
+        slot_of, token_of, region, _meta = C.moe_plan(all_idx, e_local + 1, ALIGN, cap, 1 if cap else 0, plan_slots)
         limit = region[e_local]                                  # [start of the foreign region, ...]: live rows end here
         own = region[:e_local]
+        if slots < plan_slots:
+            # bounded buffers: rows past them are cut from the plan, and a layer that needed them leaves a code
+            # in the status word, which the step reads with its loss (the host is not asked here)
+            own, limit, over = clamp_plan(own, limit, slots)
+            code = torch.full_like(st, ops.ERR_EP_OVERFLOW)
+            st.copy_(torch.where(over & (st == 0), code, st))
         slot_of = torch.where(slot_of >= limit[0], torch.full_like(slot_of, -1), slot_of)   # foreign entries have no slot here
         tile_group = C.moe_tile_groups(own, slots // 128)
         entry_of = torch.full((slots + 1,), -1, dtype=torch.int32, device=x.device)
@@ -140,6 +175,8 @@ class _EPExperts(torch.autograd.Function):
                      e_ys, sg.timeout_ms, st)
         ys_keep = ys.clone()
         sg.barrier(eng.s_done)
+        if slots < plan_slots:        # the backward reads the plan as it was cut to the buffers
+            region = torch.cat([own.view(-1, 3), limit.view(1, 3)])
         ctx.save_for_backward(xs, gu, ys_keep, rw, idx, slot_of, entry_of, region, tile_group, b1, b3, b2)
         ctx.params = (w1, w3, w2)
         ctx.eng = eng
@@ -203,7 +240,8 @@ class _EPExperts(torch.autograd.Function):
 
 def attach(model, ctx) -> EPEngine:
     """Give every MoE layer of ``model`` the peer-memory expert-parallel engine of ``ctx.ep_group``."""
-    eng = EPEngine(ctx.ep_group, ctx.device, timeout_ms=float(getattr(ctx.pc, "comm_timeout_ms", 10000)))
+    eng = EPEngine(ctx.ep_group, ctx.device, timeout_ms=float(getattr(ctx.pc, "comm_timeout_ms", 10000)),
+                   slot_factor=float(getattr(ctx.pc, "ep_slot_factor", 0.0)))
     hits = 0
     for m in model.modules():
         if hasattr(m, "ep_engine") and getattr(m, "ep_size", 1) > 1:

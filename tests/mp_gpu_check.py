@@ -208,7 +208,7 @@ def ep_fused():
     from forgeminds_b200.parallel import ep as fused_ep
     rank, world, dev = _init()
     E, k, d, h, n = 8, 2, 256, 512, 1024
-    for cap_factor in (0.0, 1.0):
+    for cap_factor, slot_factor in ((0.0, 0.0), (1.0, 0.0), (0.0, 1.5)):     # dropless, capacity, dropless in bounded buffers
         torch.manual_seed(3)
         whole = MoE(d, h, E, k, grouped_mm=True, capacity_factor=cap_factor).to(dev)
         part = MoE(d, h, E, k, grouped_mm=True, capacity_factor=cap_factor, ep_size=world, ep_rank=rank,
@@ -218,7 +218,8 @@ def ep_fused():
             part.router.gate.weight.copy_(whole.router.gate.weight)
             for name in ("w1", "w3", "w2"):
                 getattr(part.experts, name).copy_(getattr(whole.experts, name)[rank * el:(rank + 1) * el])
-        ctx = types.SimpleNamespace(pc=types.SimpleNamespace(comm_timeout_ms=5000), ep_group=dist.group.WORLD, device=dev)
+        ctx = types.SimpleNamespace(pc=types.SimpleNamespace(comm_timeout_ms=5000, ep_slot_factor=slot_factor),
+                                    ep_group=dist.group.WORLD, device=dev)
         holder = torch.nn.ModuleList([part])
         fused_ep.attach(holder, ctx)
         for step in range(2):
@@ -249,6 +250,21 @@ def ep_fused():
                 mine = getattr(part.experts, name).grad.float()
                 ref = full[rank * el:(rank + 1) * el]
                 assert (mine - ref).norm() / ref.norm() < 0.02, name
+    # buffers far too small for the routed rows: nothing is written out of bounds, the layer leaves its code in the
+    # status word and the host learns of it where it reads the word
+    from forgeminds_b200 import ops
+    holder._fm_ep.slot_factor = 0.05
+    x = (torch.randn(n, d, device=dev) * 0.5).to(torch.bfloat16).requires_grad_()
+    out = part(x)
+    out.float().sum().backward()
+    torch.cuda.synchronize()
+    try:
+        holder._fm_ep.sg.check()
+        raise AssertionError("the overflow was not reported")
+    except ops.EPOverflow:
+        pass
+    assert torch.isfinite(out.float()).all() and torch.isfinite(x.grad.float()).all()
+    holder._fm_ep.sg.check()                          # the word was cleared by the report
     dist.barrier()
     if rank == 0:
         print("OK ep_fused", flush=True)

@@ -172,3 +172,21 @@ def test_gather_schedule_copies_every_remote_row_once_nearest_rank_first(world, 
     for cta in range(min(grid, 4)):
         dist = [(src - rank) % world for c, _, src, _ in plan if c == cta]
         assert dist == sorted(dist)
+
+
+def test_bounded_expert_parallel_buffers_cut_the_plan_without_a_host_read():
+    """Row count of bounded dispatch buffers and the clamped slot plan (device-tensor arithmetic only)."""
+    from forgeminds_b200.parallel.ep import ALIGN, bounded_rows, clamp_plan
+    assert bounded_rows(10240, 8192, 4, 2, 0.0) == 10240                     # 0: the worst case
+    assert bounded_rows(10240, 8192, 4, 2, 100.0) == 10240                   # never more than the worst case
+    rows = bounded_rows(10240, 8192, 4, 2, 2.0)
+    assert rows == (2 * 8192 // 4 + 2 * ALIGN + ALIGN - 1) // ALIGN * ALIGN and rows % ALIGN == 0
+    region = torch.tensor([[0, 300, 512], [512, 700, 768], [1280, 100, 256]], dtype=torch.int32)
+    limit = torch.tensor([1536, 0, 0], dtype=torch.int32)
+    r, l, over = clamp_plan(region, limit, 2048)
+    assert torch.equal(r, region) and torch.equal(l, limit) and not bool(over)
+    r, l, over = clamp_plan(region, limit, 1024)
+    assert bool(over) and int(l[0]) == 1024
+    assert r.tolist() == [[0, 300, 512], [512, 512, 512], [1024, 0, 0]]
+    assert int((r[:, 0] + r[:, 2]).max()) <= 1024 and torch.equal(region[0], r[0])
+    assert torch.equal(limit, torch.tensor([1536, 0, 0], dtype=torch.int32))   # inputs are not modified
