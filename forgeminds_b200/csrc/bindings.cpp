@@ -592,6 +592,14 @@ void ep_collect_idx(const std::vector<int64_t>& idx_ptrs, Tensor& out, int64_t n
                         status.data_ptr<int>(), cur_stream()), "ep_collect_idx");
 }
 
+void ep_clamp_plan(Tensor& region, int64_t rows, Tensor& status, int64_t code) {
+  TORCH_CHECK(region.is_cuda() && region.scalar_type() == at::kInt && region.is_contiguous() && region.numel() % 3 == 0);
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1);
+  c10::cuda::CUDAGuard guard(region.device());
+  ok(fmb_ep_clamp_plan(region.data_ptr<int>(), static_cast<int>(region.numel() / 3), static_cast<int>(rows),
+                       status.data_ptr<int>(), static_cast<int>(code), cur_stream()), "ep_clamp_plan");
+}
+
 void ep_gather(const std::vector<int64_t>& x_ptrs, const Tensor& token_of_slot, const Tensor& limit, Tensor& out,
                int64_t tokens_per_rank, const Tensor& flags, int64_t slot, int64_t epoch, double timeout_ms,
                Tensor& status) {
@@ -884,6 +892,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_swiglu_bwd", &gemm_swiglu_bwd);
   m.def("gemm_rowdot", &gemm_rowdot);
   m.def("ep_collect_idx", &ep_collect_idx);
+  m.def("ep_clamp_plan", &ep_clamp_plan);
   m.def("ep_gather", &ep_gather);
   m.def("ep_combine", &ep_combine);
   m.def("ep_combine_bwd", &ep_combine_bwd);

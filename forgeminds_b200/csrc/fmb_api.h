@@ -127,6 +127,9 @@ int fmb_quant_tiles_fp8(const void* x, void* q, float* scale, int rows, int cols
 int fmb_ep_collect_idx(const void* const* idx_ptrs, int* out, long long n, int world, int rank, int e_local,
                        const unsigned* flags, int slot, unsigned epoch, unsigned long long timeout_ns, int* status,
                        cudaStream_t stream);
+// region [n, 3] = {start, used, padded} rows per expert, last row = first row past the live ones: cut to `rows`
+// buffer rows in place; `code` goes to the status word when the plan needed more.
+int fmb_ep_clamp_plan(int* region, int n, int rows, int* status, int code, cudaStream_t stream);
 int fmb_ep_gather(const void* const* x_ptrs, const int* token_of_slot, const int* limit_ptr, void* out,
                   long long max_slots, int d, long long tokens_per_rank, int world, const unsigned* flags, int slot,
                   unsigned epoch, unsigned long long timeout_ns, int* status, cudaStream_t stream);

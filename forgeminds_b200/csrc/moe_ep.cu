@@ -156,9 +156,30 @@ static int ep_grid(long long work) {
   return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
 }
 
+// Cuts a slot plan down to `rows` buffer rows, in place: region[i] = {start, used, padded} of expert i (the
+// last row is the region of the entries other ranks own; its start is the first row past the live ones). A plan
+// that needed more rows leaves `code` in the status word (first error wins).
+__global__ void ep_clamp_plan_kernel(int* __restrict__ region, int n, int rows, int* __restrict__ status, int code) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int start = region[3 * i], used = region[3 * i + 1], padded = region[3 * i + 2];
+  if (i == n - 1 && start > rows && status != nullptr) atomicCAS(status, 0, code);
+  const int s = min(start, rows);
+  region[3 * i] = s;
+  region[3 * i + 1] = max(min(start + used, rows) - s, 0);
+  region[3 * i + 2] = max(min(start + padded, rows) - s, 0);
+}
+
 }  // namespace fmb
 
 using namespace fmb;
+
+extern "C" int fmb_ep_clamp_plan(int* region, int n, int rows, int* status, int code, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (region == nullptr || rows < 0) return -2;
+  ep_clamp_plan_kernel<<<(n + 255) / 256, 256, 0, stream>>>(region, n, rows, status, code);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
 
 FMB_DEBUG_BIND(moe_ep)
 

@@ -136,14 +136,13 @@ class _EPExperts(torch.autograd.Function):
         C.ep_collect_idx(eng.idx_sym.ptrs, all_idx, n * k, rank, e_local, sg.flags.local, eng.s_pub, e_pub,
                          sg.timeout_ms, st)
         slot_of, token_of, region, _meta = C.moe_plan(all_idx, e_local + 1, ALIGN, cap, 1 if cap else 0, plan_slots)
+        if slots < plan_slots:
+            # bounded buffers: rows past them are cut from the plan (one small kernel, in place; `clamp_plan` is its
+            # PyTorch statement), and a layer that needed them leaves a code in the status word, which the step
+            # reads with its loss (the host is not asked here)
+            C.ep_clamp_plan(region, slots, st, ops.ERR_EP_OVERFLOW)
         limit = region[e_local]                                  # [start of the foreign region, ...]: live rows end here
         own = region[:e_local]
-        if slots < plan_slots:
-            # bounded buffers: rows past them are cut from the plan, and a layer that needed them leaves a code
-            # in the status word, which the step reads with its loss (the host is not asked here)
-            own, limit, over = clamp_plan(own, limit, slots)
-            code = torch.full_like(st, ops.ERR_EP_OVERFLOW)
-            st.copy_(torch.where(over & (st == 0), code, st))
         slot_of = torch.where(slot_of >= limit[0], torch.full_like(slot_of, -1), slot_of)   # foreign entries have no slot here
         tile_group = C.moe_tile_groups(own, slots // 128)
         entry_of = torch.full((slots + 1,), -1, dtype=torch.int32, device=x.device)
@@ -175,8 +174,6 @@ class _EPExperts(torch.autograd.Function):
                      e_ys, sg.timeout_ms, st)
         ys_keep = ys.clone()
         sg.barrier(eng.s_done)
-        if slots < plan_slots:        # the backward reads the plan as it was cut to the buffers
-            region = torch.cat([own.view(-1, 3), limit.view(1, 3)])
         ctx.save_for_backward(xs, gu, ys_keep, rw, idx, slot_of, entry_of, region, tile_group, b1, b3, b2)
         ctx.params = (w1, w3, w2)
         ctx.eng = eng
