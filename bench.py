@@ -256,6 +256,64 @@ def reference_failed(rank, exc):
     os._exit(0)
 
 
+TINY = dict(model=dict(vocab_size=32000, dim=256, n_layers=4, n_heads=8, n_kv_heads=2, max_seq=256, tie_embeddings=True),
+            hidden=704, micro_batch=4, grad_accum=2, seq=256,
+            name="tiny gpt dim256 L4 h8/kv2 swiglu704 vocab32000 tied (the reference's own width: ceil64(256 * 8 / 3))")
+
+
+def run_tiny_cpu(args, world: int, rank: int) -> int:
+    """The CPU configuration of the baseline list: tiny GPT, fp32, Gloo, data parallel over ``world`` processes
+    (``torchrun --nproc-per-node 2 bench.py --config tiny [--impl reference]``). Both arms go through their public
+    ``Trainer``; wall-clock time around exactly ``--steps`` steps between barriers, maximum over ranks. A plumbing
+    number of this host's cores, not a B200 number: the line says ``"device": "cpu"``."""
+    if args.impl == "reference":
+        ref = os.path.join(ROOT, "baseline", "_ref")
+        if not os.path.isdir(os.path.join(ref, "forgemind")):
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/forgemind is missing"}))
+            return 0
+        sys.path.insert(0, ref)
+        import forgemind as fm
+        mc = fm.GPTConfig(**TINY["model"])
+        assert ((int(mc.dim * mc.ffn_mult) + 63) // 64) * 64 == TINY["hidden"]
+    else:
+        sys.path.insert(0, ROOT)
+        import forgeminds_b200 as fm
+        mc = fm.GPTConfig(ffn_hidden=TINY["hidden"], **TINY["model"])
+    cfg = fm.ForgeConfig()
+    cfg.parallel.dp_replicate = world
+    cfg.train.__dict__.update(max_steps=10 ** 6, grad_accum=TINY["grad_accum"], lr=3e-4, bf16=False, ac="none",
+                              resume=False, ckpt_every=0, log_every=10 ** 9, warmup_steps=100, seed=1234)
+    ds = Tokens(TINY["model"]["vocab_size"], TINY["seq"], n=256)
+    trainer = fm.Trainer(lambda ctx: fm.GPT(mc), cfg, ds, micro_batch=TINY["micro_batch"])
+    assert trainer.ctx.device.type == "cpu"
+    for _ in range(args.warmup):
+        trainer.train_step()
+    if torch.distributed.is_initialized():
+        torch.distributed.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        loss = trainer.train_step()["loss"]
+    ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    ms = max_over_ranks(ms, "cpu")
+    trainer.close()
+    tokens = TINY["micro_batch"] * TINY["seq"] * TINY["grad_accum"] * world
+    if rank == 0:
+        print(json.dumps({
+            "metric": "tokens_per_sec", "value": tokens / (ms / 1e3), "unit": "tokens/s", "device": "cpu", "n_gpus": 0,
+            "n_processes": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "impl": args.impl,
+            "data": "synthetic uniform tokens, random-init weights", "final_loss": loss,
+            "config": {"model": TINY["name"], "global_batch": TINY["micro_batch"] * TINY["grad_accum"] * world,
+                       "micro_batch": TINY["micro_batch"], "grad_accum": TINY["grad_accum"], "seq_len": TINY["seq"],
+                       "parallelism": f"dp_replicate{world} (gloo)", "optimizer": "adamw lr3e-4", "ac": "none",
+                       "threads_per_process": torch.get_num_threads()}}), flush=True)
+    if torch.distributed.is_initialized():
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+    return 0
+
+
 def full_model_flops_per_token(spec, moe: bool) -> int:
     """``6 * active parameters + 12 * layers * dim * seq`` of the WHOLE model (the reference's MFU
     convention, ``forgemind/models/gpt.py:239-246``), whatever slice of it this rank holds."""
@@ -278,7 +336,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="dense", choices=sorted(CONFIGS))
+    ap.add_argument("--config", default="dense", choices=sorted(CONFIGS) + ["tiny"],
+                    help="tiny: the CPU / Gloo configuration (fp32), run under torchrun on this host's cores")
     ap.add_argument("--quant", default="none", choices=["none", "fp8", "int8"],
                     help="8-bit GEMMs of this library (the reference's fp8 / int8 need libraries the image lacks)")
     ap.add_argument("--optimizer", default="adamw", choices=["adamw", "muon"])
@@ -298,6 +357,9 @@ def main() -> int:
                "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29511"), __file__,
                *sys.argv[1:]]
         return subprocess.call(cmd)
+    if args.config == "tiny":
+        os.environ.setdefault("CUDA_VISIBLE_DEVICES", "")          # this configuration is a CPU run wherever it starts
+        return run_tiny_cpu(args, world, rank)
     if not torch.cuda.is_available():
         if rank == 0:
             print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device visible"}))

@@ -42,3 +42,13 @@ def test_flop_count_matches_the_model_and_meshes_multiply_out():
             size *= mesh.get(key, 1)
         assert size == world, (name, world, mesh)
         assert world % b.CONFIGS[name].get("min_world", 1) == 0
+
+
+def test_cpu_configuration_runs_through_the_public_trainer():
+    """``--config tiny`` is the baseline list's CPU / Gloo configuration: one process here, two steps."""
+    out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--config", "tiny", "--steps", "2", "--warmup", "1"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["device"] == "cpu" and line["dtype"] == "fp32" and line["impl"] == "ours"
+    assert line["value"] > 0 and line["config"]["seq_len"] == 256 and 9.0 < line["final_loss"] < 11.5
