@@ -10,6 +10,16 @@ import dataclasses
 from dataclasses import dataclass, field
 
 
+def _one_of(owner: str, name: str, value, allowed) -> None:
+    if value not in allowed:
+        raise ValueError(f"{owner}.{name} must be one of {', '.join(repr(a) for a in allowed)}; got {value!r}")
+
+
+def _at_least(owner: str, name: str, value, low) -> None:
+    if not isinstance(value, (int, float)) or isinstance(value, bool) or value < low:
+        raise ValueError(f"{owner}.{name} must be a number >= {low}; got {value!r}")
+
+
 @dataclass
 class ParallelConfig:
     """Device mesh: ``world = pp * dp_replicate * dp_shard * tp``; ``dp_shard=-1`` takes the rest.
@@ -42,6 +52,30 @@ class ParallelConfig:
                                        # average share of the routed rows (0: the worst case, every row); a layer
                                        # that needs more raises fm.ops.EPOverflow at the step's host read
 
+    def check(self, world: int | None = None) -> None:
+        """Raise ``ValueError`` for a mesh that cannot exist; with ``world`` also for one that does not fill it."""
+        _one_of("parallel", "backend", self.backend, ("native", "deepspeed"))
+        _one_of("parallel", "pp_schedule", self.pp_schedule, ("1f1b", "gpipe"))
+        for name in ("dp_replicate", "tp", "pp", "ep", "pp_microbatches"):
+            _at_least("parallel", name, getattr(self, name), 1)
+        if self.dp_shard != -1:
+            _at_least("parallel", "dp_shard", self.dp_shard, 1)
+        _at_least("parallel", "comm_timeout_ms", self.comm_timeout_ms, 1)
+        _at_least("parallel", "ep_slot_factor", self.ep_slot_factor, 0)
+        _at_least("parallel", "fsdp_resident_bytes", self.fsdp_resident_bytes, 0)
+        _one_of("parallel", "zero_stage", self.zero_stage, (0, 1, 2, 3))
+        if world is not None:
+            fixed = self.dp_replicate * self.tp * self.pp
+            if world % fixed:
+                raise ValueError(f"parallel: dp_replicate * tp * pp = {fixed} does not divide the {world} processes")
+            shard = world // fixed if self.dp_shard == -1 else self.dp_shard
+            if fixed * shard != world:
+                raise ValueError(f"parallel: pp {self.pp} x dp_replicate {self.dp_replicate} x dp_shard {shard} x tp "
+                                 f"{self.tp} = {fixed * shard} processes, but {world} were started")
+            if (self.dp_replicate * shard) % self.ep:
+                raise ValueError(f"parallel.ep = {self.ep} must divide dp_replicate * dp_shard = "
+                                 f"{self.dp_replicate * shard}")
+
 
 @dataclass
 class QuantConfig:
@@ -51,6 +85,11 @@ class QuantConfig:
     optimizer_8bit: bool = False
     # ---- additions
     fp8_block: int = 128               # scale granularity of the block-scaled fp8 GEMM (1x128 act, 128x128 weight)
+
+    def check(self) -> None:
+        _one_of("quant", "mode", self.mode, ("none", "fp8", "int8", "int8_wo"))
+        _one_of("quant", "backend", self.backend, ("auto", "native", "te", "torchao"))
+        _at_least("quant", "fp8_block", self.fp8_block, 1)
 
 
 @dataclass
@@ -65,6 +104,15 @@ class OffloadConfig:
     act_pool: bool = True
     pipeline_chunks: int = 4
     experts: bool = False
+
+    def check(self) -> None:
+        _at_least("offload", "min_numel", self.min_numel, 0)
+        _at_least("offload", "act_min_bytes", self.act_min_bytes, 0)
+        _at_least("offload", "pipeline_chunks", self.pipeline_chunks, 1)
+        if not 0.0 <= float(self.act_layers) <= 1.0:
+            raise ValueError(f"offload.act_layers is the fraction of blocks to wrap, 0..1; got {self.act_layers!r}")
+        if not 0.0 <= float(self.gpu_watermark) <= 1.0:
+            raise ValueError(f"offload.gpu_watermark is a fraction of device memory, 0..1; got {self.gpu_watermark!r}")
 
 
 @dataclass
@@ -107,6 +155,20 @@ class TrainConfig:
     muon_momentum: float = 0.95
     muon_ns_steps: int = 5
 
+    def check(self) -> None:
+        _one_of("train", "ac", self.ac, ("none", "full", "selective"))
+        _one_of("train", "optimizer", self.optimizer, ("adamw", "muon"))
+        for name in ("max_steps", "warmup_steps", "eval_every", "eval_steps", "ckpt_every", "workers"):
+            _at_least("train", name, getattr(self, name), 0)
+        for name in ("grad_accum", "log_every", "prefetch_depth", "muon_ns_steps"):
+            _at_least("train", name, getattr(self, name), 1)
+        for name in ("lr", "weight_decay", "grad_clip", "skip_spike_factor", "min_lr_ratio", "muon_lr"):
+            _at_least("train", name, getattr(self, name), 0)
+        if len(self.betas) != 2 or not all(0.0 <= float(b) < 1.0 for b in self.betas):
+            raise ValueError(f"train.betas must be two numbers in [0, 1); got {self.betas!r}")
+        if not float(self.eps) > 0:
+            raise ValueError(f"train.eps must be positive; got {self.eps!r}")
+
 
 @dataclass
 class ForgeConfig:
@@ -117,3 +179,12 @@ class ForgeConfig:
 
     def to_dict(self) -> dict:
         return dataclasses.asdict(self)
+
+    def check(self, world: int | None = None) -> "ForgeConfig":
+        """Validate every section (``fm.Trainer`` calls this before it builds anything): a misspelt mode or a mesh
+        that does not multiply out is reported here, by field name, instead of somewhere inside the run."""
+        self.parallel.check(world)
+        self.quant.check()
+        self.offload.check()
+        self.train.check()
+        return self

@@ -74,6 +74,8 @@ class Trainer:
         self.cfg, self.micro_batch = cfg, micro_batch
         self.callbacks, self.peak_flops = list(callbacks), peak_flops
         tc, pc = cfg.train, cfg.parallel
+        if hasattr(cfg, "check"):          # misspelt modes and meshes that do not multiply out are named here, by field
+            cfg.check(int(os.environ.get("WORLD_SIZE", "1")))
         self.ctx = ctx = init_distributed(pc)
         self.use_ds = pc.backend == "deepspeed"
         self.engine_notes: list = []

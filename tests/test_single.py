@@ -121,3 +121,28 @@ def test_flops_and_params_follow_reference_formula():
         m = fm.GPT(mc)
     assert m.num_params() == 336118784
     assert m.flops_per_token(2048) == 2620692480
+
+
+def test_config_check_names_the_offending_field():
+    """A misspelt mode or an impossible mesh is reported by field name before anything is built."""
+    import pytest
+    good = fm.ForgeConfig()
+    good.parallel.dp_shard = -1
+    assert good.check(8) is good
+    for change, world, needle in (
+            (lambda c: setattr(c.train, "ac", "selectiv"), None, "train.ac"),
+            (lambda c: setattr(c.train, "optimizer", "lion"), None, "train.optimizer"),
+            (lambda c: setattr(c.train, "grad_accum", 0), None, "train.grad_accum"),
+            (lambda c: setattr(c.quant, "mode", "fp4"), None, "quant.mode"),
+            (lambda c: setattr(c.offload, "act_layers", 1.5), None, "offload.act_layers"),
+            (lambda c: setattr(c.parallel, "pp_schedule", "zero-bubble"), None, "parallel.pp_schedule"),
+            (lambda c: setattr(c.parallel, "tp", 3), 8, "does not divide"),
+            (lambda c: (setattr(c.parallel, "dp_shard", 8), setattr(c.parallel, "ep", 3)), 8, "parallel.ep")):
+        cfg = fm.ForgeConfig()
+        change(cfg)
+        with pytest.raises(ValueError, match=needle):
+            cfg.check(world)
+    bad = fm.ForgeConfig()
+    bad.train.ac = "sometimes"
+    with pytest.raises(ValueError, match="train.ac"):
+        fm.Trainer(lambda ctx: None, bad, fm.SyntheticLM(64, 8, n=8))
