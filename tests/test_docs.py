@@ -68,3 +68,16 @@ def test_profiles_and_guides_name_existing_files():
             if not os.path.exists(os.path.join(ROOT, ref)):
                 missing.append((os.path.basename(path), ref))
     assert not missing, missing
+
+
+def test_kernel_names_in_the_kernel_guide_exist_in_the_sources():
+    """docs/kernels.md describes the device code kernel by kernel: every ``*_kernel`` it names is in csrc/."""
+    import pathlib
+    import re
+    root = pathlib.Path(__file__).resolve().parent.parent
+    text = (root / "docs" / "kernels.md").read_text()
+    named = set(re.findall(r"`([a-z0-9_]+_kernel)\b", text))
+    assert len(named) >= 15, named
+    sources = "\n".join(p.read_text() for p in (root / "forgeminds_b200" / "csrc").glob("*.cu"))
+    missing = sorted(n for n in named if n not in sources)
+    assert not missing, missing
